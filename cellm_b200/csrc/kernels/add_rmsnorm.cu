@@ -1,0 +1,80 @@
+// Residual add fused with RMSNorm.
+//
+//   all rows:       x[t] += delta[t];  y[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w
+//   selected rows:  v = x[rows[r]] + delta[rows[r]];  y[r] = v / sqrt(mean(v^2) + eps) * w
+//
+// The residual stream x is 32-bit in every mode; sum and norm are 32-bit
+// (crates/cellm-kernels/src/cpu_kernels.rs:17-34 is the formula: the weight is
+// used as it is, with no +1). delta may be absent (a plain norm). One block
+// per row; the order of the sum depends only on the row length, so a row's
+// result does not depend on what else is in the batch.
+#include "common.cuh"
+
+template <typename TA, typename TW>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta,
+                                   const TW* __restrict__ w, TA* __restrict__ y,
+                                   const int* __restrict__ rows, int H, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    float* xr = x + (size_t)t * H;
+    const TA* dr = delta ? delta + (size_t)t * H : nullptr;
+    const bool write_back = (rows == nullptr) && (delta != nullptr);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = xr[i];
+        if (dr) v += to_float(dr[i]);
+        if (write_back) xr[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    TA* yr = y + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = xr[i];
+        if (dr && !write_back) v += to_float(dr[i]);
+        yr[i] = from_float<TA>(v * inv * to_float(w[i]));
+    }
+}
+
+// x: [*, H] float; delta: [*, H] act dtype or null; w: [H]; y: [n_rows, H] act dtype;
+// rows: null (all n_rows rows, x updated in place) or n_rows row indices (x left as is).
+CELLM_API int cellm_add_rmsnorm(float* x, const void* delta, const void* w, int w_dtype, void* y,
+                                const int* rows, int n_rows, int H, float eps, int act_dtype,
+                                cudaStream_t stream) {
+    if (n_rows <= 0) return CELLM_OK;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define LAUNCH(TA, TW)                                                                          \
+    add_rmsnorm_kernel<TA, TW><<<n_rows, threads, 0, stream>>>(x, (const TA*)delta, (const TW*)w, \
+                                                               (TA*)y, rows, H, eps)
+    if (act_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float);
+    else if (act_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16);
+    else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, float);
+    else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return CELLM_ERR_DTYPE;
+#undef LAUNCH
+    CELLM_LAUNCH_CHECK();
+    return CELLM_OK;
+}
+
+// Adds a pending delta into the residual stream without a norm (used when a
+// block's output is not followed by a norm that could absorb it).
+template <typename TA>
+__global__ void residual_add_kernel(float* __restrict__ x, const TA* __restrict__ delta, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += to_float(delta[i]);
+}
+
+CELLM_API int cellm_residual_add(float* x, const void* delta, long long n, int act_dtype,
+                                 cudaStream_t stream) {
+    if (n <= 0) return CELLM_OK;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    if (act_dtype == CELLM_F32)
+        residual_add_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float*)delta, (size_t)n);
+    else if (act_dtype == CELLM_BF16)
+        residual_add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(x, (const __nv_bfloat16*)delta, (size_t)n);
+    else return CELLM_ERR_DTYPE;
+    CELLM_LAUNCH_CHECK();
+    return CELLM_OK;
+}

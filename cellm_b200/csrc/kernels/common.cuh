@@ -1,0 +1,82 @@
+// Shared helpers of the kernel sources: element types, conversions, error codes.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define CELLM_API extern "C" __attribute__((visibility("default")))
+
+// Element type tags passed from the host.
+enum { CELLM_F32 = 0, CELLM_BF16 = 1 };
+
+// Return codes of the C entry points: 0 = launched; a positive value is a
+// cudaError_t; a negative value means the entry point refused its arguments.
+enum {
+    CELLM_OK = 0,
+    CELLM_ERR_DTYPE = -1,   // unknown element type tag
+    CELLM_ERR_SIZE = -2,    // a size the kernel does not take
+    CELLM_ERR_ALIGN = -3,   // a pointer or stride that breaks an alignment rule
+    CELLM_ERR_ARG = -4      // a missing or contradictory argument
+};
+
+// Bits of the device-side error word that kernels set instead of trapping.
+enum {
+    CELLM_DEV_BAD_TOKEN = 1,   // token id outside the vocabulary
+    CELLM_DEV_BAD_PAGE = 2,    // page id outside the pool
+    CELLM_DEV_BAD_SLOT = 4,    // state slot outside the pool
+    CELLM_DEV_WAIT_TIMEOUT = 8 // a bounded wait inside a kernel gave up
+};
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block in a fixed order (warp trees, then warp 0 over the warps'
+// sums), so the result depends only on the values and the block size.
+// `scratch` holds at least 32 floats. Every thread gets the sum.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    return t;
+}
+
+#define CELLM_LAUNCH_CHECK()                         \
+    do {                                             \
+        cudaError_t e__ = cudaGetLastError();        \
+        if (e__ != cudaSuccess) return (int)e__;     \
+    } while (0)

@@ -1,0 +1,31 @@
+// Embedding: out[t, :] = float(table[ids[t], :]) into the 32-bit residual stream.
+// The reference gathers one row per token and refuses an id beyond the
+// vocabulary (crates/cellm-model/src/lfm.rs:817-890). Here a bad id sets a bit
+// in the device error word and its row is written as zeros.
+#include "common.cuh"
+
+template <typename T>
+__global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
+                             const int* __restrict__ ids, int H, int V, int* __restrict__ err) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < V;
+    if (!ok && threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_TOKEN);
+    const T* row = table + (size_t)(ok ? id : 0) * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_float(row[i]) : 0.f;
+}
+
+CELLM_API int cellm_embed(float* out, const void* table, int table_dtype, const int* ids, int T, int H,
+                          int V, int* err, cudaStream_t stream) {
+    if (T <= 0) return CELLM_OK;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == CELLM_F32)
+        embed_kernel<float><<<T, threads, 0, stream>>>(out, (const float*)table, ids, H, V, err);
+    else if (table_dtype == CELLM_BF16)
+        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, H, V, err);
+    else
+        return CELLM_ERR_DTYPE;
+    CELLM_LAUNCH_CHECK();
+    return CELLM_OK;
+}

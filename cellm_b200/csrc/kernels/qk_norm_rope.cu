@@ -1,0 +1,117 @@
+// Per-head RMSNorm of queries and keys, rotary position encoding, and the
+// write of keys and values into the paged cache, in one pass over the
+// projected rows.
+//
+// The reference normalises each head of q and k over head_dim with one eps
+// (crates/cellm-model/src/lfm.rs:486-543), rotates pairs (i, i + rot/2) by
+// pos * theta^(-2i/rot) (crates/cellm-kernels/src/cpu_kernels.rs:264-277; the
+// interleaved pairing (2i, 2i+1) of :279-292 is the other layout), and writes
+// k and v for the token's position (crates/cellm-model/src/lfm.rs:563-566).
+// Values are not normalised. Angles are formed in 64-bit from a table of
+// inverse frequencies the host computed in 64-bit, then cos/sin are rounded to
+// 32-bit, so they carry no error that grows with the position.
+//
+// Cache layout of one layer: [page][kv_head][slot in page][head_dim].
+#include "common.cuh"
+
+template <typename TA, typename TW>
+__global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict__ qkv, long long row_stride,
+                                    const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
+                                    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                    const int* __restrict__ block_table, int bt_stride,
+                                    TA* __restrict__ k_pool, TA* __restrict__ v_pool, int num_pages,
+                                    int page_size, int nh, int nkv, int hd, int rot, int interleaved,
+                                    const double* __restrict__ inv_freq, int* __restrict__ err) {
+    extern __shared__ float smem[];
+    float* cs = smem;                    // [rot/2] cos
+    float* sn = smem + rot / 2;          // [rot/2] sin
+    const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* buf = smem + rot + warp * hd; // one head per warp
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    for (int p = threadIdx.x; p < rot / 2; p += blockDim.x) {
+        double s, c;
+        sincos((double)pos * inv_freq[p], &s, &c);
+        cs[p] = (float)c;
+        sn[p] = (float)s;
+    }
+    long long page_base = -1;
+    if (nkv > 0) {
+        const int b = seq_of_token[t];
+        const int page = block_table[(size_t)b * bt_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_PAGE);
+        } else {
+            page_base = (long long)page * nkv * page_size * hd + (long long)(pos % page_size) * hd;
+        }
+    }
+    __syncthreads();
+    const TA* row = qkv + (size_t)t * row_stride;
+    for (int hh = warp; hh < nh + 2 * nkv; hh += nwarps) {
+        const TA* src = row + (size_t)hh * hd;
+        if (hh >= nh + nkv) {  // value head: copy
+            if (page_base >= 0) {
+                TA* dst = v_pool + page_base + (long long)(hh - nh - nkv) * page_size * hd;
+                for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+            }
+            continue;
+        }
+        const bool is_q = hh < nh;
+        const TW* w = is_q ? q_w : k_w;
+        float ss = 0.f;
+        for (int i = lane; i < hd; i += 32) {
+            const float v = to_float(src[i]);
+            buf[i] = v;
+            ss += v * v;
+        }
+        if (w) {
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+            for (int i = lane; i < hd; i += 32) buf[i] = buf[i] * inv * to_float(w[i]);
+        }
+        __syncwarp();
+        TA* dst;
+        if (is_q) dst = q_out + (size_t)t * nh * hd + (size_t)hh * hd;
+        else if (page_base >= 0) dst = k_pool + page_base + (long long)(hh - nh) * page_size * hd;
+        else { __syncwarp(); continue; }
+        for (int p = lane; p < rot / 2; p += 32) {
+            const int i0 = interleaved ? 2 * p : p;
+            const int i1 = interleaved ? 2 * p + 1 : p + rot / 2;
+            const float a = buf[i0], b = buf[i1];
+            dst[i0] = from_float<TA>(a * cs[p] - b * sn[p]);
+            dst[i1] = from_float<TA>(b * cs[p] + a * sn[p]);
+        }
+        for (int i = rot + lane; i < hd; i += 32) dst[i] = from_float<TA>(buf[i]);
+        __syncwarp();
+    }
+}
+
+// qkv: [T, row_stride] rows holding nh query heads, then nkv key heads, then nkv
+// value heads (nkv = 0: queries only, nothing is written to the cache).
+// q_w, k_w: [hd] norm weights or null (no norm). inv_freq: [rot/2] doubles.
+CELLM_API int cellm_qk_norm_rope(void* q_out, const void* qkv, long long row_stride, const void* q_w,
+                                 const void* k_w, int w_dtype, float eps, const int* positions,
+                                 const int* seq_of_token, const int* block_table, int bt_stride,
+                                 void* k_pool, void* v_pool, int num_pages, int page_size, int T, int nh,
+                                 int nkv, int hd, int rot, int interleaved, const double* inv_freq,
+                                 int act_dtype, int* err, cudaStream_t stream) {
+    if (T <= 0) return CELLM_OK;
+    if (rot < 0 || rot > hd || (rot & 1)) return CELLM_ERR_SIZE;
+    if ((q_w == nullptr) != (k_w == nullptr)) return CELLM_ERR_ARG;
+    const int threads = 128;
+    const size_t smem = (size_t)(rot + (threads / 32) * hd) * sizeof(float);
+    if (smem > 48 * 1024) return CELLM_ERR_SIZE;
+#define LAUNCH(TA, TW)                                                                               \
+    qk_norm_rope_kernel<TA, TW><<<T, threads, smem, stream>>>(                                       \
+        (TA*)q_out, (const TA*)qkv, row_stride, (const TW*)q_w, (const TW*)k_w, eps, positions,      \
+        seq_of_token, block_table, bt_stride, (TA*)k_pool, (TA*)v_pool, num_pages, page_size, nh,    \
+        nkv, hd, rot, interleaved, inv_freq, err)
+    if (act_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float);
+    else if (act_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16);
+    else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, float);
+    else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return CELLM_ERR_DTYPE;
+#undef LAUNCH
+    CELLM_LAUNCH_CHECK();
+    return CELLM_OK;
+}

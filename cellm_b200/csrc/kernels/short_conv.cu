@@ -1,0 +1,109 @@
+// Gated short convolution over portions of sequences, with the state carried
+// between portions (crates/cellm-model/src/lfm.rs:363-405 is the formula for
+// one token; the reference keeps one state per layer for all sessions, here a
+// request has a slot of its own).
+//
+//   bcx[t] = [ B | C | x ]   (three runs of H values, in that order)
+//   bx[t]  = B[t] * x[t]
+//   conv[t][c] = sum_k w[c][k] * bx[t - (taps-1) + k][c]  (+ bias[c])   tap taps-1 meets the current token
+//   y[t]   = C[t] * conv[t]
+//
+// History before the first token of a portion comes from the request's state
+// slot: taps-1 rows of 32-bit bx values, row taps-2 the most recent; a new
+// request's slot is all zeros. The forward kernel only reads the state; the
+// update kernel, launched after it, writes the last taps-1 values of bx (mixing
+// old rows in when the portion is shorter than taps-1).
+#include "common.cuh"
+
+#define SHORT_CONV_MAX_TAPS 16
+
+template <typename TA, typename TW>
+__global__ void short_conv_fwd_kernel(TA* __restrict__ y, const TA* __restrict__ bcx,
+                                      const TW* __restrict__ w, const TW* __restrict__ bias,
+                                      const float* __restrict__ state, long long slot_stride,
+                                      const int* __restrict__ slot_ids, const int* __restrict__ seq_of_token,
+                                      const int* __restrict__ cu_seqlens, int H, int taps, int n_slots,
+                                      int* __restrict__ err) {
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= H) return;
+    const int b = seq_of_token[t];
+    const int i = t - cu_seqlens[b];
+    const int slot = slot_ids[b];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_SLOT);
+        return;
+    }
+    const float* st = state + (long long)slot * slot_stride;
+    float acc = 0.f;
+    for (int k = 0; k < taps; ++k) {
+        const int j = i - (taps - 1) + k;
+        float v;
+        if (j >= 0) {
+            const TA* row = bcx + (size_t)(t - (taps - 1) + k) * 3 * H;
+            v = to_float(row[c]) * to_float(row[2 * H + c]);
+        } else {
+            v = st[(size_t)(taps - 1 + j) * H + c];
+        }
+        acc += v * to_float(w[(size_t)c * taps + k]);
+    }
+    if (bias) acc += to_float(bias[c]);
+    y[(size_t)t * H + c] = from_float<TA>(to_float(bcx[(size_t)t * 3 * H + H + c]) * acc);
+}
+
+template <typename TA>
+__global__ void short_conv_state_kernel(const TA* __restrict__ bcx, float* __restrict__ state,
+                                        long long slot_stride, const int* __restrict__ slot_ids,
+                                        const int* __restrict__ cu_seqlens, int H, int taps, int n_slots) {
+    const int b = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= H) return;
+    const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+    const int slot = slot_ids[b];
+    if (n <= 0 || slot < 0 || slot >= n_slots) return;
+    float* st = state + (long long)slot * slot_stride;
+    const int rows = taps - 1;
+    float old[SHORT_CONV_MAX_TAPS];
+    for (int r = 0; r < rows; ++r) old[r] = st[(size_t)r * H + c];
+    for (int r = 0; r < rows; ++r) {
+        const int j = n - rows + r;
+        float v;
+        if (j >= 0) {
+            const TA* row = bcx + (size_t)(start + j) * 3 * H;
+            v = to_float(row[c]) * to_float(row[2 * H + c]);
+        } else {
+            v = old[r + n];
+        }
+        st[(size_t)r * H + c] = v;
+    }
+}
+
+// y: [T, H]; bcx: [T, 3H]; w: [H, taps]; bias: [H] or null; state: this layer's
+// [n_slots][taps-1][H] floats with slot_stride floats between slots.
+CELLM_API int cellm_short_conv(void* y, const void* bcx, const void* w, const void* bias, int w_dtype,
+                               float* state, long long slot_stride, const int* slot_ids,
+                               const int* seq_of_token, const int* cu_seqlens, int T, int B, int H,
+                               int taps, int n_slots, int act_dtype, int* err, cudaStream_t stream) {
+    if (T <= 0) return CELLM_OK;
+    if (taps < 1 || taps > SHORT_CONV_MAX_TAPS) return CELLM_ERR_SIZE;
+    const int threads = 128;
+    dim3 grid_f((unsigned)T, (unsigned)((H + threads - 1) / threads));
+    dim3 grid_s((unsigned)B, (unsigned)((H + threads - 1) / threads));
+#define LAUNCH(TA, TW)                                                                              \
+    do {                                                                                            \
+        short_conv_fwd_kernel<TA, TW><<<grid_f, threads, 0, stream>>>(                              \
+            (TA*)y, (const TA*)bcx, (const TW*)w, (const TW*)bias, state, slot_stride, slot_ids,    \
+            seq_of_token, cu_seqlens, H, taps, n_slots, err);                                       \
+        if (taps > 1)                                                                               \
+            short_conv_state_kernel<TA><<<grid_s, threads, 0, stream>>>(                            \
+                (const TA*)bcx, state, slot_stride, slot_ids, cu_seqlens, H, taps, n_slots);        \
+    } while (0)
+    if (act_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float);
+    else if (act_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16);
+    else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, float);
+    else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return CELLM_ERR_DTYPE;
+#undef LAUNCH
+    CELLM_LAUNCH_CHECK();
+    return CELLM_OK;
+}

@@ -1,0 +1,29 @@
+// SwiGLU gate: h[t, j] = g * sigmoid(g) * u with g = gu[t, j], u = gu[t, ff + j]
+// (crates/cellm-model/src/lfm.rs:648-654; the two products W1 m and W3 m arrive
+// side by side from one matrix product over the stacked weights). 32-bit math.
+#include "common.cuh"
+
+template <typename T>
+__global__ void swiglu_kernel(T* __restrict__ h, const T* __restrict__ gu, int ff, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t t = i / ff;
+    const int j = (int)(i - t * ff);
+    const float g = to_float(gu[t * 2 * ff + j]);
+    const float u = to_float(gu[t * 2 * ff + ff + j]);
+    h[i] = from_float<T>(g * (1.0f / (1.0f + expf(-g))) * u);
+}
+
+CELLM_API int cellm_swiglu(void* h, const void* gu, int T, int ff, int dtype, cudaStream_t stream) {
+    const size_t n = (size_t)T * ff;
+    if (n == 0) return CELLM_OK;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    if (dtype == CELLM_F32)
+        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((float*)h, (const float*)gu, ff, n);
+    else if (dtype == CELLM_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)h, (const __nv_bfloat16*)gu, ff, n);
+    else return CELLM_ERR_DTYPE;
+    CELLM_LAUNCH_CHECK();
+    return CELLM_OK;
+}

@@ -1,0 +1,199 @@
+// C entry points of the host runtime (cache manager and scheduler), called
+// from Python through ctypes. Every function returns a status (0 or a count
+// on success, negative on error); the message of the last error of the calling
+// thread is read with cellm_last_error().
+#include <cstring>
+#include <string>
+
+#include "cache_manager.h"
+#include "scheduler.h"
+
+#define API extern "C" __attribute__((visibility("default")))
+
+namespace {
+thread_local std::string g_error;
+thread_local cellm::StepPlan g_plan;
+
+template <typename F>
+int guarded(F&& f) {
+    try {
+        return f();
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return -1;
+    } catch (...) {
+        g_error = "unknown error";
+        return -1;
+    }
+}
+}  // namespace
+
+API const char* cellm_last_error() { return g_error.c_str(); }
+
+// ------------------------------------------------------------------ cache
+API void* cellm_cache_create(int page_size, int n_groups, const int* pages, const int* windows, int num_slots) {
+    try {
+        std::vector<cellm::GroupSpec> groups;
+        for (int g = 0; g < n_groups; ++g) groups.push_back({pages[g], windows[g]});
+        return new cellm::CacheManager(page_size, std::move(groups), num_slots);
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return nullptr;
+    }
+}
+API void cellm_cache_destroy(void* c) { delete static_cast<cellm::CacheManager*>(c); }
+API int cellm_cache_add(void* c, long long id) {
+    return guarded([&] {
+        const int slot = static_cast<cellm::CacheManager*>(c)->add_request(id);
+        if (slot < 0) { g_error = "cache: no free state slot"; return -2; }
+        return slot;
+    });
+}
+API int cellm_cache_reserve(void* c, long long id, int new_total) {
+    return guarded([&] { return static_cast<cellm::CacheManager*>(c)->reserve(id, new_total) ? 1 : 0; });
+}
+API int cellm_cache_can_reserve(void* c, long long id, int new_total) {
+    return guarded([&] { return static_cast<cellm::CacheManager*>(c)->can_reserve(id, new_total) ? 1 : 0; });
+}
+API int cellm_cache_commit(void* c, long long id, int new_total) {
+    return guarded([&] { static_cast<cellm::CacheManager*>(c)->commit(id, new_total); return 0; });
+}
+API int cellm_cache_release(void* c, long long id) {
+    return guarded([&] { static_cast<cellm::CacheManager*>(c)->release(id); return 0; });
+}
+API int cellm_cache_has(void* c, long long id) { return static_cast<cellm::CacheManager*>(c)->has(id) ? 1 : 0; }
+API int cellm_cache_tokens(void* c, long long id) {
+    return guarded([&] { return static_cast<cellm::CacheManager*>(c)->request(id).tokens; });
+}
+API int cellm_cache_slot(void* c, long long id) {
+    return guarded([&] { return static_cast<cellm::CacheManager*>(c)->request(id).slot; });
+}
+// Copies the request's block table of group g into out (capacity cap); returns its length.
+API int cellm_cache_block_table(void* c, long long id, int g, int* out, int cap) {
+    return guarded([&] {
+        const auto& b = static_cast<cellm::CacheManager*>(c)->request(id).blocks.at((size_t)g);
+        if ((int)b.size() > cap) { g_error = "cache: block table longer than the buffer"; return -3; }
+        if (!b.empty()) std::memcpy(out, b.data(), b.size() * sizeof(int));
+        return (int)b.size();
+    });
+}
+API int cellm_cache_free_pages(void* c, int g) {
+    return guarded([&] { return static_cast<cellm::CacheManager*>(c)->free_pages(g); });
+}
+API int cellm_cache_free_slots(void* c) { return static_cast<cellm::CacheManager*>(c)->free_slots(); }
+API int cellm_cache_live(void* c) { return static_cast<cellm::CacheManager*>(c)->live_requests(); }
+API int cellm_cache_pages_for(void* c, int g, int tokens, int portion) {
+    return guarded([&] { return static_cast<cellm::CacheManager*>(c)->pages_for(g, tokens, portion); });
+}
+
+// -------------------------------------------------------------- allocator
+API void* cellm_alloc_create(int total) {
+    try { return new cellm::BlockAllocator(total); } catch (const std::exception& e) { g_error = e.what(); return nullptr; }
+}
+API void cellm_alloc_destroy(void* a) { delete static_cast<cellm::BlockAllocator*>(a); }
+API int cellm_alloc_alloc(void* a) { return static_cast<cellm::BlockAllocator*>(a)->alloc(); }
+API int cellm_alloc_alloc_n(void* a, int n, int* out) {
+    return guarded([&] {
+        std::vector<int32_t> v;
+        if (!static_cast<cellm::BlockAllocator*>(a)->alloc_n(n, v)) return 0;
+        if (n > 0) std::memcpy(out, v.data(), (size_t)n * sizeof(int));
+        return 1;
+    });
+}
+API int cellm_alloc_free(void* a, int id) {
+    return guarded([&] { static_cast<cellm::BlockAllocator*>(a)->free(id); return 0; });
+}
+API int cellm_alloc_free_count(void* a) { return static_cast<cellm::BlockAllocator*>(a)->free_count(); }
+API int cellm_alloc_is_free(void* a, int id) {
+    return guarded([&] { return static_cast<cellm::BlockAllocator*>(a)->is_free(id) ? 1 : 0; });
+}
+
+// -------------------------------------------------------------- scheduler
+API void* cellm_sched_create(void* cache, int max_batch_tokens, int prefill_chunk, int max_positions) {
+    try {
+        cellm::SchedulerConfig cfg;
+        cfg.max_batch_tokens = max_batch_tokens;
+        cfg.prefill_chunk = prefill_chunk;
+        cfg.max_positions = max_positions;
+        return new cellm::Scheduler(cfg, static_cast<cellm::CacheManager*>(cache));
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return nullptr;
+    }
+}
+API void cellm_sched_destroy(void* s) { delete static_cast<cellm::Scheduler*>(s); }
+API int cellm_sched_add(void* s, long long id, const int* tokens, int n, int max_new) {
+    return guarded([&] { static_cast<cellm::Scheduler*>(s)->add_request(id, tokens, n, max_new); return 0; });
+}
+// Plans the next step and keeps the plan for the calling thread; returns the
+// number of entries. The plan's parts are then read with the *_plan_* calls.
+API int cellm_sched_schedule(void* s) {
+    return guarded([&] {
+        g_plan = static_cast<cellm::Scheduler*>(s)->schedule();
+        return (int)g_plan.entries.size();
+    });
+}
+API int cellm_sched_plan_entries(long long* ids, int* starts, int* counts, int* wants, int cap) {
+    const int n = (int)g_plan.entries.size();
+    if (n > cap) return -3;
+    for (int i = 0; i < n; ++i) {
+        ids[i] = g_plan.entries[(size_t)i].id;
+        starts[i] = g_plan.entries[(size_t)i].start;
+        counts[i] = g_plan.entries[(size_t)i].count;
+        wants[i] = g_plan.entries[(size_t)i].wants_logits;
+    }
+    return n;
+}
+API int cellm_sched_plan_preempted(long long* ids, int cap) {
+    const int n = (int)g_plan.preempted.size();
+    if (n > cap) return -3;
+    for (int i = 0; i < n; ++i) ids[i] = g_plan.preempted[(size_t)i];
+    return n;
+}
+API int cellm_sched_plan_admitted(long long* ids, int* slots, int cap) {
+    const int n = (int)g_plan.admitted.size();
+    if (n > cap) return -3;
+    for (int i = 0; i < n; ++i) { ids[i] = g_plan.admitted[(size_t)i].first; slots[i] = g_plan.admitted[(size_t)i].second; }
+    return n;
+}
+API int cellm_sched_step_done(void* s) {
+    return guarded([&] { static_cast<cellm::Scheduler*>(s)->step_done(g_plan); return 0; });
+}
+API int cellm_sched_append(void* s, long long id, int token, int stop) {
+    return guarded([&] { return static_cast<cellm::Scheduler*>(s)->append_token(id, token, stop != 0) ? 1 : 0; });
+}
+API int cellm_sched_cancel(void* s, long long id) {
+    return guarded([&] { static_cast<cellm::Scheduler*>(s)->cancel(id); return 0; });
+}
+API int cellm_sched_forget(void* s, long long id) {
+    return guarded([&] { static_cast<cellm::Scheduler*>(s)->forget(id); return 0; });
+}
+API int cellm_sched_has(void* s, long long id) { return static_cast<cellm::Scheduler*>(s)->has(id) ? 1 : 0; }
+// info[0..5] = state, prompt_len, number of tokens, computed, generated, preemptions
+API int cellm_sched_info(void* s, long long id, int* info) {
+    return guarded([&] {
+        const auto& r = static_cast<cellm::Scheduler*>(s)->request(id);
+        info[0] = (int)r.state; info[1] = r.prompt_len; info[2] = (int)r.tokens.size();
+        info[3] = r.computed; info[4] = r.generated; info[5] = r.preemptions;
+        return 0;
+    });
+}
+API int cellm_sched_tokens(void* s, long long id, int from, int* out, int cap) {
+    return guarded([&] {
+        const auto& r = static_cast<cellm::Scheduler*>(s)->request(id);
+        const int n = (int)r.tokens.size() - from;
+        if (from < 0 || n < 0) { g_error = "scheduler: token range out of bounds"; return -3; }
+        if (n > cap) { g_error = "scheduler: token buffer too small"; return -3; }
+        if (n > 0) std::memcpy(out, r.tokens.data() + from, (size_t)n * sizeof(int));
+        return n;
+    });
+}
+API const char* cellm_sched_finish_reason(void* s, long long id) {
+    try { return static_cast<cellm::Scheduler*>(s)->request(id).finish_reason.c_str(); } catch (...) { return ""; }
+}
+// stats[0..5] = waiting, running, steps, tokens scheduled, preemptions, idle
+API void cellm_sched_stats(void* s, long long* stats) {
+    auto* sc = static_cast<cellm::Scheduler*>(s);
+    stats[0] = sc->num_waiting(); stats[1] = sc->num_running(); stats[2] = (long long)sc->steps();
+    stats[3] = (long long)sc->tokens_scheduled(); stats[4] = (long long)sc->preemptions(); stats[5] = sc->idle() ? 1 : 0;
+}

@@ -1,0 +1,81 @@
+"""ctypes bindings to the compiled kernels. A missing or unbuildable library
+raises at first use; there is no fallback to another implementation."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..csrc import build as _build
+
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+
+DTYPE_TAG = {torch.float32: 0, torch.bfloat16: 1}
+
+_ERRORS = {-1: "unsupported element type", -2: "a size this kernel does not take",
+           -3: "a pointer or stride breaks an alignment rule", -4: "missing or contradictory argument"}
+
+_SIGNATURES = {
+    "kernels_common": {
+        "cellm_embed": [P, P, I, P, I, I, I, P, P],
+        "cellm_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P],
+        "cellm_residual_add": [P, P, L, I, P],
+        "cellm_swiglu": [P, P, I, I, I, P],
+        "cellm_short_conv": [P, P, P, P, I, P, L, P, P, P, I, I, I, I, I, I, P, P],
+        "cellm_qk_norm_rope": [P, P, L, P, P, I, F, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, I, P, P],
+        "cellm_attention_plain": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P],
+        "cellm_argmax": [P, P, I, I, P],
+    },
+    "gemm_plain": {
+        "cellm_gemm_plain": [P, P, P, I, I, I, L, L, L, I, I, P],
+    },
+}
+
+_funcs: dict[str, ctypes._CFuncPtr] = {}
+
+
+def register_signatures(library: str, signatures: dict) -> None:
+    _SIGNATURES.setdefault(library, {}).update(signatures)
+
+
+def fn(library: str, name: str):
+    f = _funcs.get(name)
+    if f is None:
+        lib = _build.load(library)
+        f = getattr(lib, name)
+        f.argtypes = _SIGNATURES[library][name]
+        f.restype = c_int
+        _funcs[name] = f
+    return f
+
+
+def check(code: int, name: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise ValueError(f"{name}: refused: {_ERRORS.get(code, code)}")
+    raise RuntimeError(f"{name}: CUDA error {code} at launch")
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def tag(t_or_dtype) -> int:
+    dt = t_or_dtype if isinstance(t_or_dtype, torch.dtype) else t_or_dtype.dtype
+    try:
+        return DTYPE_TAG[dt]
+    except KeyError:
+        raise ValueError(f"element type {dt} is not supported by the kernels") from None
+
+
+def stream_of(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise ValueError("kernel arguments must be contiguous CUDA tensors "
+                             f"(got device={t.device}, contiguous={t.is_contiguous()})")

@@ -1,0 +1,51 @@
+"""Gated short convolution mixer (crates/cellm-model/src/lfm.rs:350-417):
+in_proj to B | C | x, B*x, a causal depthwise convolution over the last `taps`
+values of B*x, times C, out_proj. Its per-request state is the last taps-1
+values of B*x, in a slot of fixed size."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.errors import ConfigError
+from .base import CacheBinding, FixedState, Mixer, StepContext, TensorSpec
+from .linear import Linear
+from .registry import register_mixer
+
+
+class ShortConvMixer(Mixer):
+    """params: hidden_size, taps, bias. weights: in_proj [3H, H], conv [H, 1, taps],
+    out_proj [H, H], conv_bias [H] if bias."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        H, taps = params["hidden_size"], params["taps"]
+        specs = {"in_proj": TensorSpec((3 * H, H), "linear"), "conv": TensorSpec((H, 1, taps), "conv_tap"),
+                 "out_proj": TensorSpec((H, H), "linear")}
+        if params.get("bias"):
+            specs["conv_bias"] = TensorSpec((H,), "bias")
+        return specs
+
+    @classmethod
+    def cache_need(cls, params):
+        return FixedState((max(int(params["taps"]) - 1, 0), int(params["hidden_size"])), torch.float32)
+
+    def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        self.H, self.taps = int(params["hidden_size"]), int(params["taps"])
+        if not 1 <= self.taps <= 16:
+            raise ConfigError(f"short_conv: {self.taps} taps; the kernel takes 1 to 16")
+        self.in_proj = Linear(weights["in_proj"], dtype)
+        self.out_proj = Linear(weights["out_proj"], dtype)
+        self.conv_w = weights["conv"].reshape(self.H, self.taps).contiguous()
+        self.conv_b = None
+        if params.get("bias"):
+            self.conv_b = weights["conv_bias"].to(self.conv_w.dtype).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        bcx = self.in_proj(x)
+        y = ops.short_conv(bcx, self.conv_w, self.conv_b, cache.state, ctx.slot_ids, ctx.seq_of_token,
+                           ctx.cu_seqlens, ctx.err)
+        return self.out_proj(y)
+
+
+register_mixer("short_conv", ShortConvMixer)
