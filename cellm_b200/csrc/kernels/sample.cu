@@ -46,3 +46,270 @@ CELLM_API int cellm_argmax(int* out, const float* logits, int R, int V, cudaStre
     CELLM_LAUNCH_CHECK();
     return CELLM_OK;
 }
+
+// ------------------------------------------------------- temperature sampling
+// One block per row. With top_k > 0 the k largest logits are the candidates, in
+// descending order of logit and ascending id among equal logits (a stable
+// descending sort, crates/cellm-model/src/lfm.rs:813); with top_k = 0 the
+// whole row is, in the order of the ids. Then, as tools/infer's select_next
+// (tools/infer/src/main.rs:958-1016): candidates seen among the `recent` tokens
+// have their score divided by repeat_penalty (if > 1); weights are
+// exp((s - max) / temperature); r = u * sum; the first candidate whose running
+// sum reaches r is taken. temperature <= 0 takes the arg-max. One thread walks
+// the top-k candidates in order, so sums round as in the reference.
+#define SAMPLE_THREADS 1024
+#define SAMPLE_MAX_K 1024
+
+__device__ __forceinline__ uint32_t float_key(float v) {
+    if (!isfinite(v)) v = -INFINITY;
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+
+// Inclusive scan of one value per thread over the block; returns this thread's
+// prefix and, through `total`, the block's sum. Fixed order.
+__device__ __forceinline__ float block_scan_inclusive(float v, float* warp_tot, float* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+    }
+    __syncthreads();
+    if (lane == 31) warp_tot[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float w = lane < nw ? warp_tot[lane] : 0.f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += t;
+        }
+        warp_tot[lane] = w;
+    }
+    __syncthreads();
+    const float base = warp > 0 ? warp_tot[warp - 1] : 0.f;
+    *total = warp_tot[nw - 1];
+    return v + base;
+}
+
+__device__ __forceinline__ int block_scan_inclusive_int(int v, int* warp_tot, int* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+    }
+    __syncthreads();
+    if (lane == 31) warp_tot[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        int w = lane < nw ? warp_tot[lane] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += t;
+        }
+        warp_tot[lane] = w;
+    }
+    __syncthreads();
+    const int base = warp > 0 ? warp_tot[warp - 1] : 0;
+    *total = warp_tot[nw - 1];
+    return v + base;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
+              const float* __restrict__ temperature, const int* __restrict__ top_k,
+              const float* __restrict__ u, const float* __restrict__ penalty,
+              const int* __restrict__ recent, int W) {
+    __shared__ unsigned long long cand[SAMPLE_MAX_K];
+    __shared__ int hist[256];
+    __shared__ float fscratch[32];
+    __shared__ int iscratch[32];
+    __shared__ int s_recent[256];
+    __shared__ uint32_t s_prefix, s_mask;
+    __shared__ int s_krem, s_cnt, s_pick;
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* row = logits + (size_t)r * V;
+    const float temp = temperature[r];
+    const float pen = penalty ? penalty[r] : 1.0f;
+    const int nrec = (pen > 1.0f && recent) ? min(W, 256) : 0;
+    for (int i = tid; i < nrec; i += blockDim.x) s_recent[i] = recent[(size_t)r * W + i];
+    __syncthreads();
+
+    if (temp <= 0.0f) {  // arg-max, lowest id among equals
+        float best = -INFINITY;
+        int idx = 0x7fffffff;
+        for (int i = tid; i < V; i += blockDim.x) {
+            float v = row[i];
+            if (!isfinite(v)) v = -INFINITY;
+            if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+        }
+        unsigned long long key = ((unsigned long long)float_key(best) << 32) | (0xffffffffu - (uint32_t)idx);
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long t = __shfl_xor_sync(0xffffffffu, key, o);
+            key = t > key ? t : key;
+        }
+        if ((tid & 31) == 0) cand[tid >> 5] = key;
+        __syncthreads();
+        if (tid < 32) {
+            key = cand[tid];
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long t = __shfl_xor_sync(0xffffffffu, key, o);
+                key = t > key ? t : key;
+            }
+            if (tid == 0) out[r] = (int)(0xffffffffu - (uint32_t)(key & 0xffffffffu));
+        }
+        return;
+    }
+
+    int k = top_k[r];
+    if (k >= V) k = 0;
+    if (k > 0) {
+        // ---- radix select of the k-th largest key
+        if (tid == 0) { s_prefix = 0; s_mask = 0; s_krem = k; s_cnt = 0; }
+        __syncthreads();
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            if (tid < 256) hist[tid] = 0;
+            __syncthreads();
+            const uint32_t prefix = s_prefix, mask = s_mask;
+            for (int i = tid; i < V; i += blockDim.x) {
+                const uint32_t key = float_key(row[i]);
+                if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int rem = s_krem, b = 255;
+                for (; b > 0; --b) {
+                    if (hist[b] >= rem) break;
+                    rem -= hist[b];
+                }
+                s_krem = rem;
+                s_prefix = prefix | ((uint32_t)b << shift);
+                s_mask = mask | (0xffu << shift);
+            }
+            __syncthreads();
+        }
+        const uint32_t kth = s_prefix;
+        const int need_eq = s_krem;          // how many keys equal to kth are taken
+        const int n_gt = k - need_eq;        // keys above kth
+        for (int i = tid; i < V; i += blockDim.x) {
+            const uint32_t key = float_key(row[i]);
+            if (key > kth) {
+                const int p = atomicAdd(&s_cnt, 1);
+                cand[p] = ((unsigned long long)key << 32) | (0xffffffffu - (uint32_t)i);
+            }
+        }
+        // equal keys: the lowest ids first
+        int base = 0;
+        for (int c0 = 0; c0 < V && base < need_eq; c0 += blockDim.x) {
+            const int i = c0 + tid;
+            const int flag = (i < V && float_key(row[i]) == kth) ? 1 : 0;
+            int total;
+            const int incl = block_scan_inclusive_int(flag, iscratch, &total);
+            const int rank = base + incl - flag;
+            if (flag && rank < need_eq) cand[n_gt + rank] = ((unsigned long long)kth << 32) | (0xffffffffu - (uint32_t)i);
+            base += total;
+            __syncthreads();
+        }
+        for (int i = k + tid; i < SAMPLE_MAX_K; i += blockDim.x) cand[i] = 0ull;
+        __syncthreads();
+        // ---- bitonic sort, descending
+        for (int size = 2; size <= SAMPLE_MAX_K; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                const int j = tid ^ stride;
+                if (j > tid) {
+                    const unsigned long long a = cand[tid], b = cand[j];
+                    const bool desc = (tid & size) == 0;
+                    if ((a < b) == desc) { cand[tid] = b; cand[j] = a; }
+                }
+                __syncthreads();
+            }
+        }
+        if (tid == 0) {
+            float mx = -INFINITY;
+            for (int i = 0; i < k; ++i) {
+                const int id = (int)(0xffffffffu - (uint32_t)(cand[i] & 0xffffffffu));
+                float s = key_float((uint32_t)(cand[i] >> 32));
+                for (int j = 0; j < nrec; ++j)
+                    if (s_recent[j] == id) { s = s / pen; break; }
+                // keep the penalised score in the upper half for the second walk
+                cand[i] = ((unsigned long long)__float_as_uint(s) << 32) | (uint32_t)id;
+                mx = fmaxf(mx, s);
+            }
+            float sum = 0.f;
+            for (int i = 0; i < k; ++i) sum += expf((__uint_as_float((uint32_t)(cand[i] >> 32)) - mx) / temp);
+            int pick = (int)(cand[0] & 0xffffffffu);
+            if (sum != 0.f) {
+                const float rr = u[r] * sum;
+                float acc = 0.f;
+                pick = (int)(cand[k - 1] & 0xffffffffu);
+                for (int i = 0; i < k; ++i) {
+                    acc += expf((__uint_as_float((uint32_t)(cand[i] >> 32)) - mx) / temp);
+                    if (rr <= acc) { pick = (int)(cand[i] & 0xffffffffu); break; }
+                }
+            }
+            out[r] = pick;
+        }
+        return;
+    }
+
+    // ---- whole row, in the order of the ids
+    auto score = [&](int i) -> float {
+        float s = row[i];
+        if (!isfinite(s)) s = -INFINITY;
+        for (int j = 0; j < nrec; ++j)
+            if (s_recent[j] == i) { s = s / pen; break; }
+        return s;
+    };
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += blockDim.x) mx = fmaxf(mx, score(i));
+    mx = block_max(mx, fscratch);
+    __syncthreads();
+    float acc = 0.f;
+    for (int c0 = 0; c0 < V; c0 += blockDim.x) {
+        const int i = c0 + tid;
+        const float w = i < V ? expf((score(i) - mx) / temp) : 0.f;
+        float total;
+        block_scan_inclusive(w, fscratch, &total);
+        acc += total;
+        __syncthreads();
+    }
+    if (tid == 0) s_pick = 0x7fffffff;
+    __syncthreads();
+    if (acc == 0.f) {
+        if (tid == 0) out[r] = 0;
+        return;
+    }
+    const float rr = u[r] * acc;
+    float run = 0.f;
+    for (int c0 = 0; c0 < V; c0 += blockDim.x) {
+        const int i = c0 + tid;
+        const float w = i < V ? expf((score(i) - mx) / temp) : 0.f;
+        float total;
+        const float incl = block_scan_inclusive(w, fscratch, &total);
+        if (i < V && rr <= run + incl) atomicMin(&s_pick, i);
+        run += total;
+        __syncthreads();
+        if (s_pick != 0x7fffffff) break;
+    }
+    __syncthreads();
+    if (tid == 0) out[r] = s_pick != 0x7fffffff ? s_pick : V - 1;
+}
+
+// logits [R, V] float32; temperature, u, penalty [R] float32; top_k [R] int32
+// (0 = whole row, at most 1024); recent [R, W] int32 padded with -1 (W <= 256) or null.
+CELLM_API int cellm_sample(int* out, const float* logits, int R, int V, const float* temperature,
+                           const int* top_k, const float* u, const float* penalty, const int* recent,
+                           int W, int max_top_k, cudaStream_t stream) {
+    if (R <= 0) return CELLM_OK;
+    if (max_top_k > SAMPLE_MAX_K || W > 256 || W < 0) return CELLM_ERR_SIZE;
+    sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(out, logits, V, temperature, top_k, u, penalty, recent, W);
+    CELLM_LAUNCH_CHECK();
+    return CELLM_OK;
+}

@@ -1,0 +1,106 @@
+"""Python face of the native scheduler (csrc/runtime/scheduler.cc)."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+from ..cache.manager import CacheManager
+from ..cache.native import checked, int_array, last_error, lib
+
+
+class SchedulerError(RuntimeError):
+    pass
+
+
+@dataclass
+class PlannedEntry:
+    request_id: int
+    start: int
+    count: int
+    wants_logits: bool
+
+
+@dataclass
+class StepPlan:
+    entries: list[PlannedEntry]
+    preempted: list[int]
+    admitted: list[tuple[int, int]]      # (request, state slot)
+
+
+STATES = ("waiting", "prefill", "decoding", "finished")
+
+
+class Scheduler:
+    """Admits requests, cuts prompts into portions under a token budget, lets all
+    decoding requests take one token per step, finishes and frees. When pages
+    run out the most recently admitted running request is preempted and later
+    recomputed from its prompt and the tokens generated so far."""
+
+    def __init__(self, cache: CacheManager, max_batch_tokens: int, prefill_chunk: int, max_positions: int):
+        self.cache = cache
+        self._h = lib().cellm_sched_create(cache.handle, int(max_batch_tokens), int(prefill_chunk), int(max_positions))
+        if not self._h:
+            raise SchedulerError(last_error())
+        self._cap = max(int(max_batch_tokens), cache.num_slots) + 8
+        self._ids = (ctypes.c_longlong * self._cap)()
+        self._a = (ctypes.c_int * self._cap)()
+        self._b = (ctypes.c_int * self._cap)()
+        self._c = (ctypes.c_int * self._cap)()
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().cellm_sched_destroy(self._h)
+            self._h = None
+
+    def add_request(self, request_id: int, tokens, max_new: int) -> None:
+        checked(lib().cellm_sched_add(self._h, int(request_id), int_array(list(tokens)), len(tokens), int(max_new)),
+                SchedulerError)
+
+    def schedule(self) -> StepPlan:
+        l = lib()
+        checked(l.cellm_sched_schedule(self._h), SchedulerError)
+        n = checked(l.cellm_sched_plan_entries(self._ids, self._a, self._b, self._c, self._cap), SchedulerError)
+        entries = [PlannedEntry(self._ids[i], self._a[i], self._b[i], bool(self._c[i])) for i in range(n)]
+        n = checked(l.cellm_sched_plan_preempted(self._ids, self._cap), SchedulerError)
+        preempted = [self._ids[i] for i in range(n)]
+        n = checked(l.cellm_sched_plan_admitted(self._ids, self._a, self._cap), SchedulerError)
+        admitted = [(self._ids[i], self._a[i]) for i in range(n)]
+        return StepPlan(entries, preempted, admitted)
+
+    def step_done(self) -> None:
+        """Marks the tokens of the last planned step as cached."""
+        checked(lib().cellm_sched_step_done(self._h), SchedulerError)
+
+    def append_token(self, request_id: int, token: int, stop: bool = False) -> bool:
+        """Adds a sampled token; True when the request is finished (and freed)."""
+        return bool(checked(lib().cellm_sched_append(self._h, int(request_id), int(token), 1 if stop else 0),
+                            SchedulerError))
+
+    def cancel(self, request_id: int) -> None:
+        checked(lib().cellm_sched_cancel(self._h, int(request_id)), SchedulerError)
+
+    def forget(self, request_id: int) -> None:
+        checked(lib().cellm_sched_forget(self._h, int(request_id)), SchedulerError)
+
+    def has(self, request_id: int) -> bool:
+        return bool(lib().cellm_sched_has(self._h, int(request_id)))
+
+    def info(self, request_id: int) -> dict:
+        buf = (ctypes.c_int * 6)()
+        checked(lib().cellm_sched_info(self._h, int(request_id), buf), SchedulerError)
+        return {"state": STATES[buf[0]], "prompt_len": buf[1], "num_tokens": buf[2], "computed": buf[3],
+                "generated": buf[4], "preemptions": buf[5],
+                "finish_reason": lib().cellm_sched_finish_reason(self._h, int(request_id)).decode()}
+
+    def tokens(self, request_id: int, start: int = 0, count: int | None = None) -> list[int]:
+        total = self.info(request_id)["num_tokens"]
+        buf = (ctypes.c_int * max(total - start, 1))()
+        n = checked(lib().cellm_sched_tokens(self._h, int(request_id), int(start), buf, len(buf)), SchedulerError)
+        out = list(buf[:n])
+        return out if count is None else out[:count]
+
+    def stats(self) -> dict:
+        buf = (ctypes.c_longlong * 6)()
+        lib().cellm_sched_stats(self._h, buf)
+        return {"waiting": buf[0], "running": buf[1], "steps": buf[2], "tokens": buf[3],
+                "preemptions": buf[4], "idle": bool(buf[5])}

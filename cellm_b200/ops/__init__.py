@@ -1,9 +1,9 @@
 """Python entry points of the hand-written kernels. Each function checks its
 arguments, allocates its output with torch and launches on the current stream."""
 from .basic import (embed, add_rmsnorm, residual_add, swiglu, short_conv, qk_norm_rope,
-                    attention_plain, argmax)
+                    attention_plain, argmax, sample)
 from .gemm import gemm, gemm_plain
 from .attention import attention
 
 __all__ = ["embed", "add_rmsnorm", "residual_add", "swiglu", "short_conv", "qk_norm_rope",
-           "attention_plain", "argmax", "gemm", "gemm_plain", "attention"]
+           "attention_plain", "argmax", "sample", "gemm", "gemm_plain", "attention"]

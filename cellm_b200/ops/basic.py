@@ -128,3 +128,21 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     check(fn(_LIB, "cellm_argmax")(ptr(out), ptr(logits), R, V, stream_of(logits)), "argmax")
     return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, u: torch.Tensor,
+           penalty: Optional[torch.Tensor] = None, recent: Optional[torch.Tensor] = None,
+           max_top_k: int = 0) -> torch.Tensor:
+    """One token per row of float32 logits [R, V]: arg-max where temperature <= 0,
+    else a draw from softmax(logits / temperature) over the top_k logits (0: all),
+    decided by the uniform number u[r]. recent [R, W] int32 (-1 padded) and
+    penalty [R] apply the repetition penalty. Returns int32 [R]."""
+    require_cuda(logits, temperature, top_k, u, penalty, recent)
+    if logits.dtype != torch.float32 or logits.dim() != 2:
+        raise ValueError("sample: logits must be float32 [R, V]")
+    R, V = logits.shape
+    W = recent.shape[1] if recent is not None else 0
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    check(fn(_LIB, "cellm_sample")(ptr(out), ptr(logits), R, V, ptr(temperature), ptr(top_k), ptr(u),
+                                   ptr(penalty), ptr(recent), W, int(max_top_k), stream_of(logits)), "sample")
+    return out
