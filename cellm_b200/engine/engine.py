@@ -29,9 +29,11 @@ class RequestOutput:
 
 
 class Engine:
-    def __init__(self, model: str, config: Optional[EngineConfig] = None, **overrides):
-        """`model`: a folder with config.json and model.safetensors. Keyword
-        arguments override fields of EngineConfig (dtype, total_blocks, ...)."""
+    def __init__(self, model, config: Optional[EngineConfig] = None, **overrides):
+        """`model`: a folder with config.json and model.safetensors, or the
+        (config, plan, model) triple that `cellm_b200.models.load_model` returned
+        (several engines may share one loaded model). Keyword arguments override
+        fields of EngineConfig (dtype, total_blocks, ...)."""
         self.config = config or EngineConfig()
         for k, v in overrides.items():
             if not hasattr(self.config, k):
@@ -39,7 +41,11 @@ class Engine:
             setattr(self.config, k, v)
         self.config.__post_init__()
         c = self.config
-        self.model_config, self.plan, self.model = load_model(model, c.dtype, c.device)
+        if isinstance(model, (str, bytes)) or hasattr(model, "__fspath__"):
+            model = load_model(model, c.dtype, c.device)
+        self.model_config, self.plan, self.model = model
+        if self.model.dtype != c.dtype:
+            raise ValueError(f"the loaded model computes in {self.model.dtype}, the engine was asked for {c.dtype}")
         self.cache = CacheManager(self.model.cache_needs(), [e.cache_of for e in self.plan.order],
                                   c.tokens_per_block, c.total_blocks, c.max_num_seqs, c.dtype, c.device)
         self.runner = StepRunner(self.model, self.cache)

@@ -35,6 +35,11 @@ _SIGNATURES = {
 
 _funcs: dict[str, ctypes._CFuncPtr] = {}
 
+# Kernels launched through these bindings since the process began: every entry
+# point launches one kernel unless listed here.
+LAUNCHES = [0]
+_KERNELS_PER_CALL = {"cellm_short_conv": 2}
+
 
 def register_signatures(library: str, signatures: dict) -> None:
     _SIGNATURES.setdefault(library, {}).update(signatures)
@@ -53,6 +58,7 @@ def fn(library: str, name: str):
 
 def check(code: int, name: str) -> None:
     if code == 0:
+        LAUNCHES[0] += _KERNELS_PER_CALL.get("cellm_" + name, 1)
         return
     if code < 0:
         raise ValueError(f"{name}: refused: {_ERRORS.get(code, code)}")

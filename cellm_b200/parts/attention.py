@@ -45,7 +45,7 @@ class AttentionMixer(Mixer):
         self.dtype = dtype
         dev = weights["q_proj"].device
         self.qkv = Linear(stack_rows(weights["q_proj"], weights["k_proj"], weights["v_proj"]), dtype)
-        self.q_only = Linear(weights["q_proj"], dtype)
+        self.q_only = Linear(self.qkv.weight[:self.nh * self.hd], dtype)   # rows of the stacked matrix, no copy
         self.out_proj = Linear(weights["out_proj"], dtype)
         qk: PartSpec | None = params.get("qk_norm")
         self.q_norm_w = self.k_norm_w = None

@@ -1,0 +1,145 @@
+"""Generation through the Python entry point against the plain implementation:
+greedy, temperature with a seed, long decoding, and a pool so small that
+requests are preempted and recomputed."""
+import numpy as np
+import pytest
+
+import plain_lfm2 as plain
+from tiny_configs import CONFIGS, make_model
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    d = tmp_path_factory.mktemp("models")
+    return {name: make_model(d, name) for name in CONFIGS}
+
+
+def _prompts(vocab, lengths, seed=1):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, vocab, n).tolist() for n in lengths]
+
+
+def _margin_ok(cfg, w, prompt, out, k=2e-3):
+    """True if every greedy choice along `out` has a clear margin in the plain
+    model, so that 32-bit rounding cannot flip it."""
+    toks = list(prompt)
+    for t in out:
+        lg = plain.forward(cfg, w, toks)[-1]
+        top = lg.topk(2).values
+        if float(top[0] - top[1]) < k * (1 + float(lg.abs().max())):
+            return False
+        toks.append(t)
+    return True
+
+
+def test_greedy_generation_tiny_a(folders):
+    """BASELINE workload of Tiny A: prompts of 1, 7, 33 and 64 tokens, 16 greedy tokens each, page 8."""
+    from cellm_b200 import Engine, SamplingParams
+    cfg, w = plain.load_folder(folders["tiny_a"])
+    prompts = _prompts(cfg["vocab_size"], [1, 7, 33, 64])
+    eng = Engine(folders["tiny_a"], dtype="float32", tokens_per_block=8, total_blocks=64, max_num_seqs=4,
+                 max_batch_tokens=48, prefill_chunk=24)
+    outs = eng.generate(prompts, SamplingParams.greedy(16, stop_eos=False))
+    for p, o in zip(prompts, outs):
+        ref = plain.generate(cfg, w, p, 16)
+        if o != ref:
+            i = next(j for j in range(16) if o[j] != ref[j])
+            assert not _margin_ok(cfg, w, p, ref[:i + 1]), f"token {i} differs: {o} vs {ref}"
+        assert len(o) == 16
+    s = eng.stats()
+    assert s["idle"] and s["free_pages"] == s["total_pages"] and s["free_slots"] == 4
+
+
+def test_temperature_generation_tiny_b(folders):
+    """BASELINE workload of Tiny B: prompts 5/50/200 in portions of 13 mixed with
+    decode steps, 24 tokens at temperature 0.8 with a fixed seed, page 16."""
+    from cellm_b200 import Engine, SamplingParams
+    from cellm_b200.sampling import session_seed
+    cfg, w = plain.load_folder(folders["tiny_b"])
+    prompts = _prompts(cfg["vocab_size"], [5, 50, 200], seed=2)
+    eng = Engine(folders["tiny_b"], dtype="float32", tokens_per_block=16, total_blocks=40, max_num_seqs=3,
+                 max_batch_tokens=32, prefill_chunk=13)
+    params = SamplingParams(temperature=0.8, top_k=40, seed=1234, repeat_penalty=1.05, repeat_window=64,
+                            max_new_tokens=24, stop_eos=False)
+    outs = eng.generate(prompts, params)
+    same = 0
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        ref = plain.generate(cfg, w, p, 24, temperature=0.8, top_k=40, seed=session_seed(i, 1234),
+                             repeat_penalty=1.05, repeat_window=64)
+        assert len(o) == 24
+        same += int(o == ref)
+    # a draw that lands within rounding of a boundary of the distribution may differ; most must not
+    assert same >= 2
+
+
+def test_bfloat16_greedy_runs_and_frees(folders):
+    from cellm_b200 import Engine, SamplingParams
+    cfg, w = plain.load_folder(folders["tiny_b"])
+    prompts = _prompts(cfg["vocab_size"], [9, 40, 3, 77, 120, 16], seed=3)
+    eng = Engine(folders["tiny_b"], dtype="bfloat16", tokens_per_block=16, total_blocks=64, max_num_seqs=4,
+                 max_batch_tokens=64, prefill_chunk=32)
+    outs = eng.generate(prompts, SamplingParams.greedy(12, stop_eos=False))
+    agree = 0
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12 and all(0 <= t < cfg["vocab_size"] for t in o)
+        agree += int(o[0] == plain.generate(cfg, w, p, 1)[0])
+    assert agree >= 4
+    s = eng.stats()
+    assert s["idle"] and s["free_pages"] == s["total_pages"]
+
+
+def test_preemption_gives_the_same_tokens(folders):
+    """With too few pages for all requests at once, running requests are
+    preempted and recomputed; the tokens are the same as with a large pool."""
+    from cellm_b200 import Engine, SamplingParams
+    cfg, _ = plain.load_folder(folders["tiny_a"])
+    prompts = _prompts(cfg["vocab_size"], [30, 30, 30, 30], seed=4)
+    params = SamplingParams.greedy(40, stop_eos=False)
+    big = Engine(folders["tiny_a"], dtype="float32", tokens_per_block=8, total_blocks=64, max_num_seqs=4)
+    ref = big.generate(prompts, params)
+    small = Engine(folders["tiny_a"], dtype="float32", tokens_per_block=8, total_blocks=20, max_num_seqs=4)
+    out = small.generate(prompts, params)
+    assert small.stats()["preemptions"] > 0
+    assert out == ref
+    assert small.stats()["free_pages"] == small.stats()["total_pages"]
+
+
+def test_long_decoding_matches_plain(folders):
+    """One short prompt decoded far beyond several pages, 32-bit, logits of the
+    sampled path compared through greedy agreement with the plain model."""
+    from cellm_b200 import Engine, SamplingParams
+    cfg, w = plain.load_folder(folders["tiny_a"])
+    prompt = _prompts(cfg["vocab_size"], [3], seed=6)[0]
+    eng = Engine(folders["tiny_a"], dtype="float32", tokens_per_block=8, total_blocks=32, max_num_seqs=1)
+    out = eng.generate([prompt], SamplingParams.greedy(200, stop_eos=False))[0]
+    assert len(out) == 200
+    toks = prompt + out
+    lg = plain.forward(cfg, w, toks[:-1])
+    ref_next = lg.argmax(dim=-1).tolist()[len(prompt) - 1:]
+    mism = [i for i in range(200) if out[i] != ref_next[i]]
+    for i in mism:   # only allowed where the plain model's top two are within rounding
+        top = lg[len(prompt) - 1 + i].topk(2).values
+        assert float(top[0] - top[1]) < 2e-3 * (1 + float(lg.abs().max()))
+
+
+def test_stop_at_eos_and_request_too_large(folders):
+    from cellm_b200 import Engine, SamplingParams
+    from cellm_b200.engine import SchedulerError
+    cfg, w = plain.load_folder(folders["tiny_a"])
+    eng = Engine(folders["tiny_a"], dtype="float32", tokens_per_block=8, total_blocks=8, max_num_seqs=2)
+    with pytest.raises(SchedulerError):
+        eng.add_request(list(range(60)), SamplingParams.greedy(40))      # 100 tokens > 8 pages of 8
+    with pytest.raises(SchedulerError):
+        eng.add_request(list(range(200)), SamplingParams.greedy(100))    # beyond max_position_embeddings
+    with pytest.raises(ValueError):
+        eng.add_request([5, 100000], SamplingParams.greedy(4))
+    # find a prompt whose greedy continuation meets the eos token early
+    eos = cfg["eos_token_id"]
+    for seed in range(200):
+        p = _prompts(cfg["vocab_size"], [4], seed=100 + seed)[0]
+        out = eng.generate([p], SamplingParams.greedy(24, stop_eos=True))[0]
+        if eos in out:
+            assert out.index(eos) == len(out) - 1
+            break

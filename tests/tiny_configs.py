@@ -29,8 +29,9 @@ CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B}
 SEEDS = {"tiny_a": 11, "tiny_b": 23}
 
 # Random weights of std 0.02 give logits so flat that a wrong key or a stale
-# page barely moves them; tests use larger linears so that faults show.
-TEST_INIT = InitSpec(linear_std=0.08, embedding_std=0.5, conv_tap_std=0.3, bias_std=0.05, norm_jitter=0.1)
+# page barely moves them; tests use larger linears so that faults show, and a
+# small embedding so that the tied output does not just repeat the last token.
+TEST_INIT = InitSpec(linear_std=0.15, embedding_std=0.1, conv_tap_std=0.3, bias_std=0.05, norm_jitter=0.1)
 
 
 def make_model(tmpdir, name, dtype="bfloat16", init=TEST_INIT, overrides=None, seed=None):
