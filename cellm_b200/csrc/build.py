@@ -35,6 +35,7 @@ LIBRARIES: dict[str, tuple[str, list[str], list[str]]] = {
                                 "kernels/qk_norm_rope.cu", "kernels/swiglu.cu", "kernels/sample.cu",
                                 "kernels/attention_plain.cu"], []),
     "gemm_plain": ("nvcc", ["kernels/gemm_plain.cu"], []),
+    "gemm_tcgen05": ("nvcc", ["kernels/gemm_tcgen05.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -1,0 +1,435 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:
+//   C[M,N] = A[M,K] . W[N,K]^T, 32-bit accumulation in tensor memory.
+//
+// One CTA computes one 128 x BN tile of C. Three roles, one warp each or four:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads 128x64 of A and BNx64 of W
+//               (128-byte swizzle) into a ring of shared-memory stages;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) four
+//               times per stage, accumulating into BN columns of tensor memory, and
+//               releases each stage with tcgen05.commit;
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator (one row per thread),
+//               conversion, and guarded stores to C.
+// Rows and columns beyond M, N and K are zero-filled by the TMA unit, so any
+// M and N are taken; K must be a multiple of 8 (16-byte row pitch).
+//
+// Every wait on an mbarrier is bounded: after about a second without progress
+// the waiting role sets CELLM_DEV_WAIT_TIMEOUT in the error word and leaves its
+// loop; the CTA then frees its tensor memory and returns.
+//
+// Skinny products (few rows of A: decoding) run "swapped": the 128-row operand
+// is a tile of W, the narrow operand (16, 32 or 64 rows) is A, so the tensor
+// core tile is filled by weights and the stage ring holds almost only weights;
+// the epilogue then writes its tile transposed.
+//
+// With split_k > 1 (skinny products, M small) blockIdx.z selects a slice of K;
+// each slice writes its partial tile as float into a workspace
+// [split_k, M, N] and a second kernel sums the slices in a fixed order.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the barrier did not flip within WAIT_LIMIT_CYCLES.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes,
+// stored with the 128-byte swizzle: start address, leading offset 1 (unused with
+// a swizzle), 1024 bytes from one group of eight rows to the next, descriptor
+// version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor: D = float (1 at bit 4), A = B = bfloat16 (1 at bits 7 and 10),
+// both K-major (bits 15, 16 clear), N / 8 at bit 17, M / 16 at bit 24.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN, int STAGES>
+struct alignas(1024) GemmSmem {
+    uint8_t a[STAGES][BM * BK * 2];
+    uint8_t b[STAGES][BN * BK * 2];
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <typename TO> __device__ __forceinline__ void store_row(TO* dst, const uint32_t* r, int valid, bool aligned);
+template <> __device__ __forceinline__ void store_row<float>(float* dst, const uint32_t* r, int valid, bool aligned) {
+    if (valid >= 32 && aligned) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < valid) dst[i] = __uint_as_float(r[i]);
+    }
+}
+template <> __device__ __forceinline__ void store_row<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t* r, int valid, bool aligned) {
+    if (valid >= 32 && aligned) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 2 * j]), __uint_as_float(r[8 * i + 2 * j + 1]));
+                p[j] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(p[0], p[1], p[2], p[3]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < valid) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+    }
+}
+
+// The 128-row operand ("rows") and the BN-row operand ("cols") of a tile:
+//   SWAP = false: rows = A (tokens),  cols = W;  grid (ceil(N/BN),  ceil(M/128), split_k); tile element (p, q) -> C[p][q]
+//   SWAP = true:  rows = W,           cols = A;  grid (ceil(N/128), ceil(M/BN),  split_k); tile element (p, q) -> C[q][p]
+// C is the output [M, N] (row pitch ldc) when split_k == 1, else the float
+// workspace [split_k, M, N] (row pitch N).
+template <int BN, int STAGES, bool SWAP, typename TO>
+__global__ void __launch_bounds__(192)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
+                    TO* __restrict__ C, int M, int N, int K, long long ldc, int kblocks_per_split,
+                    int* __restrict__ err) {
+    extern __shared__ uint8_t smem_raw[];
+    auto& sm = *reinterpret_cast<GemmSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p0 = (SWAP ? blockIdx.x : blockIdx.y) * BM;    // first row of the 128-row operand
+    const int q0 = (SWAP ? blockIdx.y : blockIdx.x) * BN;    // first row of the narrow operand
+    const int P = SWAP ? N : M, Q = SWAP ? M : N;
+    const int kblocks_total = (K + BK - 1) / BK;
+    const int kb0 = blockIdx.z * kblocks_per_split;
+    const int kb1 = min(kb0 + kblocks_per_split, kblocks_total);
+    const int nkb = kb1 - kb0;           // > 0 by construction of the grid
+    if (gridDim.z > 1) C += (size_t)blockIdx.z * (size_t)M * (size_t)ldc;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        mbar_init(&sm.acc_full, 1);
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_rows) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_cols) : "memory");
+    }
+    if (warp == 1) tmem_alloc(&sm.tmem_base, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    volatile int* abort_flag = &sm.abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+                if (!mbar_wait(&sm.empty[s], phase ^ 1u, abort_flag)) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); break; }
+                mbar_expect_tx(&sm.full[s], (BM + BN) * BK * 2);
+                tma_load_2d(sm.a[s], &map_rows, (kb0 + i) * BK, p0, &sm.full[s]);
+                tma_load_2d(sm.b[s], &map_cols, (kb0 + i) * BK, q0, &sm.full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+                if (!mbar_wait(&sm.full[s], phase, abort_flag)) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); ok = false; break; }
+                tc_fence_after();
+                const uint64_t da = umma_desc(smem_u32(sm.a[s])), db = umma_desc(smem_u32(sm.b[s]));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma_bf16(tmem, da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16), idesc,
+                              (i | k) != 0 ? 1u : 0u);
+                umma_commit(&sm.empty[s]);
+            }
+            if (ok) umma_commit(&sm.acc_full);
+        }
+    } else {
+        const bool ok = mbar_wait(&sm.acc_full, 0, abort_flag);
+        if (!ok && lane == 0) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); }
+        tc_fence_after();
+        if (ok) {
+            const int qtr = warp & 3;                     // the quarter of the lanes this warp may read
+            const int p = p0 + qtr * 32 + lane;
+            const uint32_t lane_addr = tmem + ((uint32_t)(qtr * 32) << 16);
+            if constexpr (!SWAP) {
+                const bool aligned = ((reinterpret_cast<uintptr_t>(C) | (uintptr_t)(ldc * sizeof(TO))) & 15) == 0 &&
+                                     ((q0 * sizeof(TO)) & 15) == 0;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(lane_addr + (uint32_t)(c * 32), r);
+                    const int q = q0 + c * 32;
+                    if (p < P && q < Q) store_row<TO>(C + (size_t)p * ldc + q, r, Q - q, aligned);
+                }
+            } else {
+                constexpr int W = BN < 32 ? 16 : 32;
+#pragma unroll 1
+                for (int c = 0; c < BN / W; ++c) {
+                    uint32_t r[W];
+                    if constexpr (W == 16) tmem_ld16(lane_addr + (uint32_t)(c * W), r);
+                    else tmem_ld32(lane_addr + (uint32_t)(c * W), r);
+                    if (p < P) {
+#pragma unroll
+                        for (int j = 0; j < W; ++j) {
+                            const int q = q0 + c * W + j;
+                            if (q < Q) C[(size_t)q * ldc + p] = from_float<TO>(__uint_as_float(r[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// Sum of the split-K slices in the order of the slices, then the conversion.
+template <typename TO>
+__global__ void splitk_reduce_kernel(TO* __restrict__ C, const float* __restrict__ ws, int M, int N, long long ldc,
+                                     int splits) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)M * N;
+    if (i >= total) return;
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += ws[(size_t)s * total + i];
+    const size_t m = i / N, n = i - m * N;
+    C[m * ldc + n] = from_float<TO>(acc);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* base; uint64_t rows, cols, pitch; uint32_t box_rows;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.base);
+        for (uint64_t v : {k.rows, k.cols, k.pitch, (uint64_t)k.box_rows}) h = h * 1000003u ^ std::hash<uint64_t>()(v);
+        return h;
+    }
+};
+
+// A tensor map of a row-major bf16 matrix [rows, cols] with `pitch` bytes between
+// rows, boxes of box_rows x 64, 128-byte swizzle, zero fill outside.
+bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch, uint32_t box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    const MapKey key{base, rows, cols, pitch, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+    return true;
+}
+
+template <int BN, int STAGES, bool SWAP, typename TO>
+int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, int M, int N, int K, long long ldc,
+           int split_k, int kblocks_per_split, int* err, cudaStream_t stream) {
+    const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, SWAP, TO>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid = SWAP ? dim3((unsigned)((N + BM - 1) / BM), (unsigned)((M + BN - 1) / BN), (unsigned)split_k)
+                     : dim3((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)split_k);
+    gemm_tcgen05_kernel<BN, STAGES, SWAP, TO><<<grid, 192, smem, stream>>>(m_rows, m_cols, C, M, N, K, ldc,
+                                                                          kblocks_per_split, err);
+    CELLM_LAUNCH_CHECK();
+    return CELLM_OK;
+}
+
+}  // namespace
+
+// A: [M, K] bf16 (row pitch lda elements), W: [N, K] bf16 (pitch ldw), C: [M, N] of
+// out_dtype (pitch ldc). bn > 0: plain tiles of 128 rows of A by bn (64, 128, 256)
+// rows of W. bn < 0: swapped tiles of 128 rows of W by -bn (16, 32, 64) rows of A.
+// split_k >= 1; with split_k > 1 `workspace` holds split_k * M * N floats.
+CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
+                                 long long ldw, long long ldc, int out_dtype, int bn, int split_k,
+                                 float* workspace, int* err, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return CELLM_OK;
+    if (K <= 0 || (K & 7)) return CELLM_ERR_SIZE;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((lda * 2) & 15) || ((ldw * 2) & 15)) return CELLM_ERR_ALIGN;
+    if (out_dtype != CELLM_F32 && out_dtype != CELLM_BF16) return CELLM_ERR_DTYPE;
+    const bool swap = bn < 0;
+    const int narrow = swap ? -bn : bn;
+    if (swap ? (narrow != 16 && narrow != 32 && narrow != 64) : (narrow != 64 && narrow != 128 && narrow != 256))
+        return CELLM_ERR_SIZE;
+    const int kblocks = (K + BK - 1) / BK;
+    if (split_k < 1) split_k = 1;
+    if (split_k > kblocks) split_k = kblocks;
+    const int per = (kblocks + split_k - 1) / split_k;
+    split_k = (kblocks + per - 1) / per;        // no empty slice
+    if (split_k > 1 && workspace == nullptr) return CELLM_ERR_ARG;
+    CUtensorMap map_a, map_w;
+    if (!tensor_map(&map_a, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, swap ? (uint32_t)narrow : (uint32_t)BM)) return CELLM_ERR_ARG;
+    if (!tensor_map(&map_w, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, swap ? (uint32_t)BM : (uint32_t)narrow)) return CELLM_ERR_ARG;
+    const CUtensorMap& m_rows = swap ? map_w : map_a;
+    const CUtensorMap& m_cols = swap ? map_a : map_w;
+    int rc;
+#define GO(BN_, ST_, SW_)                                                                                          \
+    do {                                                                                                           \
+        if (split_k > 1) rc = launch<BN_, ST_, SW_, float>(m_rows, m_cols, workspace, M, N, K, (long long)N, split_k, per, err, stream); \
+        else if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, float>(m_rows, m_cols, (float*)C, M, N, K, ldc, 1, per, err, stream); \
+        else rc = launch<BN_, ST_, SW_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, M, N, K, ldc, 1, per, err, stream); \
+    } while (0)
+    if (swap) {
+        if (narrow == 16) GO(16, 5, true);
+        else if (narrow == 32) GO(32, 5, true);
+        else GO(64, 4, true);
+    } else {
+        if (narrow == 64) GO(64, 8, false);
+        else if (narrow == 128) GO(128, 6, false);
+        else GO(256, 4, false);
+    }
+#undef GO
+    if (rc != CELLM_OK) return rc;
+    if (split_k > 1) {
+        const size_t total = (size_t)M * N;
+        const unsigned blocks = (unsigned)((total + 255) / 256);
+        if (out_dtype == CELLM_F32)
+            splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>((float*)C, workspace, M, N, ldc, split_k);
+        else
+            splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)C, workspace, M, N, ldc, split_k);
+        CELLM_LAUNCH_CHECK();
+    }
+    return CELLM_OK;
+}

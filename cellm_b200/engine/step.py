@@ -41,7 +41,8 @@ class StepRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager):
         self.model, self.cache = model, cache
         self.device = model.device
-        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        from ..ops.gemm_bf16 import error_word
+        self.err = error_word(self.device)      # one error word for every kernel on this device
         self._pinned = [None, None]
         self._events = [None, None]
         self._flip = 0

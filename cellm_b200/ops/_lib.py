@@ -31,6 +31,9 @@ _SIGNATURES = {
     "gemm_plain": {
         "cellm_gemm_plain": [P, P, P, I, I, I, L, L, L, I, I, P],
     },
+    "gemm_tcgen05": {
+        "cellm_gemm_tcgen05": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, P],
+    },
 }
 
 _funcs: dict[str, ctypes._CFuncPtr] = {}
