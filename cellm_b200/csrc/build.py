@@ -36,6 +36,7 @@ LIBRARIES: dict[str, tuple[str, list[str], list[str]]] = {
                                 "kernels/attention_plain.cu"], []),
     "gemm_plain": ("nvcc", ["kernels/gemm_plain.cu"], []),
     "gemm_tcgen05": ("nvcc", ["kernels/gemm_tcgen05.cu"], []),
+    "attention_flash": ("nvcc", ["kernels/attention_flash.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -1,0 +1,340 @@
+// Flash-style attention over the paged cache for bfloat16, on the tensor cores
+// (mma.sync m16n8k16), for prompt portions and decoded tokens alike.
+//
+// All query heads that share a key/value head are packed into one tile: for
+// key/value head g of request b the tile's rows are (token, head in group)
+// pairs, row r = token * G + head (G = heads per key/value head). A CTA takes
+// 16 rows per warp; keys are walked in blocks of 64 through the request's
+// block table, with K and V blocks brought in by cp.async, double-buffered.
+// Scores q.k * scale, causal mask (key <= the token's position), optional
+// window, online softmax in 32-bit with the running maximum taken off
+// (crates/cellm-cache/src/kvcache.rs:753-787, :1206-1227 is the reference's
+// single-token loop). Probabilities are rounded to bfloat16 for the P.V
+// product; sums and outputs stay 32-bit until the final store.
+//
+// A token with a long context can be split over gridDim.z CTAs, each taking a
+// run of key blocks; the pieces (unnormalised output, maximum, sum) go to a
+// workspace and a second kernel merges them in the order of the pieces.
+//
+// Cache layout of one layer: [page][kv_head][slot in page][head_dim].
+#include <mma.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int FA_BN = 64;   // keys per block
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold HD
+// bfloat16, with the chunks of a row permuted so that eight rows read by one
+// ldmatrix fall into different banks.
+template <int HD>
+__device__ __forceinline__ int tile_offset(int row, int chunk) {
+    constexpr int CH = HD / 8;
+    int sw;
+    if constexpr (CH >= 8) sw = chunk ^ (row & 7);
+    else if constexpr (CH == 4) sw = chunk ^ ((row >> 1) & 3);
+    else sw = chunk ^ ((row >> 2) & 1);
+    return (row * CH + sw) * 16;
+}
+
+template <int HD, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
+attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                       const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                       const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ cu_seqlens,
+                       const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride,
+                       int B, int T, int num_pages, int page_size, int nh, int nkv, float scale_log2e, int window,
+                       int* __restrict__ err) {
+    constexpr int BM = 16 * NWARPS, BN = FA_BN, CH = HD / 8, NT = HD / 8, THREADS = NWARPS * 32;
+    extern __shared__ __align__(128) uint8_t fa_smem[];
+    uint8_t* q_s = fa_smem;                              // [BM][HD]
+    uint8_t* k_s = q_s + BM * HD * 2;                    // [2][BN][HD]
+    uint8_t* v_s = k_s + 2 * BN * HD * 2;                // [2][BN][HD]
+    const int G = nh / nkv;
+    const int kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // which request this tile belongs to
+    int b = 0, base = 0;
+    for (; b < B; ++b) {
+        const int nt = ((cu_seqlens[b + 1] - cu_seqlens[b]) * G + BM - 1) / BM;
+        if ((int)blockIdx.x < base + nt) break;
+        base += nt;
+    }
+    if (b == B) return;
+    const int t_base = cu_seqlens[b], q_len = cu_seqlens[b + 1] - t_base, rows = q_len * G;
+    const int ctx = ctx_lens[b];
+    const int r0 = ((int)blockIdx.x - base) * BM;
+    const int t_lo = r0 / G, t_hi = min(r0 + BM - 1, rows - 1) / G;
+    const int key_end = ctx + t_hi + 1;
+    const int key_begin = window > 0 ? max(0, ctx + t_lo - window + 1) : 0;
+    const int kb_begin = key_begin / BN, kb_end = (key_end + BN - 1) / BN;
+    const int per = (kb_end - kb_begin + nsplit - 1) / nsplit;
+    const int my_begin = kb_begin + split * per, my_end = min(kb_end, my_begin + per);
+    const int* bt = block_table + (size_t)b * bt_stride;
+    const size_t page_elems = (size_t)nkv * page_size * HD;
+
+    // Q tile
+    for (int i = threadIdx.x; i < BM * CH; i += THREADS) {
+        const int row = i / CH, chunk = i % CH, r = r0 + row;
+        const bool ok = r < rows;
+        const __nv_bfloat16* src = q + (size_t)(t_base + (ok ? r / G : 0)) * nh * HD + (size_t)(kvh * G + (ok ? r % G : 0)) * HD + chunk * 8;
+        cp_async16(q_s + tile_offset<HD>(row, chunk), src, ok ? 16 : 0);
+    }
+    auto load_kv = [&](int kb, int stage) {
+        uint8_t* ks = k_s + stage * BN * HD * 2;
+        uint8_t* vs = v_s + stage * BN * HD * 2;
+        for (int i = threadIdx.x; i < BN * CH; i += THREADS) {
+            const int row = i / CH, chunk = i % CH, j = kb * BN + row;
+            int page = -1;
+            if (j >= key_begin && j < key_end) {
+                page = bt[j / page_size];
+                if (page < 0 || page >= num_pages) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
+            }
+            const size_t off = page >= 0 ? (size_t)page * page_elems + ((size_t)kvh * page_size + j % page_size) * HD + chunk * 8 : 0;
+            cp_async16(ks + tile_offset<HD>(row, chunk), k_pool + off, page >= 0 ? 16 : 0);
+            cp_async16(vs + tile_offset<HD>(row, chunk), v_pool + off, page >= 0 ? 16 : 0);
+        }
+    };
+    if (my_begin < my_end) load_kv(my_begin, 0);
+    cp_async_commit();
+
+    // per-thread rows: g = lane / 4 and g + 8 of this warp's 16
+    const int row_a = r0 + warp * 16 + (lane >> 2), row_b = row_a + 8;
+    const int pos_a = row_a < rows ? ctx + row_a / G : -1, pos_b = row_b < rows ? ctx + row_b / G : -1;
+    const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    uint32_t qf[HD / 16][4];
+    bool q_loaded = false;
+
+    for (int kb = my_begin, it = 0; kb < my_end; ++kb, ++it) {
+        const int stage = it & 1;
+        if (kb + 1 < my_end) load_kv(kb + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (!q_loaded) {
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks)
+                ldmatrix_x4(qf[ks], q_s + tile_offset<HD>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+            q_loaded = true;
+        }
+        const uint8_t* ks_ = k_s + stage * BN * HD * 2;
+        const uint8_t* vs_ = v_s + stage * BN * HD * 2;
+        // S = Q K^T for 64 keys
+        float s[BN / 8][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int n2 = 0; n2 < BN / 16; ++n2) {
+                uint32_t kf[4];
+                ldmatrix_x4(kf, ks_ + tile_offset<HD>(n2 * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+                mma_bf16(s[2 * n2], qf[ks], kf[0], kf[1]);
+                mma_bf16(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
+            }
+        }
+        // mask, online softmax
+        const int j0 = kb * BN + (lane & 3) * 2;
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = j0 + n * 8 + e;
+                const float va = (j <= pos_a && j >= lo_a) ? s[n][e] * scale_log2e : -INFINITY;
+                const float vb = (j <= pos_b && j >= lo_b) ? s[n][2 + e] * scale_log2e : -INFINITY;
+                s[n][e] = va;
+                s[n][2 + e] = vb;
+                mx_a = fmaxf(mx_a, va);
+                mx_b = fmaxf(mx_b, vb);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float use_a = mn_a == -INFINITY ? 0.f : mn_a, use_b = mn_b == -INFINITY ? 0.f : mn_b;
+        const float corr_a = exp2f(m_a - use_a), corr_b = exp2f(m_b - use_b);
+        m_a = mn_a;
+        m_b = mn_b;
+        float sum_a = 0.f, sum_b = 0.f;
+        uint32_t pf[BN / 16][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+            const float p0 = exp2f(s[n][0] - use_a), p1 = exp2f(s[n][1] - use_a);
+            const float p2 = exp2f(s[n][2] - use_b), p3 = exp2f(s[n][3] - use_b);
+            sum_a += p0 + p1;
+            sum_b += p2 + p3;
+            pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+            pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        l_a = l_a * corr_a + sum_a;
+        l_b = l_b * corr_b + sum_b;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { o[n][0] *= corr_a; o[n][1] *= corr_a; o[n][2] *= corr_b; o[n][3] *= corr_b; }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+            for (int n2 = 0; n2 < NT / 2; ++n2) {
+                uint32_t vf[4];
+                ldmatrix_x4_trans(vf, vs_ + tile_offset<HD>(kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), n2 * 2 + (lane >> 4)));
+                mma_bf16(o[2 * n2], pf[kk], vf[0], vf[1]);
+                mma_bf16(o[2 * n2 + 1], pf[kk], vf[2], vf[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const int col = (lane & 3) * 2;
+    if (nsplit == 1) {
+        const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+        if (row_a < rows) {
+            __nv_bfloat16* dst = out + (size_t)(t_base + row_a / G) * nh * HD + (size_t)(kvh * G + row_a % G) * HD + col;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][0] * inv_a, o[n][1] * inv_a);
+        }
+        if (row_b < rows) {
+            __nv_bfloat16* dst = out + (size_t)(t_base + row_b / G) * nh * HD + (size_t)(kvh * G + row_b % G) * HD + col;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][2] * inv_b, o[n][3] * inv_b);
+        }
+    } else {
+        const size_t n_rows = (size_t)T * nh;
+        if (row_a < rows) {
+            const size_t gr = (size_t)(t_base + row_a / G) * nh + kvh * G + row_a % G;
+            float* dst = part_o + ((size_t)split * n_rows + gr) * HD + col;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][0], o[n][1]);
+            if ((lane & 3) == 0) { part_ml[((size_t)split * n_rows + gr) * 2] = m_a; part_ml[((size_t)split * n_rows + gr) * 2 + 1] = l_a; }
+        }
+        if (row_b < rows) {
+            const size_t gr = (size_t)(t_base + row_b / G) * nh + kvh * G + row_b % G;
+            float* dst = part_o + ((size_t)split * n_rows + gr) * HD + col;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2], o[n][3]);
+            if ((lane & 3) == 0) { part_ml[((size_t)split * n_rows + gr) * 2] = m_b; part_ml[((size_t)split * n_rows + gr) * 2 + 1] = l_b; }
+        }
+    }
+}
+
+// out[row] = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, pieces in order.
+__global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+                                       const float* __restrict__ part_ml, size_t n_rows, int hd, int nsplit) {
+    const size_t row = blockIdx.x;
+    float m = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, part_ml[((size_t)s * n_rows + row) * 2]);
+    const float use = m == -INFINITY ? 0.f : m;
+    float l = 0.f;
+    for (int s = 0; s < nsplit; ++s)
+        l += exp2f(part_ml[((size_t)s * n_rows + row) * 2] - use) * part_ml[((size_t)s * n_rows + row) * 2 + 1];
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float w = exp2f(part_ml[((size_t)s * n_rows + row) * 2] - use);
+            if (w != 0.f) acc += w * part_o[((size_t)s * n_rows + row) * hd + d];
+        }
+        out[row * hd + d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int HD, int NWARPS>
+int launch_flash(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q, const __nv_bfloat16* k_pool,
+                 const __nv_bfloat16* v_pool, const int* cu, const int* ctx, const int* bt, int bt_stride, int B, int T,
+                 int n_tiles, int num_pages, int page_size, int nh, int nkv, float scale, int window, int nsplit,
+                 int* err, cudaStream_t stream) {
+    constexpr int BM = 16 * NWARPS;
+    const size_t smem = (size_t)(BM + 4 * FA_BN) * HD * 2;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_flash_kernel<HD, NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((unsigned)n_tiles, (unsigned)nkv, (unsigned)nsplit);
+    attention_flash_kernel<HD, NWARPS><<<grid, NWARPS * 32, smem, stream>>>(
+        out, part_o, part_ml, q, k_pool, v_pool, cu, ctx, bt, bt_stride, B, T, num_pages, page_size, nh, nkv,
+        scale * 1.4426950408889634f, window, err);
+    CELLM_LAUNCH_CHECK();
+    return CELLM_OK;
+}
+
+}  // namespace
+
+// Head sizes the tensor-core kernel is built for.
+CELLM_API int cellm_attention_flash_supports(int hd) { return hd == 32 || hd == 64 || hd == 128; }
+
+// out, q: [T, nh*hd] bf16. n_tiles: sum over requests of ceil(q_len * (nh/nkv) / rows_per_cta),
+// rows_per_cta = 64 (wide = 1) or 16 (wide = 0). nsplit > 1 needs part_o
+// [nsplit, T*nh, hd] and part_ml [nsplit, T*nh, 2] floats.
+CELLM_API int cellm_attention_flash(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
+                                    const void* v_pool, const int* cu_seqlens, const int* ctx_lens,
+                                    const int* block_table, int bt_stride, int B, int T, int n_tiles, int num_pages,
+                                    int page_size, int nh, int nkv, int hd, float scale, int window, int wide,
+                                    int nsplit, int* err, cudaStream_t stream) {
+    if (T <= 0 || n_tiles <= 0) return CELLM_OK;
+    if (nkv <= 0 || nh % nkv) return CELLM_ERR_SIZE;
+    if (nsplit < 1 || (nsplit > 1 && (!part_o || !part_ml))) return CELLM_ERR_ARG;
+    if (nkv > 65535 || nsplit > 65535) return CELLM_ERR_SIZE;
+    int rc;
+#define GO(HD_)                                                                                                   \
+    rc = wide ? launch_flash<HD_, 4>((__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q,               \
+                                     (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_seqlens,      \
+                                     ctx_lens, block_table, bt_stride, B, T, n_tiles, num_pages, page_size, nh,   \
+                                     nkv, scale, window, nsplit, err, stream)                                     \
+              : launch_flash<HD_, 1>((__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q,               \
+                                     (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_seqlens,      \
+                                     ctx_lens, block_table, bt_stride, B, T, n_tiles, num_pages, page_size, nh,   \
+                                     nkv, scale, window, nsplit, err, stream)
+    if (hd == 32) GO(32);
+    else if (hd == 64) GO(64);
+    else if (hd == 128) GO(128);
+    else return CELLM_ERR_SIZE;
+#undef GO
+    if (rc != CELLM_OK) return rc;
+    if (nsplit > 1) {
+        attention_merge_kernel<<<(unsigned)((size_t)T * nh), hd >= 64 ? 64 : 32, 0, stream>>>(
+            (__nv_bfloat16*)out, part_o, part_ml, (size_t)T * nh, hd, nsplit);
+        CELLM_LAUNCH_CHECK();
+    }
+    return CELLM_OK;
+}

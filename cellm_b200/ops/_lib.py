@@ -31,6 +31,10 @@ _SIGNATURES = {
     "gemm_plain": {
         "cellm_gemm_plain": [P, P, P, I, I, I, L, L, L, I, I, P],
     },
+    "attention_flash": {
+        "cellm_attention_flash": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P],
+        "cellm_attention_flash_supports": [I],
+    },
     "gemm_tcgen05": {
         "cellm_gemm_tcgen05": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, P],
     },
@@ -42,6 +46,10 @@ _funcs: dict[str, ctypes._CFuncPtr] = {}
 # point launches one kernel unless listed here.
 LAUNCHES = [0]
 _KERNELS_PER_CALL = {"cellm_short_conv": 2}
+
+
+def count_launch(n: int = 1) -> None:
+    LAUNCHES[0] += n
 
 
 def register_signatures(library: str, signatures: dict) -> None:

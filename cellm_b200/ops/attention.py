@@ -2,12 +2,74 @@ from __future__ import annotations
 
 import torch
 
+from ._lib import check, count_launch, fn, ptr, require_cuda, stream_of
 from .basic import attention_plain
+
+_FLASH_HEAD_SIZES = (32, 64, 128)
+_WORKSPACE: dict[torch.device, torch.Tensor] = {}
+
+
+def _workspace(device, n_floats: int) -> torch.Tensor:
+    ws = _WORKSPACE.get(device)
+    if ws is None or ws.numel() < n_floats:
+        ws = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
+        _WORKSPACE[device] = ws
+    return ws
+
+
+def plan_splits(n_tiles: int, nkv: int, max_total_len: int, sms: int) -> int:
+    """How many CTAs share the keys of one tile: enough to fill the GPU when the
+    batch alone does not, but at least two blocks of 64 keys each."""
+    blocks = (max_total_len + 63) // 64
+    target = (4 * sms + n_tiles * nkv - 1) // (n_tiles * nkv)
+    return max(1, min(target, blocks // 2))
+
+
+def attention_flash(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, cu_seqlens: torch.Tensor,
+                    ctx_lens: torch.Tensor, block_table: torch.Tensor, q_lens: list[int], nh: int, scale: float,
+                    window: int, err: torch.Tensor, nsplit: int = 1, wide: bool | None = None) -> torch.Tensor:
+    """Tensor-core attention for bfloat16: q [T, nh*hd], pools [pages, kv heads,
+    page size, hd]; request b owns tokens cu_seqlens[b]..cu_seqlens[b+1] at
+    positions ctx_lens[b] + i. `q_lens` are the host's copies of the portions' lengths."""
+    require_cuda(q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, err)
+    pages, nkv, page_size, hd = k_pool.shape
+    T, B = q.shape[0], len(q_lens)
+    if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or q.shape[1] != nh * hd or hd not in _FLASH_HEAD_SIZES:
+        raise ValueError("attention_flash: bfloat16 with head size 32, 64 or 128 only")
+    G = nh // nkv
+    if wide is None:
+        wide = max(q_lens) * G > 16
+    bm = 64 if wide else 16
+    n_tiles = sum((n * G + bm - 1) // bm for n in q_lens)
+    out = torch.empty_like(q)
+    part_o = part_ml = None
+    if nsplit > 1:
+        rows = T * nh
+        ws = _workspace(q.device, nsplit * rows * (hd + 2))
+        part_o, part_ml = ws[:nsplit * rows * hd], ws[nsplit * rows * hd:nsplit * rows * (hd + 2)]
+    check(fn("attention_flash", "cellm_attention_flash")(
+        ptr(out), ptr(part_o), ptr(part_ml), ptr(q), ptr(k_pool), ptr(v_pool), ptr(cu_seqlens), ptr(ctx_lens),
+        ptr(block_table), block_table.stride(0), B, T, n_tiles, pages, page_size, nh, nkv, hd, float(scale),
+        int(window), 1 if wide else 0, int(nsplit), ptr(err), stream_of(q)), "attention_flash")
+    if nsplit > 1:
+        count_launch()
+    return out
 
 
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, block_table: torch.Tensor,
               nh: int, scale: float, window: int) -> torch.Tensor:
-    """Attention of every token of the step over its request's pages. Chooses the
-    kernel by element type and by the shape of the batch."""
+    """Attention of every token of the step over its request's pages. bfloat16
+    with a head size the tensor-core kernel is built for runs there; everything
+    else (32-bit, other head sizes) runs the plain kernel."""
+    hd = k_pool.shape[3]
+    if q.dtype == torch.bfloat16 and hd in _FLASH_HEAD_SIZES:
+        from .gemm_bf16 import _sms
+        G = nh // k_pool.shape[1]
+        wide = ctx.max_q_len * G > 16
+        bm = 64 if wide else 16
+        n_tiles = sum((n * G + bm - 1) // bm for n in ctx.q_lens)
+        nsplit = plan_splits(n_tiles, k_pool.shape[1], ctx.max_total_len, _sms(q.device))
+        return attention_flash(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.q_lens, nh, scale,
+                               window, ctx.err, nsplit, wide)
     return attention_plain(q, k_pool, v_pool, ctx.positions, ctx.seq_of_token, block_table, nh, scale,
                            window, ctx.err)
