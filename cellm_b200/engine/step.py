@@ -38,7 +38,7 @@ _ERR_BITS = {1: "token id outside the vocabulary", 2: "page id outside the pool"
 
 
 class StepRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager):
+    def __init__(self, model: DecoderModel, cache: CacheManager, use_graphs: bool = False):
         self.model, self.cache = model, cache
         self.device = model.device
         from ..ops.gemm_bf16 import error_word
@@ -48,6 +48,9 @@ class StepRunner:
         self._flip = 0
         self.steps = 0
         self.tokens = 0
+        self.use_graphs = use_graphs
+        self.graph_width_step = 32        # block-table widths are rounded up to this many pages per graph
+        self._graphs: dict = {}
 
     # ------------------------------------------------------------------
     def _staging(self, n: int) -> torch.Tensor:
@@ -60,9 +63,9 @@ class StepRunner:
             self._pinned[i] = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=True)
         return self._pinned[i]
 
-    def build_context(self, entries: Sequence[StepEntry]):
-        """Checks the entries, reserves their pages and uploads the step's index
-        arrays in one copy. Returns (ctx, block tables per paged group, logit rows, new totals)."""
+    def _prepare(self, entries: Sequence[StepEntry]):
+        """Checks the entries and reserves their pages. Returns the host-side
+        description of the batch: (q_lens, ctx_lens, slots, totals, token ids, logit rows)."""
         cache = self.cache
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -89,58 +92,127 @@ class StepRunner:
             if not cache.reserve(e.request_id, total):
                 raise OutOfPages(f"request {e.request_id}: no pages left for {total} tokens "
                                  f"(free: {[cache.free_pages(g) for g in range(len(cache.paged_keys))]})")
-        B, T = len(entries), sum(q_lens)
         ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
         V = self.model.plan.vocab_size
         if ids.min() < 0 or ids.max() >= V:
             raise ValueError(f"token id {int(ids.max() if ids.max() >= V else ids.min())} outside the vocabulary of {V}")
-        cu = np.zeros(B + 1, dtype=np.int32)
+        cu = np.zeros(len(entries) + 1, dtype=np.int32)
         np.cumsum(q_lens, out=cu[1:])
         rows = [int(cu[b]) + w for b, e in enumerate(entries) for w in e.want]
-        R = len(rows)
-        n_groups = len(cache.paged_keys)
-        widths = [max((t + cache.page_size - 1) // cache.page_size for t in totals)] * n_groups
-        n_meta = 3 * T + (B + 1) + 2 * B + R + sum(B * w for w in widths)
-        stage = self._staging(n_meta)
-        buf = stage.numpy()
+        return q_lens, ctx_lens, slots, totals, ids, cu, rows
+
+    def _fill(self, buf: np.ndarray, entries, q_lens, ctx_lens, slots, ids, cu, rows, width: int):
+        """Writes the step's index arrays into `buf`; returns the (offset, length)
+        of each array and the (offset, B, width) of each block table."""
+        cache = self.cache
+        B, T, R = len(entries), int(cu[-1]), len(rows)
         o = 0
+
         def put(arr, n):
             nonlocal o
             buf[o:o + n] = arr
             o += n
             return (o - n, n)
-        s_ids = put(ids, T)
-        s_pos = put(np.concatenate([np.arange(c, c + n) for c, n in zip(ctx_lens, q_lens)]), T)
-        s_seq = put(np.repeat(np.arange(B), q_lens), T)
-        s_cu = put(cu, B + 1)
-        s_ctx = put(ctx_lens, B)
-        s_slot = put(slots, B)
-        s_rows = put(rows, R) if R else (o, 0)
-        s_bt = []
-        for g in range(n_groups):
-            w = widths[g]
-            tab = buf[o:o + B * w].reshape(B, w)
+        spans = {"ids": put(ids, T),
+                 "pos": put(np.concatenate([np.arange(c, c + n) for c, n in zip(ctx_lens, q_lens)]), T),
+                 "seq": put(np.repeat(np.arange(B), q_lens), T),
+                 "cu": put(cu, B + 1), "ctx": put(ctx_lens, B), "slot": put(slots, B),
+                 "rows": put(rows, R) if R else (o, 0)}
+        tables = []
+        for g in range(len(cache.paged_keys)):
+            tab = buf[o:o + B * width].reshape(B, width)
             tab.fill(-1)
             for b, e in enumerate(entries):
                 cache.block_table(e.request_id, g, tab[b])
-            s_bt.append((o, B, w))
-            o += B * w
+            tables.append((o, B, width))
+            o += B * width
+        return spans, tables, o
+
+    def _meta_size(self, B, T, R, width) -> int:
+        return 3 * T + (B + 1) + 2 * B + R + len(self.cache.paged_keys) * B * width
+
+    def _context(self, dev: torch.Tensor, spans, tables, q_lens, ctx_lens, max_total_len):
+        view = lambda s: dev[s[0]:s[0] + s[1]]
+        T, B = spans["ids"][1], len(q_lens)
+        ctx = StepContext(T=T, B=B, dtype=self.model.dtype, device=self.device, token_ids=view(spans["ids"]),
+                          positions=view(spans["pos"]), seq_of_token=view(spans["seq"]), cu_seqlens=view(spans["cu"]),
+                          ctx_lens=view(spans["ctx"]), slot_ids=view(spans["slot"]), err=self.err, q_lens=list(q_lens),
+                          ctx_lens_host=list(ctx_lens), max_q_len=max(q_lens), max_total_len=max_total_len)
+        tabs = [dev[o0:o0 + b * w].view(b, w) for (o0, b, w) in tables]
+        logit_rows = view(spans["rows"]) if spans["rows"][1] else None
+        return ctx, tabs, logit_rows
+
+    def build_context(self, entries: Sequence[StepEntry]):
+        """Checks the entries, reserves their pages and uploads the step's index
+        arrays in one copy. Returns (ctx, block tables per paged group, logit rows, new totals)."""
+        q_lens, ctx_lens, slots, totals, ids, cu, rows = self._prepare(entries)
+        width = max((t + self.cache.page_size - 1) // self.cache.page_size for t in totals)
+        n_meta = self._meta_size(len(entries), int(cu[-1]), len(rows), width)
+        stage = self._staging(n_meta)
+        spans, tables, n = self._fill(stage.numpy(), entries, q_lens, ctx_lens, slots, ids, cu, rows, width)
         dev = stage[:n_meta].to(self.device, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self._events[self._flip] = ev
-        view = lambda s: dev[s[0]:s[0] + s[1]]
-        ctx = StepContext(T=T, B=B, dtype=self.model.dtype, device=self.device, token_ids=view(s_ids),
-                          positions=view(s_pos), seq_of_token=view(s_seq), cu_seqlens=view(s_cu),
-                          ctx_lens=view(s_ctx), slot_ids=view(s_slot), err=self.err, q_lens=q_lens,
-                          ctx_lens_host=ctx_lens, max_q_len=max(q_lens), max_total_len=max(totals))
-        tables = [dev[o0:o0 + b * w].view(b, w) for (o0, b, w) in s_bt]
-        logit_rows = view(s_rows) if R else None
-        return ctx, tables, logit_rows, totals
+        ctx, tabs, logit_rows = self._context(dev, spans, tables, q_lens, ctx_lens, max(totals))
+        return ctx, tabs, logit_rows, totals
+
+    # ------------------------------------------------------------- decoding with CUDA graphs
+    def _run_decode_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step in which every entry is one token whose logits are wanted: the
+        launches of such a step depend only on the number of entries and on the
+        width of the block tables, so they are captured once per (entries, width
+        bucket) in a CUDA graph and replayed; only the index arrays change."""
+        q_lens, ctx_lens, slots, totals, ids, cu, rows = self._prepare(entries)
+        B, ps = len(entries), self.cache.page_size
+        need = max((t + ps - 1) // ps for t in totals)
+        width = -(-need // self.graph_width_step) * self.graph_width_step
+        n_meta = self._meta_size(B, B, B, width)
+        stage = self._staging(n_meta)
+        spans, tables, _ = self._fill(stage.numpy(), entries, q_lens, ctx_lens, slots, ids, cu, rows, width)
+        key = (B, width)
+        g = self._graphs.get(key)
+        if g is None:
+            g = {"meta": torch.empty(n_meta, dtype=torch.int32, device=self.device)}
+            self._graphs[key] = g
+        g["meta"].copy_(stage[:n_meta], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[self._flip] = ev
+        if "graph" not in g:
+            ctx, tabs, logit_rows = self._context(g["meta"], spans, tables, q_lens, ctx_lens, width * ps)
+            bindings = self.cache.bindings(tabs)
+            # One eager run loads every kernel this shape uses; fixed-size state is
+            # put back afterwards, because the captured run will update it again.
+            slot_idx = torch.tensor(slots, dtype=torch.long, device=self.device)
+            saved = [s[:, slot_idx].clone() for s in self.cache.states]
+            self.model.forward(ctx, bindings, logit_rows)
+            for s, keep in zip(self.cache.states, saved):
+                s[:, slot_idx] = keep
+            torch.cuda.synchronize(self.device)
+            from ..ops._lib import LAUNCHES
+            graph = torch.cuda.CUDAGraph()
+            before = LAUNCHES[0]
+            with torch.cuda.graph(graph):
+                g["logits"] = self.model.forward(ctx, bindings, logit_rows)
+            g["graph"] = graph
+            g["launches"] = LAUNCHES[0] - before     # kernels one replay runs
+            LAUNCHES[0] = before
+        from ..ops._lib import LAUNCHES
+        g["graph"].replay()
+        LAUNCHES[0] += g["launches"]
+        for e, total in zip(entries, totals):
+            self.cache.commit(e.request_id, total)
+        self.steps += 1
+        self.tokens += B
+        return g["logits"]
 
     def run(self, entries: Sequence[StepEntry], max_layers: Optional[int] = None) -> Optional[torch.Tensor]:
         """Runs one step; returns float32 logits [number of wanted places, vocab] in
-        the order of the entries and of their `want`, or None if nothing is wanted."""
+        the order of the entries and of their `want`, or None if nothing is wanted.
+        The tensor may be overwritten by the next step."""
+        if self.use_graphs and max_layers is None and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return self._run_decode_graph(entries)
         ctx, tables, logit_rows, totals = self.build_context(entries)
         logits = self.model.forward(ctx, self.cache.bindings(tables), logit_rows, max_layers)
         for e, total in zip(entries, totals):

@@ -10,6 +10,9 @@ _WORKSPACE: dict[torch.device, torch.Tensor] = {}
 
 
 def _workspace(device, n_floats: int) -> torch.Tensor:
+    if torch.cuda.is_current_stream_capturing():
+        # a captured launch keeps its pointers: give it memory of the graph's own pool
+        return torch.empty(n_floats, dtype=torch.float32, device=device)
     ws = _WORKSPACE.get(device)
     if ws is None or ws.numel() < n_floats:
         ws = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
