@@ -187,6 +187,41 @@ def time_prefill(loaded, rng, reps=5, warmup=3):
     return sorted(times)[len(times) // 2]
 
 
+def profile_region(loaded, args, rng) -> int:
+    """One decode step of the batch (launched kernel by kernel, no graph) or one
+    2,048-token prefill between cudaProfilerStart and cudaProfilerStop."""
+    import torch
+    from cellm_b200.engine import StepEntry
+    if args.profile_region == "decode":
+        eng, ids = decode_setup(loaded, args.batch, args.batch * CONTEXT_LEN // PAGE, rng)
+        eng.runner.use_graphs = False
+        V = eng.plan.vocab_size
+        step = lambda: eng.runner.run([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in ids])
+    else:
+        from cellm_b200.cache import CacheManager
+        from cellm_b200.engine import StepRunner
+        cfg, plan, model = loaded
+        cache = CacheManager(model.cache_needs(), [e.cache_of for e in plan.order], PAGE, 4 * (PROMPT_LEN // PAGE + 1), 4,
+                             model.dtype, model.device)
+        runner = StepRunner(model, cache)
+        toks = rng.integers(0, plan.vocab_size, PROMPT_LEN).tolist()
+        counter = [0]
+
+        def step():
+            cache.add(counter[0])
+            runner.run([StepEntry(counter[0], toks, [PROMPT_LEN - 1])])
+            counter[0] += 1
+    for _ in range(max(args.warmup, 1)):
+        step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(f"profiled one {args.profile_region} step")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -195,6 +230,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 runs")
+    ap.add_argument("--profile-region", choices=["decode", "prefill"], default=None,
+                    help="for a profiler started with --profile-from-start off: run the set-up, then one eager "
+                         "decode step (or one prefill) between cudaProfilerStart/Stop, print no bench line")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -233,6 +271,9 @@ def main() -> int:
                     weight_bytes += w.numel() * w.element_size()
     weight_bytes += model.head.weight.numel() * model.head.weight.element_size()
     print(f"[bench] model ready in {time.time() - t_setup:.1f}s, matrix weights {weight_bytes / 1e9:.3f} GB", file=sys.stderr)
+
+    if args.profile_region:
+        return profile_region(loaded, args, rng)
 
     sampler = ClockSampler()
     sampler.start()
