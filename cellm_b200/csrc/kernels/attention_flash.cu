@@ -19,6 +19,8 @@
 // Cache layout of one layer: [page][kv_head][slot in page][head_dim].
 #include <mma.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -337,4 +339,86 @@ CELLM_API int cellm_attention_flash(void* out, float* part_o, float* part_ml, co
         CELLM_LAUNCH_CHECK();
     }
     return CELLM_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Entry point that allocates nothing (declared in attention_flash_noalloc.h).
+//
+// Who it is for: code that drives the GPU from a place where device memory
+// cannot be asked for — a host callback or a real-time thread that must not
+// block inside the driver, a plugin that was handed a fixed arena and may not
+// grow the process's footprint, a caller between graph replays that has to keep
+// every pointer stable. The regular entry point above leaves the split pieces
+// (unnormalised outputs, maxima, sums) to a workspace its caller allocates; this
+// one keeps them in the fixed array below, which lives in the library's image:
+// every GPU that loads the library holds these bytes until the process exits.
+//
+// Limits and rules:
+//   * nsplit * T * nh * (hd + 2) floats must fit NOALLOC_SCRATCH_FLOATS (8 MiB);
+//     larger calls are refused with CELLM_ERR_SCRATCH and nothing is launched.
+//   * The first call on a device looks the array's device address up
+//     (cudaGetSymbolAddress with that device current). Make that first call
+//     outside any stream capture.
+//   * All calls share the one array. It keeps the previous call's contents;
+//     nothing in it has to start at zero, because every (piece, row) the merge
+//     reads is written by this call's first kernel. Two calls whose kernels
+//     overlap on the GPU (different streams, or graphs replayed side by side)
+//     race on it: serialise them.
+//   * No cudaMalloc, cudaFree or allocating library call is made.
+#define NOALLOC_SCRATCH_FLOATS (2 * 1024 * 1024)
+#define NOALLOC_MAX_DEVICES 64
+
+static __device__ __align__(256) float noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+float* noalloc_scratch_ptr[NOALLOC_MAX_DEVICES];   // device address of the array, per device; null until looked up
+std::mutex noalloc_mutex;
+}  // namespace
+
+enum { CELLM_ERR_SCRATCH = -5, CELLM_ERR_DEVICE = -6 };
+
+CELLM_API const char* cellm_attention_flash_noalloc_error(int code) {
+    switch (code) {
+        case CELLM_OK: return "ok";
+        case CELLM_ERR_SCRATCH: return "nsplit * T * nh * (hd + 2) floats exceed the built-in scratch of 2097152 floats (8 MiB); use fewer pieces or fewer tokens per call";
+        case CELLM_ERR_DEVICE: return "the current device could not be determined, or its index is beyond the 64 this entry point keeps addresses for";
+        case CELLM_ERR_SIZE: return "a size the kernel does not take (head size must be 32, 64 or 128; heads a multiple of key/value heads)";
+        case CELLM_ERR_ARG: return "nsplit must be at least 1";
+        default: return code > 0 ? "a CUDA error (the code is a cudaError_t)" : "unknown error";
+    }
+}
+
+CELLM_API long long cellm_attention_flash_noalloc_capacity() { return NOALLOC_SCRATCH_FLOATS; }
+
+// Same arguments and result as cellm_attention_flash without the two workspace
+// pointers. Inputs and the output are the caller's; the split pieces go to the
+// library's own fixed array.
+CELLM_API int cellm_attention_flash_noalloc(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                            const int* cu_seqlens, const int* ctx_lens, const int* block_table,
+                                            int bt_stride, int B, int T, int n_tiles, int num_pages, int page_size,
+                                            int nh, int nkv, int hd, float scale, int window, int wide, int nsplit,
+                                            int* err, cudaStream_t stream) {
+    if (nsplit < 1) return CELLM_ERR_ARG;
+    if (T <= 0 || n_tiles <= 0) return CELLM_OK;
+    const long long need = (long long)nsplit * T * nh * (hd + 2);
+    if (nsplit > 1 && need > (long long)NOALLOC_SCRATCH_FLOATS) return CELLM_ERR_SCRATCH;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return CELLM_ERR_DEVICE;
+    float* base;
+    {
+        std::lock_guard<std::mutex> lock(noalloc_mutex);
+        if (noalloc_scratch_ptr[dev] == nullptr) {
+            // In host code `noalloc_scratch` is only a handle for the symbol, not a device address.
+            void* p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, noalloc_scratch);
+            if (e != cudaSuccess) return (int)e;
+            noalloc_scratch_ptr[dev] = static_cast<float*>(p);
+        }
+        base = noalloc_scratch_ptr[dev];
+    }
+    float* part_o = base;
+    float* part_ml = base + (size_t)nsplit * T * nh * hd;
+    return cellm_attention_flash(out, nsplit > 1 ? part_o : nullptr, nsplit > 1 ? part_ml : nullptr, q, k_pool, v_pool,
+                                 cu_seqlens, ctx_lens, block_table, bt_stride, B, T, n_tiles, num_pages, page_size, nh,
+                                 nkv, hd, scale, window, wide, nsplit, err, stream);
 }
