@@ -83,13 +83,19 @@ StepPlan Scheduler::schedule() {
     StepPlan plan;
     for (int attempt = 0; attempt < 1 + (int)requests_.size(); ++attempt) {
         int budget = cfg_.max_batch_tokens;
-        // 1. one token for each decoding request, in rotation order
+        // 1. one token for each decoding request, in rotation order. While prompts are
+        //    under way or waiting for a free slot, a quarter of the budget (at least one
+        //    token) is kept for them, or decoders alone could fill every step for ever.
         std::vector<int64_t> decoders;
-        for (int64_t id : running_)
+        bool prompt_work = !waiting_.empty() && cache_->free_slots() > 0;
+        for (int64_t id : running_) {
             if (requests_.at(id).state == RequestState::Decoding) decoders.push_back(id);
+            else prompt_work = true;
+        }
+        const int kept = (prompt_work && budget > 1) ? std::max(1, budget / 4) : 0;
         std::vector<int64_t> taken;
         for (int64_t id : decoders) {
-            if (budget == 0) break;
+            if (budget <= kept) break;
             if (!cache_->has(id)) continue;  // preempted a moment ago
             Request& r = requests_.at(id);
             if (r.state != RequestState::Decoding) continue;
@@ -140,9 +146,11 @@ StepPlan Scheduler::schedule() {
             Request& r = requests_.at(id);
             const int slot = cache_->add_request(id);
             if (slot < 0) break;
+            // Admit only if the pool could hold all the tokens the request has now;
+            // otherwise it would start, starve a decoding request of pages and be
+            // preempted again at once.
             int n = std::min({(int)r.tokens.size(), cfg_.prefill_chunk, budget});
-            while (n > 0 && !cache_->reserve(id, n)) n = ((n - 1) / cache_->page_size()) * cache_->page_size();
-            if (n <= 0) { cache_->release(id); break; }
+            if (!cache_->can_reserve(id, (int)r.tokens.size()) || !cache_->reserve(id, n)) { cache_->release(id); break; }
             waiting_.pop_front();
             running_.push_back(id);
             r.state = RequestState::Prefill;

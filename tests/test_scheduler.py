@@ -1,0 +1,149 @@
+"""The scheduler's decisions, on the CPU: admission, portions under a budget,
+rotation, finishing, and what happens when pages run out."""
+import pytest
+import torch
+
+from cellm_b200.cache import CacheManager
+from cellm_b200.engine import Scheduler, SchedulerError
+from cellm_b200.parts import FixedState, PagedKV
+
+
+def make(pages=16, page=4, slots=3, budget=16, chunk=8, max_pos=256):
+    cm = CacheManager([FixedState((2, 4)), PagedKV(1, 8, 0)], [None, None], page, pages, slots, torch.float32, "cpu")
+    return cm, Scheduler(cm, budget, chunk, max_pos)
+
+
+def run_step(s, token=5, stop_on=None):
+    """schedule, pretend the step ran, append a token wherever logits were wanted."""
+    plan = s.schedule()
+    s.step_done()
+    finished = []
+    for e in plan.entries:
+        if e.wants_logits and s.append_token(e.request_id, token, stop=(stop_on == e.request_id)):
+            finished.append(e.request_id)
+    return plan, finished
+
+
+def test_prompts_are_cut_into_portions_under_the_budget():
+    cm, s = make()
+    s.add_request(0, list(range(20)), 4)
+    s.add_request(1, list(range(5)), 4)
+    plan, _ = run_step(s)
+    assert [(e.request_id, e.start, e.count, e.wants_logits) for e in plan.entries] == [(0, 0, 8, False), (1, 0, 5, True)]
+    assert sorted(r for r, _ in plan.admitted) == [0, 1]
+    plan, _ = run_step(s)      # request 1 decodes first, request 0 goes on with its prompt
+    assert [(e.request_id, e.start, e.count) for e in plan.entries] == [(1, 5, 1), (0, 8, 8)]
+    plan, _ = run_step(s)
+    assert [(e.request_id, e.start, e.count, e.wants_logits) for e in plan.entries] == [(1, 6, 1, True), (0, 16, 4, True)]
+    assert s.info(0)["state"] == "decoding" and s.info(0)["generated"] == 1
+
+
+def test_budget_limits_decoders_and_rotation_serves_all():
+    cm, s = make(pages=32, slots=4, budget=2, chunk=2)
+    for r in range(3):
+        s.add_request(r, [1, 2], 50)
+    served = {0: 0, 1: 0, 2: 0}
+    while not all(s.info(r)["state"] == "decoding" for r in range(3)):
+        run_step(s)
+    for _ in range(9):
+        plan, _ = run_step(s)
+        assert len(plan.entries) == 2 and sum(e.count for e in plan.entries) == 2
+        for e in plan.entries:
+            served[e.request_id] += 1
+    assert set(served.values()) == {6}          # two of three each step, evenly
+
+
+def test_admission_waits_for_a_slot_and_keeps_arrival_order():
+    cm, s = make(slots=2)
+    for r in range(4):
+        s.add_request(r, [1, 2, 3], 2)
+    plan, _ = run_step(s)
+    assert [r for r, _ in plan.admitted] == [0, 1] and s.stats()["waiting"] == 2
+    plan, fin = run_step(s)
+    assert fin == [0, 1] and s.info(0)["finish_reason"] == "length"
+    plan, _ = run_step(s)
+    assert [r for r, _ in plan.admitted] == [2, 3]
+
+
+def test_finish_frees_pages_and_slot_stop_and_cancel():
+    cm, s = make()
+    s.add_request(0, list(range(6)), 10)
+    s.add_request(1, list(range(6)), 10)
+    run_step(s)
+    assert cm.free_pages(0) == 16 - 4 and cm.free_slots == 1
+    _, fin = run_step(s, stop_on=0)
+    assert fin == [0] and s.info(0)["finish_reason"] == "stop"
+    assert cm.free_pages(0) == 16 - 2 and cm.free_slots == 2
+    s.cancel(1)
+    assert s.info(1)["finish_reason"] == "cancelled" and cm.free_pages(0) == 16 and cm.free_slots == 3
+    assert s.stats()["idle"]
+    s.forget(0)
+    assert not s.has(0)
+    with pytest.raises(SchedulerError):
+        s.cancel(0)
+
+
+def test_requests_that_cannot_fit_are_refused_when_added():
+    cm, s = make(pages=4, page=4, max_pos=64)
+    with pytest.raises(SchedulerError, match="pages"):
+        s.add_request(0, list(range(10)), 10)           # 20 tokens > 4 pages of 4
+    with pytest.raises(SchedulerError, match="positions"):
+        s.add_request(1, list(range(60)), 10)
+    with pytest.raises(SchedulerError):
+        s.add_request(2, [], 4)
+    with pytest.raises(SchedulerError):
+        s.add_request(3, [1], 0)
+    s.add_request(4, list(range(10)), 6)
+    with pytest.raises(SchedulerError, match="exists"):
+        s.add_request(4, [1], 1)
+
+
+def test_pages_run_out_newest_request_is_preempted_and_recomputed():
+    cm, s = make(pages=6, page=4, slots=3, budget=32, chunk=16)
+    s.add_request(0, list(range(8)), 12)     # 2 pages now, 5 in the end
+    s.add_request(1, list(range(8)), 12)
+    plan, _ = run_step(s)
+    assert len(plan.entries) == 2 and cm.free_pages(0) == 2
+    preempted_at = None
+    for step in range(40):
+        plan, fin = run_step(s)
+        if plan.preempted:
+            assert plan.preempted == [1]                    # the one admitted last
+            assert not plan.admitted                        # and nobody is admitted in that step
+            assert s.info(1)["state"] == "waiting" and s.info(1)["computed"] == 0
+            assert s.info(1)["num_tokens"] == 8 + s.info(1)["generated"]      # it keeps what it generated
+            preempted_at = step
+            break
+    assert preempted_at is not None
+    recomputed = False
+    while not s.stats()["idle"]:
+        plan, fin = run_step(s)
+        for e in plan.entries:      # when 1 comes back it recomputes prompt + generated, in portions that
+            if e.request_id == 1 and e.start == 0:         # end at a page edge while pages are short
+                recomputed = True
+                assert e.count == 13 and e.wants_logits      # 8 prompt + 5 generated, admitted once all of it fits
+    assert recomputed and s.info(0)["generated"] == 12 and s.info(1)["generated"] == 12
+    assert s.info(1)["preemptions"] >= 1 and s.stats()["preemptions"] >= 1
+    assert cm.free_pages(0) == 6 and cm.free_slots == 3
+
+
+def test_prefill_that_holds_each_others_pages_is_untangled():
+    cm, s = make(pages=4, page=4, slots=2, budget=8, chunk=4)
+    s.add_request(0, list(range(12)), 2)
+    s.add_request(1, list(range(12)), 2)
+    steps = 0
+    while not s.stats()["idle"]:
+        run_step(s)
+        steps += 1
+        assert steps < 60
+    assert s.info(0)["generated"] == 2 and s.info(1)["generated"] == 2 and cm.free_pages(0) == 4
+
+
+def test_append_rules():
+    cm, s = make()
+    s.add_request(0, list(range(12)), 3)
+    s.schedule()
+    s.step_done()
+    with pytest.raises(SchedulerError, match="not decoding"):
+        s.append_token(0, 1)
+    assert s.tokens(0) == list(range(12)) and s.tokens(0, 10) == [10, 11]
