@@ -48,7 +48,7 @@ class StepRunner:
         self._flip = 0
         self.steps = 0
         self.tokens = 0
-        self.use_graphs = use_graphs
+        self.use_graphs = use_graphs and model.graph_safe
         self.graph_width_step = 32        # block-table widths are rounded up to this many pages per graph
         self._graphs: dict = {}
 

@@ -40,6 +40,10 @@ class DecoderModel:
                                                                 _weights_of(spec.feed_forward_norm, tensors), dtype)
             self.blocks.append(part_class("block", spec.block)(n1, mixer, n2, ffn))
             self.mixer_classes.append(mixer_cls)
+        self.graph_safe = self.final_norm.graph_safe and all(
+            b.graph_safe and b.mixer.graph_safe and b.feed_forward.graph_safe and b.mixer_norm.graph_safe
+            and b.feed_forward_norm.graph_safe and getattr(getattr(b.mixer, "position", None), "graph_safe", True)
+            for b in self.blocks)
         for i, e in enumerate(plan.order):
             if e.cache_of is not None:
                 if not self.mixer_classes[e.layer].can_read_foreign_cache:

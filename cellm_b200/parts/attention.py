@@ -15,6 +15,8 @@ from .registry import part_class, register_mixer
 
 
 class AttentionMixer(Mixer):
+    graph_safe = True
+
     """params: hidden_size, num_heads, num_kv_heads, head_dim, scale, window,
     qk_norm (PartSpec of a norm over head_dim, or None), position (PartSpec or None).
     weights: q_proj [nh*hd, H], k_proj, v_proj [nkv*hd, H], out_proj [H, nh*hd],

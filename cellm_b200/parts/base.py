@@ -118,6 +118,10 @@ class Residual:
 class Part:
     """Base of all parts: parameters in, tensors in."""
     kind: str = ""
+    # True if forward() only launches work on the current stream (no host read of
+    # device data, no host-side branching on it), so that a decode step may be
+    # captured in a CUDA graph. A part that does not say so keeps its model eager.
+    graph_safe: bool = False
 
     @classmethod
     def weight_specs(cls, params: dict) -> dict[str, TensorSpec]:

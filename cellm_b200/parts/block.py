@@ -7,6 +7,8 @@ from .registry import register_block
 
 
 class PreNormBlock(Block):
+    graph_safe = True
+
     def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward):
         self.mixer_norm, self.mixer = mixer_norm, mixer
         self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward

@@ -12,6 +12,8 @@ from .registry import register_norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     """params: dim, eps. weights: weight [dim]."""
 
     @classmethod

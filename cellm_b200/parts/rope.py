@@ -11,6 +11,8 @@ from .registry import register_position
 
 
 class RotaryEmbedding(Position):
+    graph_safe = True
+
     """params: head_dim, rotary_dim, theta, layout ("half" | "interleaved")."""
 
     def __init__(self, params: dict, device):

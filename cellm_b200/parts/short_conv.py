@@ -14,6 +14,8 @@ from .registry import register_mixer
 
 
 class ShortConvMixer(Mixer):
+    graph_safe = True
+
     """params: hidden_size, taps, bias. weights: in_proj [3H, H], conv [H, 1, taps],
     out_proj [H, H], conv_bias [H] if bias."""
 

@@ -12,6 +12,8 @@ from .registry import register_feed_forward
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     """params: hidden_size, ff_dim. weights: w1, w3 [ff, H]; w2 [H, ff]."""
 
     @classmethod

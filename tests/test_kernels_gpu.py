@@ -1,0 +1,357 @@
+"""Each kernel alone against a plain float32/float64 torch restatement of the
+same operation, at sizes other than the engine's (widths that are no power of
+two, odd counts, several head sizes and page sizes)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, ref):
+    k = 2e-6 if dtype == torch.float32 else 1.2e-2
+    return k * (1.0 + float(ref.abs().max()))
+
+
+def close(got, ref, dtype, what=""):
+    err = float((got.double().cpu() - ref.double().cpu()).abs().max())
+    assert err <= tol(dtype, ref.double()), f"{what}: {err} > {tol(dtype, ref.double())}"
+
+
+def err_word():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_embed(dtype):
+    from cellm_b200 import ops
+    table = torch.randn(777, 100, device=DEV).to(dtype)
+    ids = torch.tensor([0, 776, 5, 5, 300], dtype=torch.int32, device=DEV)
+    e = err_word()
+    out = ops.embed(table, ids, e)
+    assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float()) and e.item() == 0
+    out = ops.embed(table, torch.tensor([3, 777], dtype=torch.int32, device=DEV), e)
+    assert e.item() == 1 and float(out[1].abs().max()) == 0.0          # the bad id is flagged, not read
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("H", [100, 2048, 3000])
+def test_add_rmsnorm(dtype, H):
+    from cellm_b200 import ops
+    T = 7
+    x = torch.randn(T, H, device=DEV)
+    delta = torch.randn(T, H, device=DEV).to(dtype)
+    w = (torch.rand(H, device=DEV) + 0.5).to(dtype)
+    x0 = x.clone()
+    y = ops.add_rmsnorm(x, delta, w, 1e-3, dtype)
+    s = x0.double() + delta.double()
+    close(x, s, torch.float32, "stream")
+    close(y, plain.rms_norm(s.cpu(), w.double().cpu(), 1e-3), dtype, "normed")
+    rows = torch.tensor([4, 0, 4], dtype=torch.int32, device=DEV)
+    x1 = x.clone()
+    y = ops.add_rmsnorm(x, delta, w, 1e-3, dtype, rows)
+    assert torch.equal(x, x1)                                           # selected rows leave the stream alone
+    close(y, plain.rms_norm((x1.double() + delta.double())[rows.long()].cpu(), w.double().cpu(), 1e-3), dtype, "rows")
+    close(ops.add_rmsnorm(x, None, w.float(), 1e-6, dtype), plain.rms_norm(x1.double().cpu(), w.double().cpu(), 1e-6), dtype, "no addend, 32-bit weight")
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_swiglu_and_residual_add(dtype):
+    from cellm_b200 import ops
+    gu = (torch.randn(5, 600, device=DEV) * 3).to(dtype)
+    g, u = gu[:, :300].double(), gu[:, 300:].double()
+    close(ops.swiglu(gu), g * torch.sigmoid(g) * u, dtype)
+    x = torch.randn(5, 77, device=DEV)
+    d = torch.randn(5, 77, device=DEV).to(dtype)
+    ref = x.double() + d.double()
+    ops.residual_add(x, d)
+    close(x, ref, torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("taps,bias", [(1, False), (2, True), (3, False), (5, True)])
+def test_short_conv_portions_carry_the_state(dtype, taps, bias):
+    """Three requests fed in portions of 1, 2, 3 and 7 tokens, two of them in
+    the same launch, against the whole-sequence convolution."""
+    from cellm_b200 import ops
+    H, slots = 50, 4
+    lens = {0: 13, 1: 9, 2: 4}
+    bcx = {r: torch.randn(n, 3 * H, device=DEV).to(dtype) for r, n in lens.items()}
+    w = (torch.randn(H, taps, device=DEV) * 0.5).to(dtype)
+    b = (torch.randn(H, device=DEV) * 0.5).to(dtype) if bias else None
+
+    def whole(x):
+        x = x.double().cpu()
+        B, C, xt = x[:, :H], x[:, H:2 * H], x[:, 2 * H:]
+        hist = torch.cat([torch.zeros(taps - 1, H, dtype=torch.float64), B * xt])
+        conv = sum(hist[k:k + x.shape[0]] * w.double().cpu()[:, k] for k in range(taps))
+        return C * (conv + (b.double().cpu() if bias else 0))
+    state = torch.zeros(slots, max(taps - 1, 0), H, device=DEV)
+    state[3] = 7.0                                    # a slot nobody uses must stay as it is
+    slot_of = {0: 2, 1: 0, 2: 1}
+    fed = {r: 0 for r in lens}
+    got = {r: [] for r in lens}
+    e = err_word()
+    schedule = [[(0, 1), (1, 2)], [(0, 2), (2, 3)], [(1, 7)], [(0, 3), (2, 1)], [(0, 7)]]
+    for step in schedule:
+        rows = torch.cat([bcx[r][fed[r]:fed[r] + n] for r, n in step])
+        cu = torch.tensor(np.cumsum([0] + [n for _, n in step]), dtype=torch.int32, device=DEV)
+        seq = torch.cat([torch.full((n,), i) for i, (_, n) in enumerate(step)]).int().to(DEV)
+        sl = torch.tensor([slot_of[r] for r, _ in step], dtype=torch.int32, device=DEV)
+        y = ops.short_conv(rows, w, b, state, sl, seq, cu, e)
+        o = 0
+        for r, n in step:
+            got[r].append(y[o:o + n])
+            fed[r] += n
+            o += n
+    assert e.item() == 0 and fed == lens and bool((state[3] == 7).all())
+    for r in lens:
+        close(torch.cat(got[r]), whole(bcx[r]), dtype, f"request {r}")
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("hd,rot,inter", [(16, 16, False), (48, 32, False), (64, 64, True), (32, 0, False)])
+def test_qk_norm_rope_and_page_write(dtype, hd, rot, inter):
+    from cellm_b200 import ops
+    nh, nkv, ps, pages = 6, 2, 8, 9
+    pos = torch.tensor([0, 1, 17, 30, 31, 5], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([0, 0, 1, 1, 1, 2], dtype=torch.int32, device=DEV)
+    bt = torch.tensor([[3, -1, -1, -1], [0, 8, 2, 5], [7, -1, -1, -1]], dtype=torch.int32, device=DEV)
+    T = pos.numel()
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).to(dtype)
+    qw, kw = (torch.rand(hd, device=DEV) + 0.5).to(dtype), (torch.rand(hd, device=DEV) + 0.5).to(dtype)
+    theta = 1e4
+    inv = (theta ** (-(2.0 * torch.arange(rot // 2, dtype=torch.float64)) / max(rot, 1))).to(DEV) if rot else None
+    kp = torch.zeros(pages, nkv, ps, hd, device=DEV, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    e = err_word()
+    q = ops.qk_norm_rope(qkv, qw, kw, 1e-5, pos, seq, bt, kp, vp, ps, nh, nkv, hd, rot, inter, inv, e)
+    assert e.item() == 0
+
+    def ref_heads(x, w, n):
+        x = plain.rms_norm(x.double().cpu().reshape(T, n, hd), w.double().cpu(), 1e-5)
+        if rot:
+            if inter:     # pairs (2i, 2i+1)  (crates/cellm-kernels/src/cpu_kernels.rs:279-292)
+                xr = x[..., :rot].reshape(T, n, rot // 2, 2)
+                ang = pos.double().cpu()[:, None] * inv.cpu()[None, :]
+                c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+                r = torch.stack([xr[..., 0] * c - xr[..., 1] * s_, xr[..., 1] * c + xr[..., 0] * s_], -1).reshape(T, n, rot)
+            else:
+                r = plain.rope_rotate_half(x[..., :rot], pos.cpu(), theta)
+            x = torch.cat([r, x[..., rot:]], -1)
+        return x
+    close(q.reshape(T, nh, hd), ref_heads(qkv[:, :nh * hd], qw, nh), dtype, "q")
+    k_ref = ref_heads(qkv[:, nh * hd:(nh + nkv) * hd], kw, nkv)
+    v_ref = qkv[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+    written = torch.zeros(pages, ps, dtype=torch.bool)
+    for t in range(T):
+        page, off = int(bt[seq[t], pos[t] // ps]), int(pos[t]) % ps
+        close(kp[page, :, off], k_ref[t], dtype, f"k of token {t}")
+        assert torch.equal(vp[page, :, off], v_ref[t])
+        written[page, off] = True
+    assert float(kp.float().abs().sum(dim=(1, 3)).cpu()[~written].max()) == 0.0     # nothing else was touched
+    bad = bt.clone()
+    bad[2, 0] = pages
+    ops.qk_norm_rope(qkv, qw, kw, 1e-5, pos, seq, bad, kp, vp, ps, nh, nkv, hd, rot, inter, inv, e)
+    assert e.item() == 2
+
+
+def paged_case(q_lens, ctx_lens, nh, nkv, hd, ps, dtype, seed=0, scale_one=None):
+    g = torch.Generator().manual_seed(seed)
+    totals = [c + n for c, n in zip(ctx_lens, q_lens)]
+    nblk = [-(-t // ps) for t in totals]
+    pages = sum(nblk) + 2
+    perm = torch.randperm(pages, generator=g).tolist()
+    bt = torch.full((len(q_lens), max(nblk)), -1, dtype=torch.int32)
+    k_seq, v_seq, o = [], [], 0
+    kp = torch.zeros(pages, nkv, ps, hd)
+    vp = torch.zeros(pages, nkv, ps, hd)
+    for b, t in enumerate(totals):
+        bt[b, :nblk[b]] = torch.tensor(perm[o:o + nblk[b]], dtype=torch.int32)
+        o += nblk[b]
+        k = torch.randn(t, nkv, hd, generator=g)
+        v = torch.randn(t, nkv, hd, generator=g)
+        if scale_one is not None and b == scale_one[0]:
+            k[scale_one[1]] *= scale_one[2]
+        k, v = k.to(dtype).float(), v.to(dtype).float()
+        k_seq.append(k), v_seq.append(v)
+        for j in range(t):
+            kp[bt[b, j // ps], :, j % ps] = k[j]
+            vp[bt[b, j // ps], :, j % ps] = v[j]
+    q = torch.randn(sum(q_lens), nh * hd, generator=g).to(dtype)
+    return dict(q=q.to(DEV), kp=kp.to(dtype).to(DEV), vp=vp.to(dtype).to(DEV), bt=bt.to(DEV), k_seq=k_seq, v_seq=v_seq,
+                q_lens=q_lens, ctx_lens=ctx_lens,
+                pos=torch.cat([torch.arange(c, c + n) for c, n in zip(ctx_lens, q_lens)]).int().to(DEV),
+                seq=torch.cat([torch.full((n,), b) for b, n in enumerate(q_lens)]).int().to(DEV),
+                cu=torch.tensor(np.cumsum([0] + q_lens), dtype=torch.int32, device=DEV),
+                ctx=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV))
+
+
+def attention_reference(c, nh, nkv, hd, scale, window):
+    out, o = [], 0
+    for b, (n, ctx) in enumerate(zip(c["q_lens"], c["ctx_lens"])):
+        q = c["q"][o:o + n].double().cpu().reshape(n, nh, hd)
+        k, v = c["k_seq"][b].double(), c["v_seq"][b].double()
+        res = torch.zeros(n, nh, hd, dtype=torch.float64)
+        for i in range(n):
+            p = ctx + i
+            lo = max(0, p - window + 1) if window else 0
+            for h in range(nh):
+                s = (k[lo:p + 1, h // (nh // nkv)] @ q[i, h]) * scale
+                res[i, h] = torch.softmax(s, 0) @ v[lo:p + 1, h // (nh // nkv)]
+        out.append(res.reshape(n, nh * hd))
+        o += n
+    return torch.cat(out)
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(4, 2, 16, 8, 0), (3, 1, 48, 16, 0), (6, 6, 80, 4, 0), (4, 2, 32, 8, 21)])
+def test_attention_plain(dtype, nh, nkv, hd, ps, window):
+    from cellm_b200 import ops
+    c = paged_case([9, 1, 40], [0, 150, 130], nh, nkv, hd, ps, dtype, seed=1)
+    e = err_word()
+    out = ops.attention_plain(c["q"], c["kp"], c["vp"], c["pos"], c["seq"], c["bt"], nh, hd ** -0.5, window, e)
+    assert e.item() == 0
+    close(out, attention_reference(c, nh, nkv, hd, hd ** -0.5, window), dtype)
+
+
+@pytest.mark.parametrize("kernel", ["plain32", "plain16", "flash"])
+def test_a_far_key_among_hundreds_is_found(kernel):
+    """One early key is scaled so that its score towers over 600 others: the
+    output must be that key's value. A kernel that skips a page, stops short or
+    reads a neighbour's page cannot pass."""
+    from cellm_b200 import ops
+    from cellm_b200.ops.attention import attention_flash
+    dtype = torch.float32 if kernel == "plain32" else torch.bfloat16
+    nh, nkv, hd, ps = 4, 2, 64, 16
+    for far in (0, 15, 16, 337):                       # a page's first and last slot, and the middle of nowhere
+        c = paged_case([1, 3], [640, 600], nh, nkv, hd, ps, dtype, seed=far, scale_one=(0, far, 1.0))
+        kh = c["k_seq"][0][far, 0]
+        c["q"][0, :hd] = (kh / kh.norm() * 60).to(dtype).to(DEV)          # head 0 of request 0 looks at key `far`
+        e = err_word()
+        if kernel == "flash":
+            out = attention_flash(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], nh, 1.0, 0, e, nsplit=3)
+        else:
+            out = ops.attention_plain(c["q"], c["kp"], c["vp"], c["pos"], c["seq"], c["bt"], nh, 1.0, 0, e)
+        assert e.item() == 0
+        close(out[0, :hd], c["v_seq"][0][far, 0], dtype, f"far key {far}")
+        close(out, attention_reference(c, nh, nkv, hd, 1.0, 0), dtype, f"far key {far}, all rows")
+
+
+@pytest.mark.parametrize("hd,ps,nh,nkv", [(32, 8, 3, 1), (64, 16, 8, 2), (128, 32, 4, 4), (64, 4, 32, 8)])
+@pytest.mark.parametrize("window", [0, 33])
+def test_attention_flash(hd, ps, nh, nkv, window):
+    from cellm_b200.ops.attention import attention_flash
+    c = paged_case([70, 1, 5, 1], [0, 200, 59, 64], nh, nkv, hd, ps, torch.bfloat16, seed=2)
+    ref = attention_reference(c, nh, nkv, hd, hd ** -0.5, window)
+    e = err_word()
+    for nsplit, wide in ((1, None), (3, True)):
+        out = attention_flash(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], nh, hd ** -0.5, window, e, nsplit, wide)
+        close(out, ref, torch.bfloat16, f"nsplit {nsplit}")
+    d = paged_case([1, 1, 1], [3, 700, 64], nh, nkv, hd, ps, torch.bfloat16, seed=3)         # decode shape, narrow tiles
+    out = attention_flash(d["q"], d["kp"], d["vp"], d["cu"], d["ctx"], d["bt"], d["q_lens"], nh, hd ** -0.5, window, e, 4, False)
+    close(out, attention_reference(d, nh, nkv, hd, hd ** -0.5, window), torch.bfloat16, "decode")
+    assert e.item() == 0
+
+
+def test_window_edge():
+    """The key just outside the window carries a huge score and must not count;
+    the key just inside does."""
+    from cellm_b200 import ops
+    from cellm_b200.ops.attention import attention_flash
+    nh, nkv, hd, ps, window = 2, 1, 32, 8, 24
+    for dtype, kernel in ((torch.float32, "plain"), (torch.bfloat16, "plain"), (torch.bfloat16, "flash")):
+        for edge, inside in ((100 - window, False), (100 - window + 1, True)):
+            c = paged_case([1], [100], nh, nkv, hd, ps, dtype, seed=4)
+            kh = c["k_seq"][0][edge, 0]
+            c["q"][0, :hd] = (kh / kh.norm() * 50).to(dtype).to(DEV)
+            e = err_word()
+            if kernel == "flash":
+                out = attention_flash(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], nh, 1.0, window, e)
+            else:
+                out = ops.attention_plain(c["q"], c["kp"], c["vp"], c["pos"], c["seq"], c["bt"], nh, 1.0, window, e)
+            hit = float((out[0, :hd].float().cpu() - c["v_seq"][0][edge, 0]).abs().max()) < 0.05
+            assert hit == inside, (dtype, kernel, edge)
+            close(out, attention_reference(c, nh, nkv, hd, 1.0, window), dtype)
+
+
+@pytest.mark.parametrize("dtype,out", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (37, 101, 53), (130, 64, 300), (5, 1000, 96)])
+def test_gemm_plain(dtype, out, M, N, K):
+    from cellm_b200 import ops
+    a, w = torch.randn(M, K, device=DEV).to(dtype), torch.randn(N, K, device=DEV).to(dtype)
+    close(ops.gemm_plain(a, w, out), a.double() @ w.double().T, out)
+    big = torch.randn(M, K + 3, device=DEV).to(dtype)
+    close(ops.gemm_plain(big[:, :K], w, out), big[:, :K].double() @ w.double().T, out, "strided rows")
+
+
+@pytest.mark.parametrize("out", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K,bn,split", [
+    (128, 128, 64, 128, 1), (200, 1000, 96, 128, 1), (300, 520, 1024, 256, 1), (100, 72, 2048, 64, 1),
+    (129, 257, 72, 256, 1), (1, 1000, 224, -16, 1), (8, 512, 2048, -16, 4), (17, 130, 8192, -32, 8),
+    (40, 1000, 224, -64, 1), (64, 96, 96, -64, 2), (70, 300, 4096, 64, 4)])
+def test_gemm_tcgen05(out, M, N, K, bn, split):
+    from cellm_b200.ops.gemm_bf16 import error_word, gemm_tcgen05
+    a = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.5).bfloat16()
+    c = gemm_tcgen05(a, w, out, bn, split)
+    torch.cuda.synchronize()
+    assert error_word(a.device).item() == 0
+    ref = a.double() @ w.double().T
+    k = 3e-6 if out == torch.float32 else 6e-3          # 32-bit sums of exact bf16 products; then one bf16 rounding
+    assert float((c.double() - ref).abs().max()) <= k * (1 + float(ref.abs().max()))
+
+
+def test_gemm_dispatch_covers_every_size():
+    from cellm_b200 import ops
+    for M, N, K in ((3, 50, 20), (3, 50, 24), (200, 333, 40), (64, 2048, 2048), (65, 64, 64)):
+        a, w = torch.randn(M, K, device=DEV).bfloat16(), torch.randn(N, K, device=DEV).bfloat16()
+        close(ops.gemm(a, w), a.double() @ w.double().T, torch.bfloat16, f"{M}x{N}x{K}")
+        close(ops.gemm(a, w, torch.float32), a.double() @ w.double().T, torch.float32 if K < 64 else torch.bfloat16)
+    a, w = torch.randn(9, 33, device=DEV), torch.randn(21, 33, device=DEV)
+    close(ops.gemm(a, w), a.double() @ w.double().T, torch.float32)
+
+
+def test_argmax_and_sampling_follow_the_plain_sampler():
+    from cellm_b200 import ops
+    torch.manual_seed(0)
+    R, V = 6, 3001
+    logits = torch.randn(R, V, device=DEV) * 3
+    logits[0, 7] = logits[0, 2000] = 50.0          # equal maxima: the lower id wins
+    logits[1, 5] = float("nan")
+    logits[2, :] = -1.0
+    assert ops.argmax(logits).tolist() == [7] + logits[1:2].nan_to_num(-1e30).argmax(-1).tolist() + [0] + logits[3:].argmax(-1).tolist()
+    rng = plain.XorShift64(99)
+    checked = 0
+    for trial in range(40):
+        temps = [0.0, 0.7, 1.3, 0.9, 0.8, 1.0]
+        ks = [0, 40, 5, 0, 1024, 1]
+        pens = [1.0, 1.05, 1.0, 1.3, 1.0, 2.0]
+        us = [rng.next_f32() for _ in range(R)]
+        recent = [[int(x) for x in torch.randint(0, V, (9,))] for _ in range(R)]
+        for r in range(R):                                   # make the penalty matter: recent holds the leaders
+            recent[r][:3] = logits[r].nan_to_num(-1e30).topk(3).indices.tolist()
+        out = ops.sample(logits, torch.tensor(temps, device=DEV), torch.tensor(ks, dtype=torch.int32, device=DEV),
+                         torch.tensor(us, device=DEV), torch.tensor(pens, device=DEV),
+                         torch.tensor(recent, dtype=torch.int32, device=DEV), 1024).tolist()
+        for r in range(R):
+            class U:      # the plain sampler draws its own number: hand it ours
+                def next_f32(self_inner):
+                    return us[r]
+            cands = plain.top_k_candidates(logits[r].cpu(), ks[r])
+            ref = plain.select_next(cands, temps[r], pens[r], 64, recent[r], U())
+            if out[r] != ref:
+                # only a draw that falls within rounding of a boundary of the distribution may differ
+                sc = np.array([s / pens[r] if (pens[r] > 1 and i in recent[r]) else s for i, s in cands], dtype=np.float64)
+                w = np.exp((sc - sc.max()) / temps[r])
+                cdf = np.cumsum(w) / w.sum()
+                assert np.abs(cdf - us[r]).min() < 1e-5, (trial, r, out[r], ref)
+            else:
+                checked += 1
+    assert checked > 200
