@@ -15,6 +15,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
                                    const TW* __restrict__ w, TA* __restrict__ y,
                                    const int* __restrict__ rows, int H, float eps) {
     __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
     float* xr = x + (size_t)t * H;
@@ -44,16 +46,14 @@ CELLM_API int cellm_add_rmsnorm(float* x, const void* delta, const void* w, int 
                                 cudaStream_t stream) {
     if (n_rows <= 0) return CELLM_OK;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-#define LAUNCH(TA, TW)                                                                          \
-    add_rmsnorm_kernel<TA, TW><<<n_rows, threads, 0, stream>>>(x, (const TA*)delta, (const TW*)w, \
-                                                               (TA*)y, rows, H, eps)
+#define LAUNCH(TA, TW) \
+    CELLM_RUN((add_rmsnorm_kernel<TA, TW>), n_rows, threads, 0, stream, x, (const TA*)delta, (const TW*)w, (TA*)y, rows, H, eps)
     if (act_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float);
     else if (act_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16);
     else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, float);
     else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else return CELLM_ERR_DTYPE;
 #undef LAUNCH
-    CELLM_LAUNCH_CHECK();
     return CELLM_OK;
 }
 
@@ -61,6 +61,8 @@ CELLM_API int cellm_add_rmsnorm(float* x, const void* delta, const void* w, int 
 // block's output is not followed by a norm that could absorb it).
 template <typename TA>
 __global__ void residual_add_kernel(float* __restrict__ x, const TA* __restrict__ delta, size_t n) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] += to_float(delta[i]);
 }
@@ -71,10 +73,9 @@ CELLM_API int cellm_residual_add(float* x, const void* delta, long long n, int a
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     if (act_dtype == CELLM_F32)
-        residual_add_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float*)delta, (size_t)n);
+        CELLM_RUN(residual_add_kernel<float>, blocks, threads, 0, stream, x, (const float*)delta, (size_t)n);
     else if (act_dtype == CELLM_BF16)
-        residual_add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(x, (const __nv_bfloat16*)delta, (size_t)n);
+        CELLM_RUN(residual_add_kernel<__nv_bfloat16>, blocks, threads, 0, stream, x, (const __nv_bfloat16*)delta, (size_t)n);
     else return CELLM_ERR_DTYPE;
-    CELLM_LAUNCH_CHECK();
     return CELLM_OK;
 }

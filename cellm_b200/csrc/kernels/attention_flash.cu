@@ -82,6 +82,8 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
     const int G = nh / nkv;
     const int kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_trigger();
+    pdl_wait();
 
     // which request this tile belongs to
     int b = 0, base = 0;
@@ -261,6 +263,8 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
 // out[row] = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, pieces in order.
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, size_t n_rows, int hd, int nsplit) {
+    pdl_trigger();
+    pdl_wait();
     const size_t row = blockIdx.x;
     float m = -INFINITY;
     for (int s = 0; s < nsplit; ++s) m = fmaxf(m, part_ml[((size_t)s * n_rows + row) * 2]);
@@ -293,10 +297,9 @@ int launch_flash(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_b
         configured = true;
     }
     dim3 grid((unsigned)n_tiles, (unsigned)nkv, (unsigned)nsplit);
-    attention_flash_kernel<HD, NWARPS><<<grid, NWARPS * 32, smem, stream>>>(
-        out, part_o, part_ml, q, k_pool, v_pool, cu, ctx, bt, bt_stride, B, T, num_pages, page_size, nh, nkv,
-        scale * 1.4426950408889634f, window, err);
-    CELLM_LAUNCH_CHECK();
+    CELLM_RUN((attention_flash_kernel<HD, NWARPS>), grid, NWARPS * 32, smem, stream,
+              out, part_o, part_ml, q, k_pool, v_pool, cu, ctx, bt, bt_stride, B, T, num_pages, page_size, nh, nkv,
+              scale * 1.4426950408889634f, window, err);
     return CELLM_OK;
 }
 
@@ -334,9 +337,8 @@ CELLM_API int cellm_attention_flash(void* out, float* part_o, float* part_ml, co
 #undef GO
     if (rc != CELLM_OK) return rc;
     if (nsplit > 1) {
-        attention_merge_kernel<<<(unsigned)((size_t)T * nh), hd >= 64 ? 64 : 32, 0, stream>>>(
-            (__nv_bfloat16*)out, part_o, part_ml, (size_t)T * nh, hd, nsplit);
-        CELLM_LAUNCH_CHECK();
+        CELLM_RUN(attention_merge_kernel, (unsigned)((size_t)T * nh), hd >= 64 ? 64 : 32, 0, stream,
+                  (__nv_bfloat16*)out, (const float*)part_o, (const float*)part_ml, (size_t)T * nh, hd, nsplit);
     }
     return CELLM_OK;
 }

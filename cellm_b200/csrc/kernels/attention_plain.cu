@@ -29,6 +29,8 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
     float* sc = smem + hd;        // [CH]
     int* pg = (int*)(sc + CH);    // [CH] page of each key in the chunk
     __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x / nh, h = blockIdx.x % nh;
     const int kvh = h / (nh / nkv);
     const int pos = positions[t];
@@ -113,15 +115,14 @@ CELLM_API int cellm_attention_plain(void* out, const void* q, const void* k_pool
     const size_t smem = (size_t)(hd + 2 * ATTN_PLAIN_THREADS) * sizeof(float);
     const unsigned grid = (unsigned)T * (unsigned)nh;
     if (dtype == CELLM_F32)
-        attention_plain_kernel<float><<<grid, ATTN_PLAIN_THREADS, smem, stream>>>(
+        CELLM_RUN(attention_plain_kernel<float>, grid, ATTN_PLAIN_THREADS, smem, stream,
             (float*)out, (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, seq_of_token,
             block_table, bt_stride, num_pages, page_size, nh, nkv, hd, scale, window, err);
     else if (dtype == CELLM_BF16)
-        attention_plain_kernel<__nv_bfloat16><<<grid, ATTN_PLAIN_THREADS, smem, stream>>>(
+        CELLM_RUN(attention_plain_kernel<__nv_bfloat16>, grid, ATTN_PLAIN_THREADS, smem, stream,
             (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, positions, seq_of_token, block_table, bt_stride, num_pages,
             page_size, nh, nkv, hd, scale, window, err);
     else return CELLM_ERR_DTYPE;
-    CELLM_LAUNCH_CHECK();
     return CELLM_OK;
 }

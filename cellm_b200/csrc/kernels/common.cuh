@@ -4,6 +4,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+#include <utility>
+
 #define CELLM_API extern "C" __attribute__((visibility("default")))
 
 // Element type tags passed from the host.
@@ -74,6 +77,48 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     t = warp_max(t);
     return t;
 }
+
+// ---- programmatic dependent launch -----------------------------------------
+// Kernels are launched with the attribute that lets the next kernel of the
+// stream start while the previous one is still running. Every kernel therefore
+// calls pdl_wait() before it reads anything an earlier kernel wrote and before
+// it writes anything an earlier kernel may still read; what comes before the
+// wait (barrier set-up, tensor-memory allocation, loads of weights) overlaps
+// the tail of the previous kernel. pdl_trigger() lets the following kernel
+// begin its own preamble. CELLM_B200_PDL=0 in the environment turns the
+// attribute off (the instructions are then no-ops).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline int cellm_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("CELLM_B200_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t cellm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = cellm_pdl_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+
+#define CELLM_RUN(kernel, grid, block, smem, stream, ...)                                   \
+    do {                                                                                    \
+        cudaError_t e__ = cellm_launch(kernel, dim3(grid), dim3(block), smem, stream, __VA_ARGS__); \
+        if (e__ != cudaSuccess) return (int)e__;                                            \
+    } while (0)
 
 #define CELLM_LAUNCH_CHECK()                         \
     do {                                             \

@@ -7,6 +7,8 @@
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
                              const int* __restrict__ ids, int H, int V, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < V;
@@ -21,11 +23,10 @@ CELLM_API int cellm_embed(float* out, const void* table, int table_dtype, const 
     if (T <= 0) return CELLM_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == CELLM_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>(out, (const float*)table, ids, H, V, err);
+        CELLM_RUN(embed_kernel<float>, T, threads, 0, stream, out, (const float*)table, ids, H, V, err);
     else if (table_dtype == CELLM_BF16)
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, H, V, err);
+        CELLM_RUN(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, out, (const __nv_bfloat16*)table, ids, H, V, err);
     else
         return CELLM_ERR_DTYPE;
-    CELLM_LAUNCH_CHECK();
     return CELLM_OK;
 }

@@ -17,6 +17,8 @@ gemm_plain_kernel(TO* __restrict__ C, const TI* __restrict__ A, const TI* __rest
                   int K, long long lda, long long ldw, long long ldc) {
     __shared__ float As[GP_BK][GP_BM + 4];
     __shared__ float Ws[GP_BK][GP_BN + 4];
+    pdl_trigger();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * GP_BM, n0 = blockIdx.x * GP_BN;
@@ -71,12 +73,11 @@ CELLM_API int cellm_gemm_plain(void* C, const void* A, const void* W, int M, int
     dim3 grid((unsigned)((N + GP_BN - 1) / GP_BN), (unsigned)((M + GP_BM - 1) / GP_BM));
     if (grid.y > 65535) return CELLM_ERR_SIZE;
 #define LAUNCH(TI, TO) \
-    gemm_plain_kernel<TI, TO><<<grid, 256, 0, stream>>>((TO*)C, (const TI*)A, (const TI*)W, M, N, K, lda, ldw, ldc)
+    CELLM_RUN((gemm_plain_kernel<TI, TO>), grid, 256, 0, stream, (TO*)C, (const TI*)A, (const TI*)W, M, N, K, lda, ldw, ldc)
     if (in_dtype == CELLM_F32 && out_dtype == CELLM_F32) LAUNCH(float, float);
     else if (in_dtype == CELLM_BF16 && out_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (in_dtype == CELLM_BF16 && out_dtype == CELLM_F32) LAUNCH(__nv_bfloat16, float);
     else return CELLM_ERR_DTYPE;
 #undef LAUNCH
-    CELLM_LAUNCH_CHECK();
     return CELLM_OK;
 }

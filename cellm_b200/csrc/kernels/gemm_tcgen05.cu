@@ -22,8 +22,12 @@
 // the epilogue then writes its tile transposed.
 //
 // With split_k > 1 (skinny products, M small) blockIdx.z selects a slice of K;
-// each slice writes its partial tile as float into a workspace
-// [split_k, M, N] and a second kernel sums the slices in a fixed order.
+// each slice writes its partial tile as float into a workspace [split_k, M, N]
+// and the slice that finishes last sums them in a fixed order (see the kernel).
+//
+// The kernel takes part in programmatic dependent launch: barrier set-up, the
+// tensor-memory allocation and the loads of W for the first stages run before
+// the wait on the preceding kernel; only loads of A and all stores come after.
 #include <cuda.h>
 
 #include <mutex>
@@ -147,6 +151,7 @@ struct alignas(1024) GemmSmem {
     uint64_t acc_full;
     uint32_t tmem_base;
     int abort_flag;
+    int is_last;
 };
 
 template <typename TO> __device__ __forceinline__ void store_row(TO* dst, const uint32_t* r, int valid, bool aligned);
@@ -180,16 +185,28 @@ template <> __device__ __forceinline__ void store_row<__nv_bfloat16>(__nv_bfloat
     }
 }
 
+__device__ __forceinline__ float silu_mul(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
+
 // The 128-row operand ("rows") and the BN-row operand ("cols") of a tile:
 //   SWAP = false: rows = A (tokens),  cols = W;  grid (ceil(N/BN),  ceil(M/128), split_k); tile element (p, q) -> C[p][q]
 //   SWAP = true:  rows = W,           cols = A;  grid (ceil(N/128), ceil(M/BN),  split_k); tile element (p, q) -> C[q][p]
-// C is the output [M, N] (row pitch ldc) when split_k == 1, else the float
-// workspace [split_k, M, N] (row pitch N).
-template <int BN, int STAGES, bool SWAP, typename TO>
+//
+// EPI = 0: C[M, N] = A.W^T.
+// EPI = 1: W holds blocks of 64 gate rows followed by their 64 up rows; the
+//          output is C[M, N/2] with C[m][64j + i] = silu(g) * u for
+//          g = (A.W^T)[m][128j + i], u = (A.W^T)[m][128j + 64 + i].
+//
+// A tile goes through the float workspace ws[split][M][N] when K is split
+// (gridDim.z > 1) or when gate and up sit in different threads (EPI = 1 with
+// SWAP). With a split, every CTA of a tile adds one to the tile's counter after
+// its piece is written; the CTA that finds the counter at split_k - 1 sums all
+// pieces in the order of the splits, writes the output and sets the counter
+// back to zero. No CTA waits for another.
+template <int BN, int STAGES, bool SWAP, int EPI, typename TO>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
-                    TO* __restrict__ C, int M, int N, int K, long long ldc, int kblocks_per_split,
-                    int* __restrict__ err) {
+                    TO* __restrict__ C, float* __restrict__ ws, int* __restrict__ counters, int M, int N, int K,
+                    long long ldc, int kblocks_per_split, int w_is_static, int* __restrict__ err) {
     extern __shared__ uint8_t smem_raw[];
     auto& sm = *reinterpret_cast<GemmSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
@@ -198,15 +215,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     const int q0 = (SWAP ? blockIdx.y : blockIdx.x) * BN;    // first row of the narrow operand
     const int P = SWAP ? N : M, Q = SWAP ? M : N;
     const int kblocks_total = (K + BK - 1) / BK;
+    const int splits = gridDim.z;
     const int kb0 = blockIdx.z * kblocks_per_split;
     const int kb1 = min(kb0 + kblocks_per_split, kblocks_total);
     const int nkb = kb1 - kb0;           // > 0 by construction of the grid
-    if (gridDim.z > 1) C += (size_t)blockIdx.z * (size_t)M * (size_t)ldc;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
         mbar_init(&sm.acc_full, 1);
         sm.abort_flag = 0;
+        sm.is_last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_rows) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_cols) : "memory");
@@ -215,12 +233,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_trigger();
     const uint32_t tmem = sm.tmem_base;
     volatile int* abort_flag = &sm.abort_flag;
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb; ++i) {
+            // Weights that no kernel writes (w_is_static) do not depend on the kernel
+            // before this one: their loads for the first stages go out before the wait
+            // on that kernel, the activations' loads after it.
+            if (!w_is_static) pdl_wait();
+            const CUtensorMap* map_w = SWAP ? &map_rows : &map_cols;
+            const CUtensorMap* map_x = SWAP ? &map_cols : &map_rows;
+            const int w0 = SWAP ? p0 : q0, x0 = SWAP ? q0 : p0;
+            const int early = nkb < STAGES ? nkb : STAGES;
+            for (int i = 0; i < early; ++i) {
+                mbar_expect_tx(&sm.full[i], (BM + BN) * BK * 2);
+                tma_load_2d(SWAP ? (void*)sm.a[i] : (void*)sm.b[i], map_w, (kb0 + i) * BK, w0, &sm.full[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(SWAP ? (void*)sm.b[i] : (void*)sm.a[i], map_x, (kb0 + i) * BK, x0, &sm.full[i]);
+            for (int i = early; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
                 if (!mbar_wait(&sm.empty[s], phase ^ 1u, abort_flag)) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); break; }
@@ -251,11 +285,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         const bool ok = mbar_wait(&sm.acc_full, 0, abort_flag);
         if (!ok && lane == 0) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); }
         tc_fence_after();
-        if (ok) {
-            const int qtr = warp & 3;                     // the quarter of the lanes this warp may read
-            const int p = p0 + qtr * 32 + lane;
-            const uint32_t lane_addr = tmem + ((uint32_t)(qtr * 32) << 16);
-            if constexpr (!SWAP) {
+        pdl_wait();     // global writes below must not pass the kernel before this one
+        const int qtr = warp & 3;                     // the quarter of the lanes this warp may read
+        const int pl = qtr * 32 + lane;               // row of the tile this thread holds
+        const int p = p0 + pl;
+        const uint32_t lane_addr = tmem + ((uint32_t)(qtr * 32) << 16);
+        const bool through_ws = splits > 1 || (EPI == 1 && SWAP);
+        if (ok && !through_ws) {
+            if constexpr (EPI == 0 && !SWAP) {
                 const bool aligned = ((reinterpret_cast<uintptr_t>(C) | (uintptr_t)(ldc * sizeof(TO))) & 15) == 0 &&
                                      ((q0 * sizeof(TO)) & 15) == 0;
 #pragma unroll 1
@@ -265,7 +302,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     const int q = q0 + c * 32;
                     if (p < P && q < Q) store_row<TO>(C + (size_t)p * ldc + q, r, Q - q, aligned);
                 }
-            } else {
+            } else if constexpr (EPI == 0 && SWAP) {
                 constexpr int W = BN < 32 ? 16 : 32;
 #pragma unroll 1
                 for (int c = 0; c < BN / W; ++c) {
@@ -280,25 +317,143 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                         }
                     }
                 }
+            } else if constexpr (EPI == 1 && !SWAP && BN >= 128) {
+                // columns of the tile come as [64 gate | 64 up] per 128: both halves are in this thread
+                const int o0 = q0 / 2;
+                const bool aligned = ((reinterpret_cast<uintptr_t>(C) | (uintptr_t)(ldc * sizeof(TO))) & 15) == 0 &&
+                                     ((o0 * sizeof(TO)) & 15) == 0;
+#pragma unroll 1
+                for (int j = 0; j < BN / 128; ++j) {
+#pragma unroll 1
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t g[32], u[32];
+                        tmem_ld32(lane_addr + (uint32_t)(j * 128 + h * 32), g);
+                        tmem_ld32(lane_addr + (uint32_t)(j * 128 + 64 + h * 32), u);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(silu_mul(__uint_as_float(g[i]), __uint_as_float(u[i])));
+                        const int o = o0 + j * 64 + h * 32;
+                        if (p < P && o < Q / 2) store_row<TO>(C + (size_t)p * ldc + o, g, Q / 2 - o, aligned);
+                    }
+                }
+            }
+        }
+        if (through_ws) {
+            float* mine = ws + (size_t)blockIdx.z * (size_t)M * (size_t)N;
+            if (ok) {
+                constexpr int W = BN < 32 ? 16 : 32;
+#pragma unroll 1
+                for (int c = 0; c < BN / W; ++c) {
+                    uint32_t r[W];
+                    if constexpr (W == 16) tmem_ld16(lane_addr + (uint32_t)(c * W), r);
+                    else tmem_ld32(lane_addr + (uint32_t)(c * W), r);
+                    if (p < P) {
+                        if constexpr (SWAP) {
+#pragma unroll
+                            for (int j = 0; j < W; ++j) {
+                                const int q = q0 + c * W + j;
+                                if (q < Q) mine[(size_t)q * N + p] = __uint_as_float(r[j]);
+                            }
+                        } else {
+                            const int q = q0 + c * W;
+                            if (q < Q) store_row<float>(mine + (size_t)p * N + q, r, Q - q, (N & 3) == 0);
+                        }
+                    }
+                }
+            }
+            bool last = true;
+            if (splits > 1) {
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+                    const int old = atomicAdd(&counters[tile], 1);
+                    sm.is_last = (old == splits - 1) ? 1 : 0;
+                    if (old == splits - 1) counters[tile] = 0;      // ready for the next product
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                last = sm.is_last != 0;
+                __threadfence();
+            } else {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            if (last && !*abort_flag) {
+                // Pieces are summed in the order of the splits. Eight outputs are carried at
+                // a time so that eight loads are in flight for every add that has to wait.
+                const size_t slice = (size_t)M * (size_t)N;
+                const int q_end = min(Q, q0 + BN);
+                if constexpr (SWAP) {
+                    // this thread owns weight row p (an output column) for the tile's tokens
+                    const bool gate = EPI == 1;
+                    const int pu = p + 64;
+                    const bool active = gate ? (pl < 64 && pu < P) : (p < P);
+                    if (active) {
+                        for (int q = q0; q < q_end; q += 8) {
+                            float g[8], u[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) g[j] = u[j] = 0.f;
+#pragma unroll 2
+                            for (int sp = 0; sp < splits; ++sp) {
+                                const float* src = ws + (size_t)sp * slice + (size_t)q * N;
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    if (q + j < q_end) {
+                                        g[j] += src[(size_t)j * N + p];
+                                        if (gate) u[j] += src[(size_t)j * N + pu];
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                if (q + j < q_end) {
+                                    if (gate) C[(size_t)(q + j) * ldc + (p0 / 2 + pl)] = from_float<TO>(silu_mul(g[j], u[j]));
+                                    else C[(size_t)(q + j) * ldc + p] = from_float<TO>(g[j]);
+                                }
+                            }
+                        }
+                    }
+                } else if (p < P) {
+                    // this thread owns token row p for the tile's columns
+                    if constexpr (EPI == 0) {
+                        for (int q = q0; q < q_end; q += 8) {
+                            float acc[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll 2
+                            for (int sp = 0; sp < splits; ++sp) {
+                                const float* src = ws + (size_t)sp * slice + (size_t)p * N + q;
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    if (q + j < q_end) acc[j] += src[j];
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (q + j < q_end) C[(size_t)p * ldc + q + j] = from_float<TO>(acc[j]);
+                        }
+                    } else {
+                        for (int q = q0; q + 64 < q_end; q += 128)
+                            for (int i = 0; i < 64 && q + 64 + i < q_end; i += 8) {
+                                float g[8], u[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) g[j] = u[j] = 0.f;
+#pragma unroll 2
+                                for (int sp = 0; sp < splits; ++sp) {
+                                    const float* src = ws + (size_t)sp * slice + (size_t)p * N + q + i;
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j)
+                                        if (q + 64 + i + j < q_end) { g[j] += src[j]; u[j] += src[64 + j]; }
+                                }
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    if (q + 64 + i + j < q_end) C[(size_t)p * ldc + (q / 2 + i + j)] = from_float<TO>(silu_mul(g[j], u[j]));
+                            }
+                    }
+                }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
-}
-
-// Sum of the split-K slices in the order of the slices, then the conversion.
-template <typename TO>
-__global__ void splitk_reduce_kernel(TO* __restrict__ C, const float* __restrict__ ws, int M, int N, long long ldc,
-                                     int splits) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t total = (size_t)M * N;
-    if (i >= total) return;
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) acc += ws[(size_t)s * total + i];
-    const size_t m = i / N, n = i - m * N;
-    C[m * ldc + n] = from_float<TO>(acc);
 }
 
 // ---------------------------------------------------------------- host side
@@ -357,79 +512,104 @@ bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
     return true;
 }
 
-template <int BN, int STAGES, bool SWAP, typename TO>
-int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, int M, int N, int K, long long ldc,
-           int split_k, int kblocks_per_split, int* err, cudaStream_t stream) {
+template <int BN, int STAGES, bool SWAP, int EPI, typename TO>
+int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* ws, int* counters, int M, int N, int K,
+           long long ldc, int split_k, int kblocks_per_split, int w_is_static, int* err, cudaStream_t stream) {
     const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, SWAP, TO>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, SWAP, EPI, TO>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid = SWAP ? dim3((unsigned)((N + BM - 1) / BM), (unsigned)((M + BN - 1) / BN), (unsigned)split_k)
                      : dim3((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)split_k);
-    gemm_tcgen05_kernel<BN, STAGES, SWAP, TO><<<grid, 192, smem, stream>>>(m_rows, m_cols, C, M, N, K, ldc,
-                                                                          kblocks_per_split, err);
-    CELLM_LAUNCH_CHECK();
-    return CELLM_OK;
+    cudaError_t e = cellm_launch(gemm_tcgen05_kernel<BN, STAGES, SWAP, EPI, TO>, grid, dim3(192), smem, stream, m_rows,
+                                 m_cols, C, ws, counters, M, N, K, ldc, kblocks_per_split, w_is_static, err);
+    return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
 }  // namespace
 
-// A: [M, K] bf16 (row pitch lda elements), W: [N, K] bf16 (pitch ldw), C: [M, N] of
-// out_dtype (pitch ldc). bn > 0: plain tiles of 128 rows of A by bn (64, 128, 256)
-// rows of W. bn < 0: swapped tiles of 128 rows of W by -bn (16, 32, 64) rows of A.
-// split_k >= 1; with split_k > 1 `workspace` holds split_k * M * N floats.
-CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
-                                 long long ldw, long long ldc, int out_dtype, int bn, int split_k,
-                                 float* workspace, int* err, cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return CELLM_OK;
-    if (K <= 0 || (K & 7)) return CELLM_ERR_SIZE;
-    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((lda * 2) & 15) || ((ldw * 2) & 15)) return CELLM_ERR_ALIGN;
-    if (out_dtype != CELLM_F32 && out_dtype != CELLM_BF16) return CELLM_ERR_DTYPE;
-    const bool swap = bn < 0;
-    const int narrow = swap ? -bn : bn;
-    if (swap ? (narrow != 16 && narrow != 32 && narrow != 64) : (narrow != 64 && narrow != 128 && narrow != 256))
-        return CELLM_ERR_SIZE;
+// Most tiles a product may have when K is split (one counter each).
+#define GEMM_MAX_COUNTERS 65536
+
+// How a call with these sizes uses scratch memory: *ws_floats of float workspace
+// (0: none) and whether the tile counters are needed. epilogue: 0 plain, 1 SwiGLU.
+CELLM_API int cellm_gemm_tcgen05_plan(int M, int N, int K, int bn, int split_k, int epilogue, long long* ws_floats,
+                                      int* effective_split) {
     const int kblocks = (K + BK - 1) / BK;
     if (split_k < 1) split_k = 1;
     if (split_k > kblocks) split_k = kblocks;
     const int per = (kblocks + split_k - 1) / split_k;
     split_k = (kblocks + per - 1) / per;        // no empty slice
-    if (split_k > 1 && workspace == nullptr) return CELLM_ERR_ARG;
+    *effective_split = split_k;
+    const bool through_ws = split_k > 1 || (epilogue == 1 && bn < 0);
+    *ws_floats = through_ws ? (long long)split_k * M * N : 0;
+    return CELLM_OK;
+}
+
+// A: [M, K] bf16 (row pitch lda elements), W: [N, K] bf16 (pitch ldw). epilogue 0:
+// C: [M, N] of out_dtype (pitch ldc). epilogue 1 (SwiGLU): W is laid out in blocks
+// of 64 gate rows followed by their 64 up rows (N a multiple of 128) and C is
+// [M, N/2]. bn > 0: plain tiles of 128 rows of A by bn (64, 128, 256) rows of W;
+// bn < 0: swapped tiles of 128 rows of W by -bn (16, 32, 64) rows of A.
+// w_is_static: W is a weight that no kernel on the stream writes, so its loads may
+// start before the preceding kernel has finished.
+// workspace: as many floats as cellm_gemm_tcgen05_plan says; counters: GEMM_MAX_COUNTERS
+// zeroed ints that products on one stream may share (each product leaves them zero).
+CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
+                                 long long ldw, long long ldc, int out_dtype, int bn, int split_k, int epilogue,
+                                 int w_is_static, float* workspace, int* counters, int* err, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return CELLM_OK;
+    if (K <= 0 || (K & 7)) return CELLM_ERR_SIZE;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((lda * 2) & 15) || ((ldw * 2) & 15)) return CELLM_ERR_ALIGN;
+    if (out_dtype != CELLM_F32 && out_dtype != CELLM_BF16) return CELLM_ERR_DTYPE;
+    if (epilogue != 0 && epilogue != 1) return CELLM_ERR_ARG;
+    const bool swap = bn < 0;
+    const int narrow = swap ? -bn : bn;
+    if (swap ? (narrow != 16 && narrow != 32 && narrow != 64) : (narrow != 64 && narrow != 128 && narrow != 256))
+        return CELLM_ERR_SIZE;
+    if (epilogue == 1 && ((N & 127) || (!swap && narrow < 128))) return CELLM_ERR_SIZE;
+    long long ws_floats;
+    int split;
+    cellm_gemm_tcgen05_plan(M, N, K, bn, split_k, epilogue, &ws_floats, &split);
+    const int kblocks = (K + BK - 1) / BK;
+    const int per = (kblocks + split - 1) / split;
+    if (ws_floats > 0 && workspace == nullptr) return CELLM_ERR_ARG;
+    if (split > 1) {
+        if (counters == nullptr) return CELLM_ERR_ARG;
+        const long long tiles = swap ? (long long)((N + BM - 1) / BM) * ((M + narrow - 1) / narrow)
+                                     : (long long)((N + narrow - 1) / narrow) * ((M + BM - 1) / BM);
+        if (tiles > GEMM_MAX_COUNTERS) return CELLM_ERR_SIZE;
+    }
     CUtensorMap map_a, map_w;
     if (!tensor_map(&map_a, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, swap ? (uint32_t)narrow : (uint32_t)BM)) return CELLM_ERR_ARG;
     if (!tensor_map(&map_w, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, swap ? (uint32_t)BM : (uint32_t)narrow)) return CELLM_ERR_ARG;
     const CUtensorMap& m_rows = swap ? map_w : map_a;
     const CUtensorMap& m_cols = swap ? map_a : map_w;
-    int rc;
-#define GO(BN_, ST_, SW_)                                                                                          \
-    do {                                                                                                           \
-        if (split_k > 1) rc = launch<BN_, ST_, SW_, float>(m_rows, m_cols, workspace, M, N, K, (long long)N, split_k, per, err, stream); \
-        else if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, float>(m_rows, m_cols, (float*)C, M, N, K, ldc, 1, per, err, stream); \
-        else rc = launch<BN_, ST_, SW_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, M, N, K, ldc, 1, per, err, stream); \
+    int rc = CELLM_ERR_SIZE;
+#define GO2(BN_, ST_, SW_, EP_)                                                                                       \
+    do {                                                                                                              \
+        if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, EP_, float>(m_rows, m_cols, (float*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
+        else rc = launch<BN_, ST_, SW_, EP_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
+    } while (0)
+#define GO(BN_, ST_, SW_)                           \
+    do {                                            \
+        if (epilogue == 0) GO2(BN_, ST_, SW_, 0);   \
+        else GO2(BN_, ST_, SW_, 1);                 \
     } while (0)
     if (swap) {
         if (narrow == 16) GO(16, 5, true);
         else if (narrow == 32) GO(32, 5, true);
         else GO(64, 4, true);
     } else {
-        if (narrow == 64) GO(64, 8, false);
+        if (narrow == 64) GO2(64, 8, false, 0);
         else if (narrow == 128) GO(128, 6, false);
         else GO(256, 4, false);
     }
 #undef GO
-    if (rc != CELLM_OK) return rc;
-    if (split_k > 1) {
-        const size_t total = (size_t)M * N;
-        const unsigned blocks = (unsigned)((total + 255) / 256);
-        if (out_dtype == CELLM_F32)
-            splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>((float*)C, workspace, M, N, ldc, split_k);
-        else
-            splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)C, workspace, M, N, ldc, split_k);
-        CELLM_LAUNCH_CHECK();
-    }
-    return CELLM_OK;
+#undef GO2
+    return rc;
 }

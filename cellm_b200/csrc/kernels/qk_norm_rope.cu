@@ -27,6 +27,8 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
     float* sn = smem + rot / 2;          // [rot/2] sin
     const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* buf = smem + rot + warp * hd; // one head per warp
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     for (int p = threadIdx.x; p < rot / 2; p += blockDim.x) {
@@ -102,7 +104,7 @@ CELLM_API int cellm_qk_norm_rope(void* q_out, const void* qkv, long long row_str
     const size_t smem = (size_t)(rot + (threads / 32) * hd) * sizeof(float);
     if (smem > 48 * 1024) return CELLM_ERR_SIZE;
 #define LAUNCH(TA, TW)                                                                               \
-    qk_norm_rope_kernel<TA, TW><<<T, threads, smem, stream>>>(                                       \
+    CELLM_RUN((qk_norm_rope_kernel<TA, TW>), T, threads, smem, stream,                               \
         (TA*)q_out, (const TA*)qkv, row_stride, (const TW*)q_w, (const TW*)k_w, eps, positions,      \
         seq_of_token, block_table, bt_stride, (TA*)k_pool, (TA*)v_pool, num_pages, page_size, nh,    \
         nkv, hd, rot, interleaved, inv_freq, err)
@@ -112,6 +114,5 @@ CELLM_API int cellm_qk_norm_rope(void* q_out, const void* qkv, long long row_str
     else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else return CELLM_ERR_DTYPE;
 #undef LAUNCH
-    CELLM_LAUNCH_CHECK();
     return CELLM_OK;
 }

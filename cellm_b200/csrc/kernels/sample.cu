@@ -11,6 +11,8 @@
 __global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int V) {
     __shared__ float bv[32];
     __shared__ int bi[32];
+    pdl_trigger();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * V;
     float best = -INFINITY;
     int idx = 0x7fffffff;
@@ -42,8 +44,7 @@ __global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ l
 
 CELLM_API int cellm_argmax(int* out, const float* logits, int R, int V, cudaStream_t stream) {
     if (R <= 0) return CELLM_OK;
-    argmax_kernel<<<R, 512, 0, stream>>>(out, logits, V);
-    CELLM_LAUNCH_CHECK();
+    CELLM_RUN(argmax_kernel, R, 512, 0, stream, out, logits, V);
     return CELLM_OK;
 }
 
@@ -133,6 +134,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
     __shared__ int s_recent[256];
     __shared__ uint32_t s_prefix, s_mask;
     __shared__ int s_krem, s_cnt, s_pick;
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * V;
     const float temp = temperature[r];
@@ -309,7 +312,6 @@ CELLM_API int cellm_sample(int* out, const float* logits, int R, int V, const fl
                            int W, int max_top_k, cudaStream_t stream) {
     if (R <= 0) return CELLM_OK;
     if (max_top_k > SAMPLE_MAX_K || W > 256 || W < 0) return CELLM_ERR_SIZE;
-    sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(out, logits, V, temperature, top_k, u, penalty, recent, W);
-    CELLM_LAUNCH_CHECK();
+    CELLM_RUN(sample_kernel, R, SAMPLE_THREADS, 0, stream, out, logits, V, temperature, top_k, u, penalty, recent, W);
     return CELLM_OK;
 }

@@ -24,6 +24,8 @@ __global__ void short_conv_fwd_kernel(TA* __restrict__ y, const TA* __restrict__
                                       const int* __restrict__ slot_ids, const int* __restrict__ seq_of_token,
                                       const int* __restrict__ cu_seqlens, int H, int taps, int n_slots,
                                       int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= H) return;
@@ -55,6 +57,8 @@ template <typename TA>
 __global__ void short_conv_state_kernel(const TA* __restrict__ bcx, float* __restrict__ state,
                                         long long slot_stride, const int* __restrict__ slot_ids,
                                         const int* __restrict__ cu_seqlens, int H, int taps, int n_slots) {
+    pdl_trigger();
+    pdl_wait();
     const int b = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= H) return;
@@ -91,12 +95,12 @@ CELLM_API int cellm_short_conv(void* y, const void* bcx, const void* w, const vo
     dim3 grid_s((unsigned)B, (unsigned)((H + threads - 1) / threads));
 #define LAUNCH(TA, TW)                                                                              \
     do {                                                                                            \
-        short_conv_fwd_kernel<TA, TW><<<grid_f, threads, 0, stream>>>(                              \
-            (TA*)y, (const TA*)bcx, (const TW*)w, (const TW*)bias, state, slot_stride, slot_ids,    \
-            seq_of_token, cu_seqlens, H, taps, n_slots, err);                                       \
+        CELLM_RUN((short_conv_fwd_kernel<TA, TW>), grid_f, threads, 0, stream,                      \
+                  (TA*)y, (const TA*)bcx, (const TW*)w, (const TW*)bias, (const float*)state, slot_stride, slot_ids, \
+                  seq_of_token, cu_seqlens, H, taps, n_slots, err);                                 \
         if (taps > 1)                                                                               \
-            short_conv_state_kernel<TA><<<grid_s, threads, 0, stream>>>(                            \
-                (const TA*)bcx, state, slot_stride, slot_ids, cu_seqlens, H, taps, n_slots);        \
+            CELLM_RUN(short_conv_state_kernel<TA>, grid_s, threads, 0, stream,                      \
+                      (const TA*)bcx, state, slot_stride, slot_ids, cu_seqlens, H, taps, n_slots);  \
     } while (0)
     if (act_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float);
     else if (act_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16);
@@ -104,6 +108,5 @@ CELLM_API int cellm_short_conv(void* y, const void* bcx, const void* w, const vo
     else if (act_dtype == CELLM_BF16 && w_dtype == CELLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else return CELLM_ERR_DTYPE;
 #undef LAUNCH
-    CELLM_LAUNCH_CHECK();
     return CELLM_OK;
 }

@@ -5,6 +5,8 @@
 
 template <typename T>
 __global__ void swiglu_kernel(T* __restrict__ h, const T* __restrict__ gu, int ff, size_t n) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const size_t t = i / ff;
@@ -20,10 +22,9 @@ CELLM_API int cellm_swiglu(void* h, const void* gu, int T, int ff, int dtype, cu
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     if (dtype == CELLM_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((float*)h, (const float*)gu, ff, n);
+        CELLM_RUN(swiglu_kernel<float>, blocks, threads, 0, stream, (float*)h, (const float*)gu, ff, n);
     else if (dtype == CELLM_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)h, (const __nv_bfloat16*)gu, ff, n);
+        CELLM_RUN(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)h, (const __nv_bfloat16*)gu, ff, n);
     else return CELLM_ERR_DTYPE;
-    CELLM_LAUNCH_CHECK();
     return CELLM_OK;
 }

@@ -4,6 +4,7 @@ from .basic import (embed, add_rmsnorm, residual_add, swiglu, short_conv, qk_nor
                     attention_plain, argmax, sample)
 from .gemm import gemm, gemm_plain
 from .attention import attention
+from .gemm_bf16 import gemm_swiglu_bf16, tensor_core_ok
 
 __all__ = ["embed", "add_rmsnorm", "residual_add", "swiglu", "short_conv", "qk_norm_rope",
-           "attention_plain", "argmax", "sample", "gemm", "gemm_plain", "attention"]
+           "attention_plain", "argmax", "sample", "gemm", "gemm_plain", "attention", "gemm_swiglu_bf16", "tensor_core_ok"]

@@ -20,11 +20,12 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None =
     return c
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+         w_is_static: bool = False) -> torch.Tensor:
     """The product a . w^T by the kernel that serves the operands' element type:
     32-bit operands run the plain 32-bit kernel; bfloat16 operands run the
     tensor-core kernels."""
     if a.dtype == torch.float32:
         return gemm_plain(a, w, out_dtype)
     from .gemm_bf16 import gemm_bf16
-    return gemm_bf16(a, w, out_dtype)
+    return gemm_bf16(a, w, out_dtype, w_is_static)

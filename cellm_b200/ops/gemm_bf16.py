@@ -4,12 +4,14 @@ from __future__ import annotations
 
 import torch
 
-from ._lib import LAUNCHES, check, fn, ptr, stream_of, tag
+from ._lib import check, fn, ptr, stream_of, tag
 from .gemm import gemm_plain
 
 _SM_COUNT: dict[int, int] = {}
 _WORKSPACE: dict[torch.device, torch.Tensor] = {}
+_COUNTERS: dict[torch.device, torch.Tensor] = {}
 _ERR: dict[torch.device, torch.Tensor] = {}
+MAX_COUNTERS = 65536
 
 
 def _sms(device) -> int:
@@ -30,8 +32,19 @@ def _workspace(device, n_floats: int) -> torch.Tensor:
     return ws
 
 
+def _counters(device) -> torch.Tensor:
+    """Tile counters of split products: zero between products, shared by all
+    products of one stream (each leaves them zero), never reallocated."""
+    c = _COUNTERS.get(device)
+    if c is None:
+        c = torch.zeros(MAX_COUNTERS, dtype=torch.int32, device=device)
+        _COUNTERS[device] = c
+    return c
+
+
 def error_word(device) -> torch.Tensor:
-    """The device error word the tensor-core kernels report a timed-out wait in."""
+    """The device error word the kernels report a bad index or a timed-out wait in."""
+    device = torch.device(device)
     e = _ERR.get(device)
     if e is None:
         e = torch.zeros(1, dtype=torch.int32, device=device)
@@ -46,8 +59,9 @@ def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
     if M <= 64:
         narrow = 16 if M <= 16 else (32 if M <= 32 else 64)
         tiles = (N + 127) // 128
-        # enough CTAs to keep two per SM streaming, but at least four K blocks each
-        split = max(1, min((2 * sms + tiles - 1) // tiles, kblocks // 4))
+        # about one CTA per SM (its stage ring alone keeps ~90 KB of loads in flight), at
+        # least four K blocks each; few splits keep the final sum of the pieces short
+        split = max(1, min(sms // tiles, kblocks // 4))
         return -narrow, split
     bn = 256 if N >= 256 else (128 if N > 64 else 64)
     tiles = ((N + bn - 1) // bn) * ((M + 127) // 128)
@@ -57,29 +71,57 @@ def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
     return bn, split
 
 
+def _effective_split(K: int, split_k: int) -> int:
+    kblocks = (K + 63) // 64
+    split_k = max(1, min(split_k, kblocks))
+    per = (kblocks + split_k - 1) // split_k
+    return (kblocks + per - 1) // per
+
+
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bn: int, split_k: int,
-                 err: torch.Tensor | None = None) -> torch.Tensor:
+                 err: torch.Tensor | None = None, epilogue: int = 0, w_is_static: bool = False) -> torch.Tensor:
+    """The tensor-core kernel with a given tile shape and split. epilogue 1: `w`
+    holds blocks of 64 gate rows followed by their 64 up rows and the result is
+    silu(gate) * up, [M, N/2]."""
     M, K = a.shape
     N = w.shape[0]
-    c = torch.empty((M, N), dtype=out_dtype, device=a.device)
-    ws = _workspace(a.device, split_k * M * N) if split_k > 1 else None
+    c = torch.empty((M, N // 2 if epilogue else N), dtype=out_dtype, device=a.device)
+    split = _effective_split(K, split_k)
+    through_ws = split > 1 or (epilogue == 1 and bn < 0)
+    ws = _workspace(a.device, split * M * N) if through_ws else None
+    counters = _counters(a.device) if split > 1 else None
     err = err if err is not None else error_word(a.device)
     check(fn("gemm_tcgen05", "cellm_gemm_tcgen05")(
         ptr(c), ptr(a), ptr(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), tag(out_dtype), int(bn),
-        int(split_k), ptr(ws), ptr(err), stream_of(a)), "gemm_tcgen05")
-    if split_k > 1:
-        LAUNCHES[0] += 1
+        int(split_k), int(epilogue), 1 if w_is_static else 0, ptr(ws), ptr(counters), ptr(err), stream_of(a)),
+        "gemm_tcgen05")
     return c
 
 
-def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def tensor_core_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    K = a.shape[1]
+    return not ((K % 8) or a.stride(1) != 1 or w.stride(1) != 1 or (a.stride(0) % 8) or (w.stride(0) % 8)
+                or (a.data_ptr() % 16) or (w.data_ptr() % 16))
+
+
+def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+              w_is_static: bool = False) -> torch.Tensor:
     """a [M, K] . w [N, K]^T for bfloat16 operands, 32-bit accumulation, output
     bfloat16 or float32. Sizes the tensor-core kernel does not take (K not a
-    multiple of 8, unaligned rows) go to the plain kernel."""
+    multiple of 8, unaligned rows) go to the plain kernel. `w_is_static`: w is a
+    weight that nothing on the stream writes (its loads may then start early)."""
     out_dtype = out_dtype or a.dtype
-    M, K = a.shape
-    if (K % 8) or a.stride(1) != 1 or w.stride(1) != 1 or (a.stride(0) % 8) or (w.stride(0) % 8) \
-            or (a.data_ptr() % 16) or (w.data_ptr() % 16):
+    if not tensor_core_ok(a, w):
         return gemm_plain(a, w, out_dtype)
-    bn, split = plan_tiles(M, w.shape[0], K, _sms(a.device))
-    return gemm_tcgen05(a, w, out_dtype, bn, split)
+    bn, split = plan_tiles(a.shape[0], w.shape[0], a.shape[1], _sms(a.device))
+    return gemm_tcgen05(a, w, out_dtype, bn, split, w_is_static=w_is_static)
+
+
+def gemm_swiglu_bf16(a: torch.Tensor, w_blocked: torch.Tensor, w_is_static: bool = False) -> torch.Tensor:
+    """silu(a . w1^T) * (a . w3^T) in one kernel; `w_blocked` is w1 and w3 cut into
+    blocks of 64 rows and laid out gate block, up block, gate block, ...; the
+    caller has checked `tensor_core_ok` and that the width is a multiple of 64."""
+    bn, split = plan_tiles(a.shape[0], w_blocked.shape[0], a.shape[1], _sms(a.device))
+    if bn == 64:
+        bn = 128
+    return gemm_tcgen05(a, w_blocked, a.dtype, bn, split, epilogue=1, w_is_static=w_is_static)

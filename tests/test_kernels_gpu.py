@@ -308,6 +308,22 @@ def test_gemm_tcgen05(out, M, N, K, bn, split):
     assert float((c.double() - ref).abs().max()) <= k * (1 + float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("M,ff,K,bn,split", [(8, 192, 64, -16, 1), (3, 128, 2048, -16, 4), (40, 320, 96, -64, 1), (64, 64, 512, -64, 2),
+                                              (130, 192, 64, 128, 1), (300, 256, 1024, 256, 1), (70, 128, 4096, 128, 4), (200, 384, 2048, 256, 2)])
+def test_gemm_tcgen05_swiglu_epilogue(M, ff, K, bn, split):
+    from cellm_b200.ops.gemm_bf16 import error_word, gemm_tcgen05
+    a = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w1 = (torch.randn(ff, K, device=DEV) * K ** -0.5).bfloat16()
+    w3 = (torch.randn(ff, K, device=DEV) * K ** -0.5).bfloat16()
+    blocked = torch.stack([w1.reshape(ff // 64, 64, K), w3.reshape(ff // 64, 64, K)], dim=1).reshape(2 * ff, K).contiguous()
+    h = gemm_tcgen05(a, blocked, torch.bfloat16, bn, split, epilogue=1)
+    torch.cuda.synchronize()
+    assert error_word(a.device).item() == 0 and tuple(h.shape) == (M, ff)
+    g, u = a.double() @ w1.double().T, a.double() @ w3.double().T
+    ref = g * torch.sigmoid(g) * u
+    assert float((h.double() - ref).abs().max()) <= 6e-3 * (1 + float(ref.abs().max()))
+
+
 def test_gemm_dispatch_covers_every_size():
     from cellm_b200 import ops
     for M, N, K in ((3, 50, 20), (3, 50, 24), (200, 333, 40), (64, 2048, 2048), (65, 64, 64)):
