@@ -39,12 +39,78 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
     }
 }
 
+// The same for rows of bfloat16 activations whose length is a multiple of 8 and at
+// most 8 * 1024: every thread keeps its 8 values in registers, so each element is
+// read once and written once, in 16-byte pieces. The sum over a row is taken in
+// the same order whatever the batch (thread partials of 8, then the block tree).
+template <typename TW>
+__global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                                        const TW* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                        const int* __restrict__ rows, int H, float eps) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    const int i0 = threadIdx.x * 8;
+    const bool on = i0 < H;
+    const bool write_back = (rows == nullptr) && (delta != nullptr);
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    if (on) {
+        const float4 a = *reinterpret_cast<const float4*>(x + (size_t)t * H + i0);
+        const float4 b = *reinterpret_cast<const float4*>(x + (size_t)t * H + i0 + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        if (delta) {
+            const uint4 d = *reinterpret_cast<const uint4*>(delta + (size_t)t * H + i0);
+            const __nv_bfloat162* dp = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(dp[j]);
+                v[2 * j] += f.x;
+                v[2 * j + 1] += f.y;
+            }
+        }
+        if (write_back) {
+            *reinterpret_cast<float4*>(x + (size_t)t * H + i0) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(x + (size_t)t * H + i0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    if (on) {
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 pk = __floats2bfloat162_rn(v[2 * j] * inv * to_float(w[i0 + 2 * j]),
+                                                      v[2 * j + 1] * inv * to_float(w[i0 + 2 * j + 1]));
+            o[j] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+        *reinterpret_cast<uint4*>(y + (size_t)r * H + i0) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 // x: [*, H] float; delta: [*, H] act dtype or null; w: [H]; y: [n_rows, H] act dtype;
 // rows: null (all n_rows rows, x updated in place) or n_rows row indices (x left as is).
 CELLM_API int cellm_add_rmsnorm(float* x, const void* delta, const void* w, int w_dtype, void* y,
                                 const int* rows, int n_rows, int H, float eps, int act_dtype,
                                 cudaStream_t stream) {
     if (n_rows <= 0) return CELLM_OK;
+    if (act_dtype == CELLM_BF16 && (H & 7) == 0 && H <= 8192 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)y) & 15) == 0) {
+        const int vthreads = ((H / 8 + 31) / 32) * 32;
+        if (w_dtype == CELLM_BF16)
+            CELLM_RUN(add_rmsnorm_vec8_kernel<__nv_bfloat16>, n_rows, vthreads, 0, stream, x, (const __nv_bfloat16*)delta,
+                      (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rows, H, eps);
+        else if (w_dtype == CELLM_F32)
+            CELLM_RUN(add_rmsnorm_vec8_kernel<float>, n_rows, vthreads, 0, stream, x, (const __nv_bfloat16*)delta,
+                      (const float*)w, (__nv_bfloat16*)y, rows, H, eps);
+        else return CELLM_ERR_DTYPE;
+        return CELLM_OK;
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
 #define LAUNCH(TA, TW) \
     CELLM_RUN((add_rmsnorm_kernel<TA, TW>), n_rows, threads, 0, stream, x, (const TA*)delta, (const TW*)w, (TA*)y, rows, H, eps)

@@ -7,9 +7,11 @@
 // pos * theta^(-2i/rot) (crates/cellm-kernels/src/cpu_kernels.rs:264-277; the
 // interleaved pairing (2i, 2i+1) of :279-292 is the other layout), and writes
 // k and v for the token's position (crates/cellm-model/src/lfm.rs:563-566).
-// Values are not normalised. Angles are formed in 64-bit from a table of
-// inverse frequencies the host computed in 64-bit, then cos/sin are rounded to
-// 32-bit, so they carry no error that grows with the position.
+// Values are not normalised. The host computes the inverse frequencies in 64-bit
+// and passes each as a pair of floats (high part, remainder); the angle
+// pos * inv_freq is formed as a float plus its exact rounding error, and that
+// error enters cos/sin through the first terms of the addition formulas, so the
+// rotation carries no error that grows with the position.
 //
 // Cache layout of one layer: [page][kv_head][slot in page][head_dim].
 #include "common.cuh"
@@ -21,7 +23,7 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
                                     const int* __restrict__ block_table, int bt_stride,
                                     TA* __restrict__ k_pool, TA* __restrict__ v_pool, int num_pages,
                                     int page_size, int nh, int nkv, int hd, int rot, int interleaved,
-                                    const double* __restrict__ inv_freq, int* __restrict__ err) {
+                                    const float* __restrict__ inv_freq, int* __restrict__ err) {
     extern __shared__ float smem[];
     float* cs = smem;                    // [rot/2] cos
     float* sn = smem + rot / 2;          // [rot/2] sin
@@ -32,10 +34,14 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
     const int t = blockIdx.x;
     const int pos = positions[t];
     for (int p = threadIdx.x; p < rot / 2; p += blockDim.x) {
-        double s, c;
-        sincos((double)pos * inv_freq[p], &s, &c);
-        cs[p] = (float)c;
-        sn[p] = (float)s;
+        const float hi = inv_freq[2 * p], lo = inv_freq[2 * p + 1], fp = (float)pos;
+        const float a = fp * hi;                              // angle, rounded
+        const float e = fmaf(fp, hi, -a) + fp * lo;           // what the rounding dropped, plus the remainder's share
+        float s, c;
+        sincosf(a, &s, &c);
+        const float h = 1.0f - 0.5f * e * e;
+        cs[p] = c * h - s * e;                                // cos(a + e)
+        sn[p] = s * h + c * e;                                // sin(a + e)
     }
     long long page_base = -1;
     if (nkv > 0) {
@@ -90,12 +96,13 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
 
 // qkv: [T, row_stride] rows holding nh query heads, then nkv key heads, then nkv
 // value heads (nkv = 0: queries only, nothing is written to the cache).
-// q_w, k_w: [hd] norm weights or null (no norm). inv_freq: [rot/2] doubles.
+// q_w, k_w: [hd] norm weights or null (no norm). inv_freq: [rot/2] pairs of floats
+// (high part, remainder) of the 64-bit inverse frequencies.
 CELLM_API int cellm_qk_norm_rope(void* q_out, const void* qkv, long long row_stride, const void* q_w,
                                  const void* k_w, int w_dtype, float eps, const int* positions,
                                  const int* seq_of_token, const int* block_table, int bt_stride,
                                  void* k_pool, void* v_pool, int num_pages, int page_size, int T, int nh,
-                                 int nkv, int hd, int rot, int interleaved, const double* inv_freq,
+                                 int nkv, int hd, int rot, int interleaved, const float* inv_freq,
                                  int act_dtype, int* err, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
     if (rot < 0 || rot > hd || (rot & 1)) return CELLM_ERR_SIZE;

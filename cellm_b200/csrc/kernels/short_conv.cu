@@ -82,12 +82,52 @@ __global__ void short_conv_state_kernel(const TA* __restrict__ bcx, float* __res
     }
 }
 
+// Short portions (decoding: one token per request): one thread owns a channel of
+// a request, walks the portion's tokens with the history in registers and writes
+// the new state itself, so one launch does what the two kernels above do.
+template <typename TA, typename TW>
+__global__ void short_conv_walk_kernel(TA* __restrict__ y, const TA* __restrict__ bcx, const TW* __restrict__ w,
+                                       const TW* __restrict__ bias, float* __restrict__ state, long long slot_stride,
+                                       const int* __restrict__ slot_ids, const int* __restrict__ cu_seqlens, int H,
+                                       int taps, int n_slots, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= H) return;
+    const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+    const int slot = slot_ids[b];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_SLOT);
+        return;
+    }
+    float* st = state + (long long)slot * slot_stride;
+    const int rows = taps - 1;
+    float hist[SHORT_CONV_MAX_TAPS], wt[SHORT_CONV_MAX_TAPS];
+    for (int r = 0; r < rows; ++r) hist[r] = st[(size_t)r * H + c];
+    for (int k = 0; k < taps; ++k) wt[k] = to_float(w[(size_t)c * taps + k]);
+    const float bs = bias ? to_float(bias[c]) : 0.f;
+    for (int i = 0; i < n; ++i) {
+        const TA* row = bcx + (size_t)(start + i) * 3 * H;
+        const float bx = to_float(row[c]) * to_float(row[2 * H + c]);
+        float acc = 0.f;
+        for (int k = 0; k < rows; ++k) acc += hist[k] * wt[k];
+        acc += bx * wt[rows];
+        if (bias) acc += bs;
+        y[(size_t)(start + i) * H + c] = from_float<TA>(to_float(row[H + c]) * acc);
+        for (int k = 0; k + 1 < rows; ++k) hist[k] = hist[k + 1];
+        if (rows > 0) hist[rows - 1] = bx;
+    }
+    for (int r = 0; r < rows; ++r) st[(size_t)r * H + c] = hist[r];
+}
+
 // y: [T, H]; bcx: [T, 3H]; w: [H, taps]; bias: [H] or null; state: this layer's
-// [n_slots][taps-1][H] floats with slot_stride floats between slots.
+// [n_slots][taps-1][H] floats with slot_stride floats between slots. max_q_len: the
+// longest portion of the batch (portions of up to 4 tokens take the one-launch walk).
 CELLM_API int cellm_short_conv(void* y, const void* bcx, const void* w, const void* bias, int w_dtype,
                                float* state, long long slot_stride, const int* slot_ids,
                                const int* seq_of_token, const int* cu_seqlens, int T, int B, int H,
-                               int taps, int n_slots, int act_dtype, int* err, cudaStream_t stream) {
+                               int taps, int n_slots, int max_q_len, int act_dtype, int* err, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
     if (taps < 1 || taps > SHORT_CONV_MAX_TAPS) return CELLM_ERR_SIZE;
     const int threads = 128;
@@ -95,6 +135,11 @@ CELLM_API int cellm_short_conv(void* y, const void* bcx, const void* w, const vo
     dim3 grid_s((unsigned)B, (unsigned)((H + threads - 1) / threads));
 #define LAUNCH(TA, TW)                                                                              \
     do {                                                                                            \
+        if (max_q_len > 0 && max_q_len <= 4) {                                                      \
+            CELLM_RUN((short_conv_walk_kernel<TA, TW>), grid_s, threads, 0, stream, (TA*)y, (const TA*)bcx, \
+                      (const TW*)w, (const TW*)bias, state, slot_stride, slot_ids, cu_seqlens, H, taps, n_slots, err); \
+            break;                                                                                  \
+        }                                                                                           \
         CELLM_RUN((short_conv_fwd_kernel<TA, TW>), grid_f, threads, 0, stream,                      \
                   (TA*)y, (const TA*)bcx, (const TW*)w, (const TW*)bias, (const float*)state, slot_stride, slot_ids, \
                   seq_of_token, cu_seqlens, H, taps, n_slots, err);                                 \

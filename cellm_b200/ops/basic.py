@@ -4,7 +4,7 @@ from typing import Optional
 
 import torch
 
-from ._lib import check, fn, ptr, require_cuda, stream_of, tag
+from ._lib import check, count_launch, fn, ptr, require_cuda, stream_of, tag
 
 _LIB = "kernels_common"
 
@@ -54,9 +54,11 @@ def swiglu(gu: torch.Tensor) -> torch.Tensor:
 
 def short_conv(bcx: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
                slot_ids: torch.Tensor, seq_of_token: torch.Tensor, cu_seqlens: torch.Tensor,
-               err: torch.Tensor) -> torch.Tensor:
+               err: torch.Tensor, max_q_len: int = 0) -> torch.Tensor:
     """bcx [T, 3H]; w [H, taps]; bias [H] or None; state [slots, taps-1, H] float32
-    (read, then updated in place). Returns y [T, H]."""
+    (read, then updated in place). Returns y [T, H]. `max_q_len`: the longest
+    portion of the batch if the host knows it (0: unknown); short portions run a
+    single fused kernel."""
     require_cuda(bcx, w, bias, state, slot_ids, seq_of_token, cu_seqlens, err)
     T, H3 = bcx.shape
     H, taps = w.shape
@@ -68,8 +70,10 @@ def short_conv(bcx: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     B = cu_seqlens.numel() - 1
     check(fn(_LIB, "cellm_short_conv")(ptr(y), ptr(bcx), ptr(w), ptr(bias), tag(w), ptr(state),
                                        state.stride(0), ptr(slot_ids), ptr(seq_of_token), ptr(cu_seqlens),
-                                       T, B, H, taps, state.shape[0], tag(bcx), ptr(err), stream_of(bcx)),
-          "short_conv")
+                                       T, B, H, taps, state.shape[0], int(max_q_len), tag(bcx), ptr(err),
+                                       stream_of(bcx)), "short_conv")
+    if taps > 1 and not 0 < max_q_len <= 4:
+        count_launch()          # the state update is a launch of its own
     return y
 
 
@@ -87,8 +91,8 @@ def qk_norm_rope(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[t
     T = qkv.shape[0]
     if qkv.shape[1] != (nh + 2 * nkv) * hd:
         raise ValueError(f"qk_norm_rope: row of {qkv.shape[1]} values, expected {(nh + 2 * nkv) * hd}")
-    if rot > 0 and (inv_freq is None or inv_freq.dtype != torch.float64 or inv_freq.numel() != rot // 2):
-        raise ValueError("qk_norm_rope: inv_freq must be float64 with rot/2 values")
+    if rot > 0 and (inv_freq is None or inv_freq.dtype != torch.float32 or tuple(inv_freq.shape) != (rot // 2, 2)):
+        raise ValueError("qk_norm_rope: inv_freq must be float32 [rot/2, 2] (high part, remainder)")
     if nkv > 0 and (k_pool.dtype != qkv.dtype or tuple(k_pool.shape[1:]) != (nkv, page_size, hd) or k_pool.shape != v_pool.shape):
         raise ValueError(f"qk_norm_rope: pool {tuple(k_pool.shape)} {k_pool.dtype} does not fit [pages, {nkv}, {page_size}, {hd}] {qkv.dtype}")
     w_tag = tag(q_w) if q_w is not None else 0

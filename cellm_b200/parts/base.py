@@ -137,7 +137,7 @@ class Norm(Part):
 
 class Position(Part):
     def rotation(self):
-        """(rotary_dim, interleaved, inv_freq[rotary_dim/2] float64 device tensor) if the
+        """(rotary_dim, interleaved, inv_freq [rotary_dim/2, 2] float32 device tensor: high part, remainder) if the
         encoding is a rotation a fused kernel can apply, else None."""
         return None
 

@@ -46,7 +46,7 @@ class ShortConvMixer(Mixer):
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         bcx = self.in_proj(x)
         y = ops.short_conv(bcx, self.conv_w, self.conv_b, cache.state, ctx.slot_ids, ctx.seq_of_token,
-                           ctx.cu_seqlens, ctx.err)
+                           ctx.cu_seqlens, ctx.err, ctx.max_q_len)
         return self.out_proj(y)
 
 

@@ -75,8 +75,9 @@ def test_swiglu_and_residual_add(dtype):
 
 
 @pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("walk", [False, True])
 @pytest.mark.parametrize("taps,bias", [(1, False), (2, True), (3, False), (5, True)])
-def test_short_conv_portions_carry_the_state(dtype, taps, bias):
+def test_short_conv_portions_carry_the_state(dtype, taps, bias, walk):
     """Three requests fed in portions of 1, 2, 3 and 7 tokens, two of them in
     the same launch, against the whole-sequence convolution."""
     from cellm_b200 import ops
@@ -99,12 +100,13 @@ def test_short_conv_portions_carry_the_state(dtype, taps, bias):
     got = {r: [] for r in lens}
     e = err_word()
     schedule = [[(0, 1), (1, 2)], [(0, 2), (2, 3)], [(1, 7)], [(0, 3), (2, 1)], [(0, 7)]]
+    # walk: steps whose portions are all short take the one-launch kernel, as the engine would ask
     for step in schedule:
         rows = torch.cat([bcx[r][fed[r]:fed[r] + n] for r, n in step])
         cu = torch.tensor(np.cumsum([0] + [n for _, n in step]), dtype=torch.int32, device=DEV)
         seq = torch.cat([torch.full((n,), i) for i, (_, n) in enumerate(step)]).int().to(DEV)
         sl = torch.tensor([slot_of[r] for r, _ in step], dtype=torch.int32, device=DEV)
-        y = ops.short_conv(rows, w, b, state, sl, seq, cu, e)
+        y = ops.short_conv(rows, w, b, state, sl, seq, cu, e, max(n for _, n in step) if walk else 0)
         o = 0
         for r, n in step:
             got[r].append(y[o:o + n])
@@ -127,11 +129,13 @@ def test_qk_norm_rope_and_page_write(dtype, hd, rot, inter):
     qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).to(dtype)
     qw, kw = (torch.rand(hd, device=DEV) + 0.5).to(dtype), (torch.rand(hd, device=DEV) + 0.5).to(dtype)
     theta = 1e4
-    inv = (theta ** (-(2.0 * torch.arange(rot // 2, dtype=torch.float64)) / max(rot, 1))).to(DEV) if rot else None
+    from cellm_b200.parts.rope import split_inv_freq
+    inv = (theta ** (-(2.0 * torch.arange(rot // 2, dtype=torch.float64)) / max(rot, 1))) if rot else None
+    inv_dev = split_inv_freq(theta, rot).to(DEV) if rot else None
     kp = torch.zeros(pages, nkv, ps, hd, device=DEV, dtype=dtype)
     vp = torch.zeros_like(kp)
     e = err_word()
-    q = ops.qk_norm_rope(qkv, qw, kw, 1e-5, pos, seq, bt, kp, vp, ps, nh, nkv, hd, rot, inter, inv, e)
+    q = ops.qk_norm_rope(qkv, qw, kw, 1e-5, pos, seq, bt, kp, vp, ps, nh, nkv, hd, rot, inter, inv_dev, e)
     assert e.item() == 0
 
     def ref_heads(x, w, n):
@@ -139,7 +143,7 @@ def test_qk_norm_rope_and_page_write(dtype, hd, rot, inter):
         if rot:
             if inter:     # pairs (2i, 2i+1)  (crates/cellm-kernels/src/cpu_kernels.rs:279-292)
                 xr = x[..., :rot].reshape(T, n, rot // 2, 2)
-                ang = pos.double().cpu()[:, None] * inv.cpu()[None, :]
+                ang = pos.double().cpu()[:, None] * inv[None, :]
                 c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
                 r = torch.stack([xr[..., 0] * c - xr[..., 1] * s_, xr[..., 1] * c + xr[..., 0] * s_], -1).reshape(T, n, rot)
             else:
@@ -158,8 +162,23 @@ def test_qk_norm_rope_and_page_write(dtype, hd, rot, inter):
     assert float(kp.float().abs().sum(dim=(1, 3)).cpu()[~written].max()) == 0.0     # nothing else was touched
     bad = bt.clone()
     bad[2, 0] = pages
-    ops.qk_norm_rope(qkv, qw, kw, 1e-5, pos, seq, bad, kp, vp, ps, nh, nkv, hd, rot, inter, inv, e)
+    ops.qk_norm_rope(qkv, qw, kw, 1e-5, pos, seq, bad, kp, vp, ps, nh, nkv, hd, rot, inter, inv_dev, e)
     assert e.item() == 2
+
+
+def test_rotation_angles_stay_exact_far_out():
+    """At positions in the hundreds of thousands a float angle is off by whole
+    hundredths of a radian; the kernel's split arithmetic is not."""
+    from cellm_b200 import ops
+    from cellm_b200.parts.rope import split_inv_freq
+    hd, theta = 64, 1e6
+    pos = torch.tensor([0, 1, 4097, 131071, 500000, 1048575], dtype=torch.int32, device=DEV)
+    T = pos.numel()
+    q = torch.randn(T, hd, device=DEV)
+    out = ops.qk_norm_rope(q, None, None, 0.0, pos, torch.zeros(T, dtype=torch.int32, device=DEV), None, None, None, 16,
+                           1, 0, hd, hd, False, split_inv_freq(theta, hd).to(DEV), err_word())
+    ref = plain.rope_rotate_half(q.double().cpu().reshape(T, 1, hd), pos.cpu(), theta).reshape(T, hd)
+    assert float((out.double().cpu() - ref).abs().max()) < 3e-6 * float(q.abs().max())
 
 
 def paged_case(q_lens, ctx_lens, nh, nkv, hd, ps, dtype, seed=0, scale_one=None):

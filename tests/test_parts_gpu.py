@@ -120,8 +120,9 @@ def test_rope_part_describes_itself():
     from cellm_b200.parts.rope import RotaryEmbedding
     r = RotaryEmbedding({"head_dim": 32, "rotary_dim": 16, "theta": 100.0, "layout": "interleaved"}, DEV)
     rot, inter, inv = r.rotation()
-    assert rot == 16 and inter and inv.dtype == torch.float64
-    assert torch.allclose(inv.cpu(), 100.0 ** (-(2.0 * torch.arange(8, dtype=torch.float64)) / 16))
+    assert rot == 16 and inter and inv.dtype == torch.float32 and tuple(inv.shape) == (8, 2)
+    exact = 100.0 ** (-(2.0 * torch.arange(8, dtype=torch.float64)) / 16)
+    assert float((inv.cpu().double().sum(1) - exact).abs().max()) < 1e-15
     with pytest.raises(ConfigError):
         RotaryEmbedding({"head_dim": 32, "rotary_dim": 34, "theta": 100.0}, DEV)
 
