@@ -37,6 +37,7 @@ LIBRARIES: dict[str, tuple[str, list[str], list[str]]] = {
     "gemm_plain": ("nvcc", ["kernels/gemm_plain.cu"], []),
     "gemm_tcgen05": ("nvcc", ["kernels/gemm_tcgen05.cu"], []),
     "attention_flash": ("nvcc", ["kernels/attention_flash.cu"], []),
+    "attention_decode": ("nvcc", ["kernels/attention_decode.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -1,0 +1,298 @@
+// Attention for decoded tokens over the paged cache (bfloat16, tensor cores).
+//
+// One CTA serves one (request, key/value head, piece of the keys). The query
+// heads that share the key/value head are the rows of one 16-row tile (at most
+// 16 / group-size tokens per request, so a request's portion must be that
+// short). Each warp of the CTA walks its own share of the 64-key blocks
+// (block b goes to warp b mod NW) with a cp.async ring of its own, so no warp
+// waits for another while the keys stream in. The warps' partial results
+// (maximum, sum, unnormalised output) are combined through shared memory.
+//
+// When the keys of a request are split over several CTAs (gridDim.z > 1), each
+// CTA leaves its piece in the workspace and adds one to the counter of its
+// (request, key/value head); the CTA that finds the counter at gridDim.z - 1
+// combines the pieces in the order of the splits, writes the output and sets
+// the counter back to zero. No CTA waits for another, and no second kernel runs.
+//
+// Scores, mask and softmax are as in the flash kernel for prompts
+// (attention_flash.cu): q.k * scale, key <= the token's position, optional
+// window, 32-bit online softmax, probabilities rounded to bfloat16 for P.V.
+// Cache layout of one layer: [page][kv_head][slot in page][head_dim].
+#include "common.cuh"
+#include "mma_tiles.cuh"
+
+namespace {
+
+template <int HD, int NW>
+struct DecodeSmem {
+    static constexpr int KV_BYTES = FA_BN * HD * 2;
+    static constexpr size_t q_off = 0;
+    static constexpr size_t kv_off = 16 * HD * 2;                         // [NW][2 stages][K | V]
+    static constexpr size_t o_off = kv_off + (size_t)NW * 2 * 2 * KV_BYTES;   // [NW][16][HD] float
+    static constexpr size_t ml_off = o_off + (size_t)NW * 16 * HD * 4;    // [NW][16][2] float
+    static constexpr size_t flag_off = ml_off + (size_t)NW * 16 * 2 * 4;
+    static constexpr size_t total = flag_off + 16;
+};
+
+template <int HD, int NW>
+__global__ void __launch_bounds__(NW * 32)
+attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int* __restrict__ counters, const __nv_bfloat16* __restrict__ q,
+                        const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
+                        const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens,
+                        const int* __restrict__ block_table, int bt_stride, int T, int num_pages, int page_size,
+                        int nh, int nkv, float scale_log2e, int window, int* __restrict__ err) {
+    constexpr int BN = FA_BN, CH = HD / 8, NT = HD / 8;
+    using L = DecodeSmem<HD, NW>;
+    extern __shared__ __align__(128) uint8_t dec_smem[];
+    uint8_t* q_s = dec_smem + L::q_off;
+    float* o_s = reinterpret_cast<float*>(dec_smem + L::o_off);
+    float* ml_s = reinterpret_cast<float*>(dec_smem + L::ml_off);
+    int* flag_s = reinterpret_cast<int*>(dec_smem + L::flag_off);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* kv_s = dec_smem + L::kv_off + (size_t)warp * 4 * L::KV_BYTES;
+    const int G = nh / nkv;
+    const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+    pdl_trigger();
+    pdl_wait();
+    const int t_base = cu_seqlens[b], q_len = cu_seqlens[b + 1] - t_base, rows = q_len * G;   // rows <= 16
+    const int ctx = ctx_lens[b];
+    const int key_end = ctx + q_len;
+    const int key_begin = window > 0 ? max(0, ctx - window + 1) : 0;
+    const int kb_begin = key_begin / BN, kb_end = (key_end + BN - 1) / BN;
+    const int per = (kb_end - kb_begin + nsplit - 1) / nsplit;
+    const int my_begin = kb_begin + split * per, my_end = min(kb_end, my_begin + per);
+    const int* bt = block_table + (size_t)b * bt_stride;
+    const size_t page_elems = (size_t)nkv * page_size * HD;
+
+    for (int i = threadIdx.x; i < 16 * CH; i += NW * 32) {
+        const int row = i / CH, chunk = i % CH;
+        const bool ok = row < rows;
+        const __nv_bfloat16* src = q + (size_t)(t_base + (ok ? row / G : 0)) * nh * HD + (size_t)(kvh * G + (ok ? row % G : 0)) * HD + chunk * 8;
+        cp_async16(q_s + tile_offset<HD>(row, chunk), src, ok ? 16 : 0);
+    }
+    cp_async_commit();
+    auto load_kv = [&](int kb, int stage) {      // by this warp alone
+        uint8_t* ks = kv_s + (size_t)stage * 2 * L::KV_BYTES;
+        uint8_t* vs = ks + L::KV_BYTES;
+        for (int i = lane; i < BN * CH; i += 32) {
+            const int row = i / CH, chunk = i % CH, j = kb * BN + row;
+            int page = -1;
+            if (j >= key_begin && j < key_end) {
+                page = bt[j / page_size];
+                if (page < 0 || page >= num_pages) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
+            }
+            const size_t off = page >= 0 ? (size_t)page * page_elems + ((size_t)kvh * page_size + j % page_size) * HD + chunk * 8 : 0;
+            cp_async16(ks + tile_offset<HD>(row, chunk), k_pool + off, page >= 0 ? 16 : 0);
+            cp_async16(vs + tile_offset<HD>(row, chunk), v_pool + off, page >= 0 ? 16 : 0);
+        }
+    };
+    const int first = my_begin + warp;
+    if (first < my_end) load_kv(first, 0);
+    cp_async_commit();
+    cp_async_wait<1>();          // the Q tile (this thread's share)
+    __syncthreads();             // everybody's share
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldmatrix_x4(qf[ks], q_s + tile_offset<HD>(lane & 15, ks * 2 + (lane >> 4)));
+
+    const int row_a = lane >> 2, row_b = row_a + 8;
+    const int pos_a = row_a < rows ? ctx + row_a / G : -1, pos_b = row_b < rows ? ctx + row_b / G : -1;
+    const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+    for (int kb = first, it = 0; kb < my_end; kb += NW, ++it) {
+        const int stage = it & 1;
+        if (kb + NW < my_end) load_kv(kb + NW, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const uint8_t* ks_ = kv_s + (size_t)stage * 2 * L::KV_BYTES;
+        const uint8_t* vs_ = ks_ + L::KV_BYTES;
+        float s[BN / 8][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int n2 = 0; n2 < BN / 16; ++n2) {
+                uint32_t kf[4];
+                ldmatrix_x4(kf, ks_ + tile_offset<HD>(n2 * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+                mma_bf16(s[2 * n2], qf[ks], kf[0], kf[1]);
+                mma_bf16(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
+            }
+        }
+        const int j0 = kb * BN + (lane & 3) * 2;
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = j0 + n * 8 + e;
+                const float va = (j <= pos_a && j >= lo_a) ? s[n][e] * scale_log2e : -INFINITY;
+                const float vb = (j <= pos_b && j >= lo_b) ? s[n][2 + e] * scale_log2e : -INFINITY;
+                s[n][e] = va;
+                s[n][2 + e] = vb;
+                mx_a = fmaxf(mx_a, va);
+                mx_b = fmaxf(mx_b, vb);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float use_a = mn_a == -INFINITY ? 0.f : mn_a, use_b = mn_b == -INFINITY ? 0.f : mn_b;
+        const float corr_a = exp2f(m_a - use_a), corr_b = exp2f(m_b - use_b);
+        m_a = mn_a;
+        m_b = mn_b;
+        float sum_a = 0.f, sum_b = 0.f;
+        uint32_t pf[BN / 16][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+            const float p0 = exp2f(s[n][0] - use_a), p1 = exp2f(s[n][1] - use_a);
+            const float p2 = exp2f(s[n][2] - use_b), p3 = exp2f(s[n][3] - use_b);
+            sum_a += p0 + p1;
+            sum_b += p2 + p3;
+            pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+            pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        l_a = l_a * corr_a + sum_a;
+        l_b = l_b * corr_b + sum_b;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { o[n][0] *= corr_a; o[n][1] *= corr_a; o[n][2] *= corr_b; o[n][3] *= corr_b; }
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+            for (int n2 = 0; n2 < NT / 2; ++n2) {
+                uint32_t vf[4];
+                ldmatrix_x4_trans(vf, vs_ + tile_offset<HD>(kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), n2 * 2 + (lane >> 4)));
+                mma_bf16(o[2 * n2], pf[kk], vf[0], vf[1]);
+                mma_bf16(o[2 * n2 + 1], pf[kk], vf[2], vf[3]);
+            }
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+    // ---- the warps' results meet in shared memory
+    {
+        float* ow = o_s + (size_t)warp * 16 * HD;
+        const int col = (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            *reinterpret_cast<float2*>(ow + row_a * HD + n * 8 + col) = make_float2(o[n][0], o[n][1]);
+            *reinterpret_cast<float2*>(ow + row_b * HD + n * 8 + col) = make_float2(o[n][2], o[n][3]);
+        }
+        if ((lane & 3) == 0) {
+            ml_s[(warp * 16 + row_a) * 2] = m_a;
+            ml_s[(warp * 16 + row_a) * 2 + 1] = l_a;
+            ml_s[(warp * 16 + row_b) * 2] = m_b;
+            ml_s[(warp * 16 + row_b) * 2 + 1] = l_b;
+        }
+    }
+    __syncthreads();
+    const size_t n_rows = (size_t)T * nh;
+    // element e = (row, dim) of the 16 x HD tile, owned by thread e mod (NW*32)
+    for (int e = threadIdx.x; e < rows * HD; e += NW * 32) {
+        const int row = e / HD, d = e % HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) m = fmaxf(m, ml_s[(w * 16 + row) * 2]);
+        const float use = m == -INFINITY ? 0.f : m;
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float f = exp2f(ml_s[(w * 16 + row) * 2] - use);
+            l += f * ml_s[(w * 16 + row) * 2 + 1];
+            acc += f * o_s[((size_t)w * 16 + row) * HD + d];
+        }
+        const size_t gr = (size_t)(t_base + row / G) * nh + kvh * G + row % G;
+        if (nsplit == 1) {
+            out[gr * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            part_o[((size_t)split * n_rows + gr) * HD + d] = acc;
+            if (d == 0) { part_ml[((size_t)split * n_rows + gr) * 2] = m; part_ml[((size_t)split * n_rows + gr) * 2 + 1] = l; }
+        }
+    }
+    if (nsplit == 1) return;
+
+    // ---- the pieces of a split meet in the workspace; the last CTA combines them
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int idx = b * nkv + kvh;
+        const int old = atomicAdd(&counters[idx], 1);
+        *flag_s = (old == nsplit - 1) ? 1 : 0;
+        if (old == nsplit - 1) counters[idx] = 0;
+    }
+    __syncthreads();
+    if (*flag_s == 0) return;
+    __threadfence();
+    for (int e = threadIdx.x; e < rows * HD; e += NW * 32) {
+        const int row = e / HD, d = e % HD;
+        const size_t gr = (size_t)(t_base + row / G) * nh + kvh * G + row % G;
+        float m = -INFINITY;
+        for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, part_ml[((size_t)sp * n_rows + gr) * 2]);
+        const float use = m == -INFINITY ? 0.f : m;
+        float l = 0.f, acc = 0.f;
+        for (int sp = 0; sp < nsplit; ++sp) {
+            const float f = exp2f(part_ml[((size_t)sp * n_rows + gr) * 2] - use);
+            l += f * part_ml[((size_t)sp * n_rows + gr) * 2 + 1];
+            if (f != 0.f) acc += f * part_o[((size_t)sp * n_rows + gr) * HD + d];
+        }
+        out[gr * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+}
+
+template <int HD, int NW>
+int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, int* counters, const __nv_bfloat16* q,
+                  const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, const int* cu, const int* ctx, const int* bt,
+                  int bt_stride, int B, int T, int num_pages, int page_size, int nh, int nkv, float scale, int window,
+                  int nsplit, int* err, cudaStream_t stream) {
+    const size_t smem = DecodeSmem<HD, NW>::total;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((unsigned)B, (unsigned)nkv, (unsigned)nsplit);
+    CELLM_RUN((attention_decode_kernel<HD, NW>), grid, NW * 32, smem, stream, out, part_o, part_ml, counters, q, k_pool,
+              v_pool, cu, ctx, bt, bt_stride, T, num_pages, page_size, nh, nkv, scale * 1.4426950408889634f, window, err);
+    return CELLM_OK;
+}
+
+}  // namespace
+
+// out, q: [T, nh*hd] bf16; request b owns tokens cu_seqlens[b]..cu_seqlens[b+1], at most
+// 16 / (nh / nkv) of them. nsplit > 1 needs part_o [nsplit, T*nh, hd], part_ml
+// [nsplit, T*nh, 2] floats and B*nkv zeroed counters (left zero by the call).
+CELLM_API int cellm_attention_decode(void* out, float* part_o, float* part_ml, int* counters, const void* q,
+                                     const void* k_pool, const void* v_pool, const int* cu_seqlens,
+                                     const int* ctx_lens, const int* block_table, int bt_stride, int B, int T,
+                                     int num_pages, int page_size, int nh, int nkv, int hd, float scale, int window,
+                                     int nsplit, int* err, cudaStream_t stream) {
+    if (T <= 0 || B <= 0) return CELLM_OK;
+    if (nkv <= 0 || nh % nkv || nh / nkv > 16) return CELLM_ERR_SIZE;
+    if (nsplit < 1 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return CELLM_ERR_ARG;
+    if (nkv > 65535 || nsplit > 65535) return CELLM_ERR_SIZE;
+#define GO(HD_, NW_)                                                                                                \
+    return launch_decode<HD_, NW_>((__nv_bfloat16*)out, part_o, part_ml, counters, (const __nv_bfloat16*)q,         \
+                                   (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_seqlens, ctx_lens, \
+                                   block_table, bt_stride, B, T, num_pages, page_size, nh, nkv, scale, window, nsplit, \
+                                   err, stream)
+    if (hd == 32) GO(32, 4);
+    if (hd == 64) GO(64, 4);
+    if (hd == 128) GO(128, 2);
+#undef GO
+    return CELLM_ERR_SIZE;
+}

@@ -29,6 +29,10 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
     float* sn = smem + rot / 2;          // [rot/2] sin
     const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* buf = smem + rot + warp * hd; // one head per warp
+    const int n_heads_all = nh + 2 * nkv;
+    // blockIdx.y selects a run of heads, so that a token's heads are spread over several blocks
+    const int heads_per_block = (n_heads_all + gridDim.y - 1) / gridDim.y;
+    const int h_begin = blockIdx.y * heads_per_block, h_end = min(n_heads_all, h_begin + heads_per_block);
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -55,7 +59,7 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
     }
     __syncthreads();
     const TA* row = qkv + (size_t)t * row_stride;
-    for (int hh = warp; hh < nh + 2 * nkv; hh += nwarps) {
+    for (int hh = h_begin + warp; hh < h_end; hh += nwarps) {
         const TA* src = row + (size_t)hh * hd;
         if (hh >= nh + nkv) {  // value head: copy
             if (page_base >= 0) {
@@ -108,10 +112,14 @@ CELLM_API int cellm_qk_norm_rope(void* q_out, const void* qkv, long long row_str
     if (rot < 0 || rot > hd || (rot & 1)) return CELLM_ERR_SIZE;
     if ((q_w == nullptr) != (k_w == nullptr)) return CELLM_ERR_ARG;
     const int threads = 128;
+    // few tokens: spread each token's heads over blocks of four (one per warp); many tokens: one block each
+    const int heads_all = nh + 2 * nkv;
+    const unsigned gy = T >= 1024 ? 1u : (unsigned)((heads_all + 3) / 4);
+    dim3 grid((unsigned)T, gy > 65535u ? 65535u : gy);
     const size_t smem = (size_t)(rot + (threads / 32) * hd) * sizeof(float);
     if (smem > 48 * 1024) return CELLM_ERR_SIZE;
 #define LAUNCH(TA, TW)                                                                               \
-    CELLM_RUN((qk_norm_rope_kernel<TA, TW>), T, threads, smem, stream,                               \
+    CELLM_RUN((qk_norm_rope_kernel<TA, TW>), grid, threads, smem, stream,                            \
         (TA*)q_out, (const TA*)qkv, row_stride, (const TW*)q_w, (const TW*)k_w, eps, positions,      \
         seq_of_token, block_table, bt_stride, (TA*)k_pool, (TA*)v_pool, num_pages, page_size, nh,    \
         nkv, hd, rot, interleaved, inv_freq, err)

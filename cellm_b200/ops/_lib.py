@@ -31,6 +31,9 @@ _SIGNATURES = {
     "gemm_plain": {
         "cellm_gemm_plain": [P, P, P, I, I, I, L, L, L, I, I, P],
     },
+    "attention_decode": {
+        "cellm_attention_decode": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
+    },
     "attention_flash": {
         "cellm_attention_flash": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P],
         "cellm_attention_flash_supports": [I],

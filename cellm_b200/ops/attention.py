@@ -59,6 +59,34 @@ def attention_flash(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     return out
 
 
+def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, cu_seqlens: torch.Tensor,
+                     ctx_lens: torch.Tensor, block_table: torch.Tensor, B: int, nh: int, scale: float, window: int,
+                     err: torch.Tensor, nsplit: int = 1) -> torch.Tensor:
+    """Tensor-core attention for short portions (decoded tokens): every request has
+    at most 16 / (nh / kv heads) tokens in the step. One CTA per (request, kv head,
+    piece of the keys); with nsplit > 1 the last CTA of a request combines the pieces."""
+    require_cuda(q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, err)
+    pages, nkv, page_size, hd = k_pool.shape
+    T = q.shape[0]
+    if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or q.shape[1] != nh * hd or hd not in _FLASH_HEAD_SIZES:
+        raise ValueError("attention_decode: bfloat16 with head size 32, 64 or 128 only")
+    out = torch.empty_like(q)
+    part_o = part_ml = counters = None
+    if nsplit > 1:
+        from .gemm_bf16 import MAX_COUNTERS, _counters
+        if B * nkv > MAX_COUNTERS:
+            raise ValueError("attention_decode: too many (request, kv head) pairs for the counters")
+        rows = T * nh
+        ws = _workspace(q.device, nsplit * rows * (hd + 2))
+        part_o, part_ml = ws[:nsplit * rows * hd], ws[nsplit * rows * hd:nsplit * rows * (hd + 2)]
+        counters = _counters(q.device)
+    check(fn("attention_decode", "cellm_attention_decode")(
+        ptr(out), ptr(part_o), ptr(part_ml), ptr(counters), ptr(q), ptr(k_pool), ptr(v_pool), ptr(cu_seqlens),
+        ptr(ctx_lens), ptr(block_table), block_table.stride(0), B, T, pages, page_size, nh, nkv, hd, float(scale),
+        int(window), int(nsplit), ptr(err), stream_of(q)), "attention_decode")
+    return out
+
+
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, block_table: torch.Tensor,
               nh: int, scale: float, window: int) -> torch.Tensor:
     """Attention of every token of the step over its request's pages. bfloat16
@@ -68,6 +96,11 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, 
     if q.dtype == torch.bfloat16 and hd in _FLASH_HEAD_SIZES:
         from .gemm_bf16 import _sms
         G = nh // k_pool.shape[1]
+        if ctx.max_q_len * G <= 16:
+            blocks = (ctx.max_total_len + 63) // 64
+            nsplit = max(1, min(_sms(q.device) // (ctx.B * k_pool.shape[1]), blocks // 8))
+            return attention_decode(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.B, nh, scale,
+                                    window, ctx.err, nsplit)
         wide = ctx.max_q_len * G > 16
         bm = 64 if wide else 16
         n_tiles = sum((n * G + bm - 1) // bm for n in ctx.q_lens)

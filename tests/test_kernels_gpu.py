@@ -240,13 +240,13 @@ def test_attention_plain(dtype, nh, nkv, hd, ps, window):
     close(out, attention_reference(c, nh, nkv, hd, hd ** -0.5, window), dtype)
 
 
-@pytest.mark.parametrize("kernel", ["plain32", "plain16", "flash"])
+@pytest.mark.parametrize("kernel", ["plain32", "plain16", "flash", "decode"])
 def test_a_far_key_among_hundreds_is_found(kernel):
     """One early key is scaled so that its score towers over 600 others: the
     output must be that key's value. A kernel that skips a page, stops short or
     reads a neighbour's page cannot pass."""
     from cellm_b200 import ops
-    from cellm_b200.ops.attention import attention_flash
+    from cellm_b200.ops.attention import attention_decode, attention_flash
     dtype = torch.float32 if kernel == "plain32" else torch.bfloat16
     nh, nkv, hd, ps = 4, 2, 64, 16
     for far in (0, 15, 16, 337):                       # a page's first and last slot, and the middle of nowhere
@@ -256,6 +256,8 @@ def test_a_far_key_among_hundreds_is_found(kernel):
         e = err_word()
         if kernel == "flash":
             out = attention_flash(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], nh, 1.0, 0, e, nsplit=3)
+        elif kernel == "decode":
+            out = attention_decode(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], 2, nh, 1.0, 0, e, nsplit=3)
         else:
             out = ops.attention_plain(c["q"], c["kp"], c["vp"], c["pos"], c["seq"], c["bt"], nh, 1.0, 0, e)
         assert e.item() == 0
@@ -279,13 +281,32 @@ def test_attention_flash(hd, ps, nh, nkv, window):
     assert e.item() == 0
 
 
+@pytest.mark.parametrize("hd,ps,nh,nkv", [(32, 8, 3, 1), (64, 16, 8, 2), (128, 32, 4, 4), (64, 4, 32, 8), (64, 16, 16, 1)])
+@pytest.mark.parametrize("window", [0, 33])
+def test_attention_decode(hd, ps, nh, nkv, window):
+    """Decoded tokens (and portions of two or three where the group is small)
+    through the kernel with a ring per warp, unsplit and split over the keys."""
+    from cellm_b200.ops.attention import attention_decode
+    G = nh // nkv
+    few = max(1, min(3, 16 // G))
+    c = paged_case([1, few, 1, 1, 1], [3, 700, 64, 255, 1000], nh, nkv, hd, ps, torch.bfloat16, seed=5)
+    ref = attention_reference(c, nh, nkv, hd, hd ** -0.5, window)
+    e = err_word()
+    for nsplit in (1, 2, 5):
+        for _ in range(2):            # twice: the counters must be back at zero
+            out = attention_decode(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], 5, nh, hd ** -0.5, window, e, nsplit)
+            close(out, ref, torch.bfloat16, f"nsplit {nsplit}")
+    assert e.item() == 0
+
+
 def test_window_edge():
     """The key just outside the window carries a huge score and must not count;
     the key just inside does."""
     from cellm_b200 import ops
     from cellm_b200.ops.attention import attention_flash
     nh, nkv, hd, ps, window = 2, 1, 32, 8, 24
-    for dtype, kernel in ((torch.float32, "plain"), (torch.bfloat16, "plain"), (torch.bfloat16, "flash")):
+    from cellm_b200.ops.attention import attention_decode
+    for dtype, kernel in ((torch.float32, "plain"), (torch.bfloat16, "plain"), (torch.bfloat16, "flash"), (torch.bfloat16, "decode")):
         for edge, inside in ((100 - window, False), (100 - window + 1, True)):
             c = paged_case([1], [100], nh, nkv, hd, ps, dtype, seed=4)
             kh = c["k_seq"][0][edge, 0]
@@ -293,6 +314,8 @@ def test_window_edge():
             e = err_word()
             if kernel == "flash":
                 out = attention_flash(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], nh, 1.0, window, e)
+            elif kernel == "decode":
+                out = attention_decode(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], 1, nh, 1.0, window, e, 2)
             else:
                 out = ops.attention_plain(c["q"], c["kp"], c["vp"], c["pos"], c["seq"], c["bt"], nh, 1.0, window, e)
             hit = float((out[0, :hd].float().cpu() - c["v_seq"][0][edge, 0]).abs().max()) < 0.05
