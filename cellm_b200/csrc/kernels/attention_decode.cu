@@ -3,10 +3,12 @@
 // One CTA serves one (request, key/value head, piece of the keys). The query
 // heads that share the key/value head are the rows of one 16-row tile (at most
 // 16 / group-size tokens per request, so a request's portion must be that
-// short). Each warp of the CTA walks its own share of the 64-key blocks
-// (block b goes to warp b mod NW) with a cp.async ring of its own, so no warp
-// waits for another while the keys stream in. The warps' partial results
-// (maximum, sum, unnormalised output) are combined through shared memory.
+// short). The CTA walks its keys in blocks of 64 that all its threads bring in
+// with cp.async (two stages); within a block every warp takes its own run of
+// 64 / NW keys and keeps an online-softmax state of its own, so the work of a
+// block is spread over the warps and a CTA needs only one ring of shared memory
+// (several CTAs fit an SM). The warps' partial results (maximum, sum,
+// unnormalised output) are combined through shared memory at the end.
 //
 // When the keys of a request are split over several CTAs (gridDim.z > 1), each
 // CTA leaves its piece in the workspace and adds one to the counter of its
@@ -27,8 +29,8 @@ template <int HD, int NW>
 struct DecodeSmem {
     static constexpr int KV_BYTES = FA_BN * HD * 2;
     static constexpr size_t q_off = 0;
-    static constexpr size_t kv_off = 16 * HD * 2;                         // [NW][2 stages][K | V]
-    static constexpr size_t o_off = kv_off + (size_t)NW * 2 * 2 * KV_BYTES;   // [NW][16][HD] float
+    static constexpr size_t kv_off = 16 * HD * 2;                         // [2 stages][K | V]
+    static constexpr size_t o_off = kv_off + (size_t)2 * 2 * KV_BYTES;    // [NW][16][HD] float
     static constexpr size_t ml_off = o_off + (size_t)NW * 16 * HD * 4;    // [NW][16][2] float
     static constexpr size_t flag_off = ml_off + (size_t)NW * 16 * 2 * 4;
     static constexpr size_t total = flag_off + 16;
@@ -50,7 +52,9 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     float* ml_s = reinterpret_cast<float*>(dec_smem + L::ml_off);
     int* flag_s = reinterpret_cast<int*>(dec_smem + L::flag_off);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint8_t* kv_s = dec_smem + L::kv_off + (size_t)warp * 4 * L::KV_BYTES;
+    uint8_t* kv_s = dec_smem + L::kv_off;
+    constexpr int WK = FA_BN / NW;          // keys of a block that one warp takes (16 or 32)
+    constexpr int THREADS = NW * 32;
     const int G = nh / nkv;
     const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
     pdl_trigger();
@@ -72,23 +76,31 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         cp_async16(q_s + tile_offset<HD>(row, chunk), src, ok ? 16 : 0);
     }
     cp_async_commit();
-    auto load_kv = [&](int kb, int stage) {      // by this warp alone
+    // By all threads. The pages of a thread's keys are looked up first, all at once,
+    // so that the copies that follow do not each wait for a load of the block table.
+    constexpr int KV_ITERS = (BN * CH + THREADS - 1) / THREADS;
+    auto load_kv = [&](int kb, int stage) {
         uint8_t* ks = kv_s + (size_t)stage * 2 * L::KV_BYTES;
         uint8_t* vs = ks + L::KV_BYTES;
-        for (int i = lane; i < BN * CH; i += 32) {
+        int pages[KV_ITERS];
+#pragma unroll
+        for (int it = 0; it < KV_ITERS; ++it) {
+            const int i = threadIdx.x + it * THREADS, j = kb * BN + i / CH;
+            pages[it] = (i < BN * CH && j >= key_begin && j < key_end) ? bt[j / page_size] : -1;
+        }
+#pragma unroll
+        for (int it = 0; it < KV_ITERS; ++it) {
+            const int i = threadIdx.x + it * THREADS;
+            if (i >= BN * CH) break;
             const int row = i / CH, chunk = i % CH, j = kb * BN + row;
-            int page = -1;
-            if (j >= key_begin && j < key_end) {
-                page = bt[j / page_size];
-                if (page < 0 || page >= num_pages) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
-            }
+            int page = pages[it];
+            if (j >= key_begin && j < key_end && (page < 0 || page >= num_pages)) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
             const size_t off = page >= 0 ? (size_t)page * page_elems + ((size_t)kvh * page_size + j % page_size) * HD + chunk * 8 : 0;
             cp_async16(ks + tile_offset<HD>(row, chunk), k_pool + off, page >= 0 ? 16 : 0);
             cp_async16(vs + tile_offset<HD>(row, chunk), v_pool + off, page >= 0 ? 16 : 0);
         }
     };
-    const int first = my_begin + warp;
-    if (first < my_end) load_kv(first, 0);
+    if (my_begin < my_end) load_kv(my_begin, 0);
     cp_async_commit();
     cp_async_wait<1>();          // the Q tile (this thread's share)
     __syncthreads();             // everybody's share
@@ -105,31 +117,32 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 #pragma unroll
     for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
-    for (int kb = first, it = 0; kb < my_end; kb += NW, ++it) {
+    for (int kb = my_begin, it = 0; kb < my_end; ++kb, ++it) {
         const int stage = it & 1;
-        if (kb + NW < my_end) load_kv(kb + NW, stage ^ 1);
+        if (kb + 1 < my_end) load_kv(kb + 1, stage ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
-        __syncwarp();
+        __syncthreads();
         const uint8_t* ks_ = kv_s + (size_t)stage * 2 * L::KV_BYTES;
         const uint8_t* vs_ = ks_ + L::KV_BYTES;
-        float s[BN / 8][4];
+        const int k0 = warp * WK;               // this warp's keys of the block: k0 .. k0 + WK - 1
+        float s[WK / 8][4];
 #pragma unroll
-        for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        for (int n = 0; n < WK / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
 #pragma unroll
-            for (int n2 = 0; n2 < BN / 16; ++n2) {
+            for (int n2 = 0; n2 < WK / 16; ++n2) {
                 uint32_t kf[4];
-                ldmatrix_x4(kf, ks_ + tile_offset<HD>(n2 * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+                ldmatrix_x4(kf, ks_ + tile_offset<HD>(k0 + n2 * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
                 mma_bf16(s[2 * n2], qf[ks], kf[0], kf[1]);
                 mma_bf16(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
             }
         }
-        const int j0 = kb * BN + (lane & 3) * 2;
+        const int j0 = kb * BN + k0 + (lane & 3) * 2;
         float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-        for (int n = 0; n < BN / 8; ++n) {
+        for (int n = 0; n < WK / 8; ++n) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int j = j0 + n * 8 + e;
@@ -147,15 +160,15 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
         const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
         const float use_a = mn_a == -INFINITY ? 0.f : mn_a, use_b = mn_b == -INFINITY ? 0.f : mn_b;
-        const float corr_a = exp2f(m_a - use_a), corr_b = exp2f(m_b - use_b);
+        const float corr_a = fast_exp2(m_a - use_a), corr_b = fast_exp2(m_b - use_b);
         m_a = mn_a;
         m_b = mn_b;
         float sum_a = 0.f, sum_b = 0.f;
-        uint32_t pf[BN / 16][4];
+        uint32_t pf[WK / 16][4];
 #pragma unroll
-        for (int n = 0; n < BN / 8; ++n) {
-            const float p0 = exp2f(s[n][0] - use_a), p1 = exp2f(s[n][1] - use_a);
-            const float p2 = exp2f(s[n][2] - use_b), p3 = exp2f(s[n][3] - use_b);
+        for (int n = 0; n < WK / 8; ++n) {
+            const float p0 = fast_exp2(s[n][0] - use_a), p1 = fast_exp2(s[n][1] - use_a);
+            const float p2 = fast_exp2(s[n][2] - use_b), p3 = fast_exp2(s[n][3] - use_b);
             sum_a += p0 + p1;
             sum_b += p2 + p3;
             pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
@@ -166,16 +179,16 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 #pragma unroll
         for (int n = 0; n < NT; ++n) { o[n][0] *= corr_a; o[n][1] *= corr_a; o[n][2] *= corr_b; o[n][3] *= corr_b; }
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
+        for (int kk = 0; kk < WK / 16; ++kk) {
 #pragma unroll
             for (int n2 = 0; n2 < NT / 2; ++n2) {
                 uint32_t vf[4];
-                ldmatrix_x4_trans(vf, vs_ + tile_offset<HD>(kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), n2 * 2 + (lane >> 4)));
+                ldmatrix_x4_trans(vf, vs_ + tile_offset<HD>(k0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), n2 * 2 + (lane >> 4)));
                 mma_bf16(o[2 * n2], pf[kk], vf[0], vf[1]);
                 mma_bf16(o[2 * n2 + 1], pf[kk], vf[2], vf[3]);
             }
         }
-        __syncwarp();
+        __syncthreads();
     }
     cp_async_wait<0>();
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
@@ -292,7 +305,7 @@ CELLM_API int cellm_attention_decode(void* out, float* part_o, float* part_ml, i
                                    err, stream)
     if (hd == 32) GO(32, 4);
     if (hd == 64) GO(64, 4);
-    if (hd == 128) GO(128, 2);
+    if (hd == 128) GO(128, 4);
 #undef GO
     return CELLM_ERR_SIZE;
 }

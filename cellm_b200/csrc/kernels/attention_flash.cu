@@ -72,16 +72,25 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
         const __nv_bfloat16* src = q + (size_t)(t_base + (ok ? r / G : 0)) * nh * HD + (size_t)(kvh * G + (ok ? r % G : 0)) * HD + chunk * 8;
         cp_async16(q_s + tile_offset<HD>(row, chunk), src, ok ? 16 : 0);
     }
+    // The pages of a block's keys are looked up first, all at once, so that the
+    // copies that follow do not each wait for a load of the block table.
+    constexpr int KV_ITERS = (BN * CH + THREADS - 1) / THREADS;
     auto load_kv = [&](int kb, int stage) {
         uint8_t* ks = k_s + stage * BN * HD * 2;
         uint8_t* vs = v_s + stage * BN * HD * 2;
-        for (int i = threadIdx.x; i < BN * CH; i += THREADS) {
+        int pages[KV_ITERS];
+#pragma unroll
+        for (int it = 0; it < KV_ITERS; ++it) {
+            const int i = threadIdx.x + it * THREADS, j = kb * BN + i / CH;
+            pages[it] = (i < BN * CH && j >= key_begin && j < key_end) ? bt[j / page_size] : -1;
+        }
+#pragma unroll
+        for (int it = 0; it < KV_ITERS; ++it) {
+            const int i = threadIdx.x + it * THREADS;
+            if (i >= BN * CH) break;
             const int row = i / CH, chunk = i % CH, j = kb * BN + row;
-            int page = -1;
-            if (j >= key_begin && j < key_end) {
-                page = bt[j / page_size];
-                if (page < 0 || page >= num_pages) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
-            }
+            int page = pages[it];
+            if (j >= key_begin && j < key_end && (page < 0 || page >= num_pages)) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
             const size_t off = page >= 0 ? (size_t)page * page_elems + ((size_t)kvh * page_size + j % page_size) * HD + chunk * 8 : 0;
             cp_async16(ks + tile_offset<HD>(row, chunk), k_pool + off, page >= 0 ? 16 : 0);
             cp_async16(vs + tile_offset<HD>(row, chunk), v_pool + off, page >= 0 ? 16 : 0);

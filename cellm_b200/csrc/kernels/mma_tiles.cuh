@@ -34,6 +34,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// 2^x by the hardware's approximation (relative error about 2^-22; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold HD
 // bfloat16, with the chunks of a row permuted so that eight rows read by one
 // ldmatrix fall into different banks.

@@ -98,7 +98,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, 
         G = nh // k_pool.shape[1]
         if ctx.max_q_len * G <= 16:
             blocks = (ctx.max_total_len + 63) // 64
-            nsplit = max(1, min(_sms(q.device) // (ctx.B * k_pool.shape[1]), blocks // 8))
+            nsplit = max(1, min(4 * _sms(q.device) // (ctx.B * k_pool.shape[1]), blocks // 4))
             return attention_decode(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.B, nh, scale,
                                     window, ctx.err, nsplit)
         wide = ctx.max_q_len * G > 16
