@@ -45,17 +45,19 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
     pdl_trigger();
     pdl_wait();
 
-    // which request this tile belongs to
+    // which request this tile belongs to; tiles are taken from the last to the first, so
+    // that the tiles with the most keys (the latest rows of a prompt) start first
+    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
     int b = 0, base = 0;
     for (; b < B; ++b) {
         const int nt = ((cu_seqlens[b + 1] - cu_seqlens[b]) * G + BM - 1) / BM;
-        if ((int)blockIdx.x < base + nt) break;
+        if (tile < base + nt) break;
         base += nt;
     }
     if (b == B) return;
     const int t_base = cu_seqlens[b], q_len = cu_seqlens[b + 1] - t_base, rows = q_len * G;
     const int ctx = ctx_lens[b];
-    const int r0 = ((int)blockIdx.x - base) * BM;
+    const int r0 = (tile - base) * BM;
     const int t_lo = r0 / G, t_hi = min(r0 + BM - 1, rows - 1) / G;
     const int key_end = ctx + t_hi + 1;
     const int key_begin = window > 0 ? max(0, ctx + t_lo - window + 1) : 0;
@@ -138,20 +140,34 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
                 mma_bf16(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
             }
         }
-        // mask, online softmax
+        // mask, online softmax. A block whose keys every row of this warp may read
+        // (all below the diagonal, all inside the window) needs no mask.
         const int j0 = kb * BN + (lane & 3) * 2;
         float mx_a = -INFINITY, mx_b = -INFINITY;
+        const int w_row0 = r0 + warp * 16, w_row1 = min(w_row0 + 15, rows - 1);
+        const bool open_block = w_row0 + 15 < rows && kb * BN + BN - 1 <= ctx + w_row0 / G &&
+                                (window <= 0 || kb * BN >= ctx + w_row1 / G - window + 1);
+        if (open_block) {
 #pragma unroll
-        for (int n = 0; n < BN / 8; ++n) {
+            for (int n = 0; n < BN / 8; ++n) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int j = j0 + n * 8 + e;
-                const float va = (j <= pos_a && j >= lo_a) ? s[n][e] * scale_log2e : -INFINITY;
-                const float vb = (j <= pos_b && j >= lo_b) ? s[n][2 + e] * scale_log2e : -INFINITY;
-                s[n][e] = va;
-                s[n][2 + e] = vb;
-                mx_a = fmaxf(mx_a, va);
-                mx_b = fmaxf(mx_b, vb);
+                for (int e = 0; e < 4; ++e) s[n][e] *= scale_log2e;
+                mx_a = fmaxf(mx_a, fmaxf(s[n][0], s[n][1]));
+                mx_b = fmaxf(mx_b, fmaxf(s[n][2], s[n][3]));
+            }
+        } else {
+#pragma unroll
+            for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = j0 + n * 8 + e;
+                    const float va = (j <= pos_a && j >= lo_a) ? s[n][e] * scale_log2e : -INFINITY;
+                    const float vb = (j <= pos_b && j >= lo_b) ? s[n][2 + e] * scale_log2e : -INFINITY;
+                    s[n][e] = va;
+                    s[n][2 + e] = vb;
+                    mx_a = fmaxf(mx_a, va);
+                    mx_b = fmaxf(mx_b, vb);
+                }
             }
         }
         mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
@@ -160,15 +176,15 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
         const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
         const float use_a = mn_a == -INFINITY ? 0.f : mn_a, use_b = mn_b == -INFINITY ? 0.f : mn_b;
-        const float corr_a = exp2f(m_a - use_a), corr_b = exp2f(m_b - use_b);
+        const float corr_a = fast_exp2(m_a - use_a), corr_b = fast_exp2(m_b - use_b);
         m_a = mn_a;
         m_b = mn_b;
         float sum_a = 0.f, sum_b = 0.f;
         uint32_t pf[BN / 16][4];
 #pragma unroll
         for (int n = 0; n < BN / 8; ++n) {
-            const float p0 = exp2f(s[n][0] - use_a), p1 = exp2f(s[n][1] - use_a);
-            const float p2 = exp2f(s[n][2] - use_b), p3 = exp2f(s[n][3] - use_b);
+            const float p0 = fast_exp2(s[n][0] - use_a), p1 = fast_exp2(s[n][1] - use_a);
+            const float p2 = fast_exp2(s[n][2] - use_b), p3 = fast_exp2(s[n][3] - use_b);
             sum_a += p0 + p1;
             sum_b += p2 + p3;
             pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);

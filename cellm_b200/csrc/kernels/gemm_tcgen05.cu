@@ -77,6 +77,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
 
+// Asks the TMA unit to bring a box into L2 only (no shared memory, no barrier).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c0, int c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -251,6 +256,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 mbar_expect_tx(&sm.full[i], (BM + BN) * BK * 2);
                 tma_load_2d(SWAP ? (void*)sm.a[i] : (void*)sm.b[i], map_w, (kb0 + i) * BK, w0, &sm.full[i]);
             }
+            // Static weights beyond the ring are asked into L2 meanwhile, so that after
+            // the wait they stream from there; up to 64 blocks (1 MiB of weights) a CTA.
+            if (w_is_static)
+                for (int i = early; i < nkb && i < early + 64; ++i) tma_prefetch_l2_2d(map_w, (kb0 + i) * BK, w0);
             pdl_wait();
             for (int i = 0; i < early; ++i)
                 tma_load_2d(SWAP ? (void*)sm.b[i] : (void*)sm.a[i], map_x, (kb0 + i) * BK, x0, &sm.full[i]);
@@ -391,7 +400,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                             float g[8], u[8];
 #pragma unroll
                             for (int j = 0; j < 8; ++j) g[j] = u[j] = 0.f;
-#pragma unroll 2
+#pragma unroll 4
                             for (int sp = 0; sp < splits; ++sp) {
                                 const float* src = ws + (size_t)sp * slice + (size_t)q * N;
 #pragma unroll

@@ -41,11 +41,11 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
         const float hi = inv_freq[2 * p], lo = inv_freq[2 * p + 1], fp = (float)pos;
         const float a = fp * hi;                              // angle, rounded
         const float e = fmaf(fp, hi, -a) + fp * lo;           // what the rounding dropped, plus the remainder's share
-        float s, c;
+        float s, c, se, ce;
         sincosf(a, &s, &c);
-        const float h = 1.0f - 0.5f * e * e;
-        cs[p] = c * h - s * e;                                // cos(a + e)
-        sn[p] = s * h + c * e;                                // sin(a + e)
+        sincosf(e, &se, &ce);                                 // e is small (at most a few hundredths far out)
+        cs[p] = c * ce - s * se;                              // cos(a + e)
+        sn[p] = s * ce + c * se;                              // sin(a + e)
     }
     long long page_base = -1;
     if (nkv > 0) {

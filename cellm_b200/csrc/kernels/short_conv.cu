@@ -53,6 +53,68 @@ __global__ void short_conv_fwd_kernel(TA* __restrict__ y, const TA* __restrict__
     y[(size_t)t * H + c] = from_float<TA>(to_float(bcx[(size_t)t * 3 * H + H + c]) * acc);
 }
 
+// The same for bfloat16 rows whose width is a multiple of 8: a thread takes eight
+// neighbouring channels of one token and moves them in 16-byte pieces.
+template <typename TW>
+__global__ void short_conv_fwd_vec8_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ bcx,
+                                           const TW* __restrict__ w, const TW* __restrict__ bias,
+                                           const float* __restrict__ state, long long slot_stride,
+                                           const int* __restrict__ slot_ids, const int* __restrict__ seq_of_token,
+                                           const int* __restrict__ cu_seqlens, int H, int taps, int n_slots,
+                                           int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c0 >= H) return;
+    const int b = seq_of_token[t];
+    const int i = t - cu_seqlens[b];
+    const int slot = slot_ids[b];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_SLOT);
+        return;
+    }
+    const float* st = state + (long long)slot * slot_stride;
+    auto load8 = [](const __nv_bfloat16* p, float* out) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); out[2 * j] = f.x; out[2 * j + 1] = f.y; }
+    };
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = 0; k < taps; ++k) {
+        const int jj = i - (taps - 1) + k;
+        float v[8];
+        if (jj >= 0) {
+            const __nv_bfloat16* row = bcx + (size_t)(t - (taps - 1) + k) * 3 * H;
+            float bb[8], xx[8];
+            load8(row + c0, bb);
+            load8(row + 2 * H + c0, xx);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = bb[j] * xx[j];
+        } else {
+            const float4 a = *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 + jj) * H + c0);
+            const float4 d = *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 + jj) * H + c0 + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = d.x; v[5] = d.y; v[6] = d.z; v[7] = d.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += v[j] * to_float(w[(size_t)(c0 + j) * taps + k]);
+    }
+    float cc[8];
+    load8(bcx + (size_t)t * 3 * H + H + c0, cc);
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float r0 = cc[2 * j] * (acc[2 * j] + (bias ? to_float(bias[c0 + 2 * j]) : 0.f));
+        const float r1 = cc[2 * j + 1] * (acc[2 * j + 1] + (bias ? to_float(bias[c0 + 2 * j + 1]) : 0.f));
+        __nv_bfloat162 pk = __floats2bfloat162_rn(r0, r1);
+        o[j] = *reinterpret_cast<uint32_t*>(&pk);
+    }
+    *reinterpret_cast<uint4*>(y + (size_t)t * H + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 template <typename TA>
 __global__ void short_conv_state_kernel(const TA* __restrict__ bcx, float* __restrict__ state,
                                         long long slot_stride, const int* __restrict__ slot_ids,
@@ -133,6 +195,9 @@ CELLM_API int cellm_short_conv(void* y, const void* bcx, const void* w, const vo
     const int threads = 128;
     dim3 grid_f((unsigned)T, (unsigned)((H + threads - 1) / threads));
     dim3 grid_s((unsigned)B, (unsigned)((H + threads - 1) / threads));
+    dim3 grid_v((unsigned)T, (unsigned)((H / 8 + threads - 1) / threads));
+    const bool vec8 = act_dtype == CELLM_BF16 && (H & 7) == 0 && (slot_stride & 3) == 0 &&
+                      (((uintptr_t)y | (uintptr_t)bcx | (uintptr_t)state) & 15) == 0;
 #define LAUNCH(TA, TW)                                                                              \
     do {                                                                                            \
         if (max_q_len > 0 && max_q_len <= 4) {                                                      \
@@ -140,9 +205,15 @@ CELLM_API int cellm_short_conv(void* y, const void* bcx, const void* w, const vo
                       (const TW*)w, (const TW*)bias, state, slot_stride, slot_ids, cu_seqlens, H, taps, n_slots, err); \
             break;                                                                                  \
         }                                                                                           \
-        CELLM_RUN((short_conv_fwd_kernel<TA, TW>), grid_f, threads, 0, stream,                      \
-                  (TA*)y, (const TA*)bcx, (const TW*)w, (const TW*)bias, (const float*)state, slot_stride, slot_ids, \
-                  seq_of_token, cu_seqlens, H, taps, n_slots, err);                                 \
+        if (vec8) {                                                                                 \
+            CELLM_RUN(short_conv_fwd_vec8_kernel<TW>, grid_v, threads, 0, stream, (__nv_bfloat16*)y,     \
+                      (const __nv_bfloat16*)bcx, (const TW*)w, (const TW*)bias, (const float*)state, slot_stride, \
+                      slot_ids, seq_of_token, cu_seqlens, H, taps, n_slots, err);                   \
+        } else {                                                                                    \
+            CELLM_RUN((short_conv_fwd_kernel<TA, TW>), grid_f, threads, 0, stream,                  \
+                      (TA*)y, (const TA*)bcx, (const TW*)w, (const TW*)bias, (const float*)state, slot_stride, slot_ids, \
+                      seq_of_token, cu_seqlens, H, taps, n_slots, err);                             \
+        }                                                                                           \
         if (taps > 1)                                                                               \
             CELLM_RUN(short_conv_state_kernel<TA>, grid_s, threads, 0, stream,                      \
                       (const TA*)bcx, state, slot_stride, slot_ids, cu_seqlens, H, taps, n_slots);  \
