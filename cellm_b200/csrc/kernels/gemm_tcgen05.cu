@@ -71,6 +71,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -154,6 +158,8 @@ struct alignas(1024) GemmSmem {
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_full;
+    uint64_t acc_full2[2];     // persistent kernel: one per accumulator buffer
+    uint64_t acc_empty2[2];
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
@@ -190,7 +196,13 @@ template <> __device__ __forceinline__ void store_row<__nv_bfloat16>(__nv_bfloat
     }
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
+// silu(g) * u with the hardware's exp2 and division approximations (a few units of
+// 32-bit rounding; the result is rounded to bfloat16 anyway). g -> -inf gives -0, not NaN.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
+    return __fdividef(g, 1.0f + e) * u;
+}
 
 // The 128-row operand ("rows") and the BN-row operand ("cols") of a tile:
 //   SWAP = false: rows = A (tokens),  cols = W;  grid (ceil(N/BN),  ceil(M/128), split_k); tile element (p, q) -> C[p][q]
@@ -465,6 +477,152 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// Persistent form for large products (plain tiles, no K split): one CTA per SM walks
+// the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles of A fastest, so
+// CTAs that run side by side share a tile of W in L2). The accumulator is double
+// buffered in tensor memory (2 x BN columns): while the epilogue warps drain one
+// buffer and store it, the MMA warp already fills the other, and the TMA warp keeps
+// the stage ring full across tile borders.
+template <int BN, int STAGES, int EPI, typename TO>
+__global__ void __launch_bounds__(192)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                               TO* __restrict__ C, int M, int N, int K, long long ldc, int w_is_static,
+                               int* __restrict__ err) {
+    extern __shared__ uint8_t smem_raw[];
+    auto& sm = *reinterpret_cast<GemmSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, num_tiles = m_tiles * n_tiles;
+    const int nkb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sm.acc_full2[b], 1); mbar_init(&sm.acc_empty2[b], 128); }
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    }
+    if (warp == 1) tmem_alloc(&sm.tmem_base, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    pdl_trigger();
+    const uint32_t tmem = sm.tmem_base;
+    volatile int* abort_flag = &sm.abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool waited = false;
+            if (!w_is_static) { pdl_wait(); waited = true; }
+            for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+                const int p0 = (tile % m_tiles) * BM, q0 = (tile / m_tiles) * BN;
+                int kb = 0;
+                if (!waited) {
+                    // static weights: the ring's first loads of W go out before the wait on the preceding kernel
+                    const int early = nkb < STAGES ? nkb : STAGES;
+                    for (int i = 0; i < early; ++i) {
+                        mbar_expect_tx(&sm.full[i], (BM + BN) * BK * 2);
+                        tma_load_2d(sm.b[i], &map_w, i * BK, q0, &sm.full[i]);
+                    }
+                    pdl_wait();
+                    waited = true;
+                    for (int i = 0; i < early; ++i) tma_load_2d(sm.a[i], &map_a, i * BK, p0, &sm.full[i]);
+                    kb = early;
+                    it = early;
+                }
+                for (; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+                    if (!mbar_wait(&sm.empty[s], phase ^ 1u, abort_flag)) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); break; }
+                    mbar_expect_tx(&sm.full[s], (BM + BN) * BK * 2);
+                    tma_load_2d(sm.a[s], &map_a, kb * BK, p0, &sm.full[s]);
+                    tma_load_2d(sm.b[s], &map_w, kb * BK, q0, &sm.full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(BM, BN);
+            int it = 0, tcount = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+                const int buf = tcount & 1;
+                const uint32_t acc_phase = (uint32_t)(tcount >> 1) & 1u;
+                if (!mbar_wait(&sm.acc_empty2[buf], acc_phase ^ 1u, abort_flag)) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); break; }
+                tc_fence_after();
+                const uint32_t acc = tmem + (uint32_t)(buf * BN);
+                bool ok = true;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+                    if (!mbar_wait(&sm.full[s], phase, abort_flag)) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t da = umma_desc(smem_u32(sm.a[s])), db = umma_desc(smem_u32(sm.b[s]));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(acc, da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16), idesc,
+                                  (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(&sm.empty[s]);
+                }
+                if (!ok) break;
+                umma_commit(&sm.acc_full2[buf]);
+            }
+        }
+    } else {
+        const int qtr = warp & 3;
+        const int pl = qtr * 32 + lane;
+        bool waited = false;
+        int tcount = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+            const int buf = tcount & 1;
+            const uint32_t acc_phase = (uint32_t)(tcount >> 1) & 1u;
+            if (!mbar_wait(&sm.acc_full2[buf], acc_phase, abort_flag)) {
+                if (lane == 0) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); }
+                break;
+            }
+            tc_fence_after();
+            if (!waited) { pdl_wait(); waited = true; }    // stores must not pass the kernel before this one
+            const int p0 = (tile % m_tiles) * BM, q0 = (tile / m_tiles) * BN;
+            const int p = p0 + pl;
+            const uint32_t lane_addr = tmem + ((uint32_t)(qtr * 32) << 16) + (uint32_t)(buf * BN);
+            if constexpr (EPI == 0) {
+                const bool aligned = ((reinterpret_cast<uintptr_t>(C) | (uintptr_t)(ldc * sizeof(TO))) & 15) == 0 &&
+                                     ((q0 * sizeof(TO)) & 15) == 0;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(lane_addr + (uint32_t)(c * 32), r);
+                    if (c == BN / 32 - 1) { tc_fence_before(); mbar_arrive(&sm.acc_empty2[buf]); }
+                    const int q = q0 + c * 32;
+                    if (p < M && q < N) store_row<TO>(C + (size_t)p * ldc + q, r, N - q, aligned);
+                }
+            } else {
+                const int o0 = q0 / 2;
+                const bool aligned = ((reinterpret_cast<uintptr_t>(C) | (uintptr_t)(ldc * sizeof(TO))) & 15) == 0 &&
+                                     ((o0 * sizeof(TO)) & 15) == 0;
+#pragma unroll 1
+                for (int j = 0; j < BN / 128; ++j) {
+#pragma unroll 1
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t g[32], u[32];
+                        tmem_ld32(lane_addr + (uint32_t)(j * 128 + h * 32), g);
+                        tmem_ld32(lane_addr + (uint32_t)(j * 128 + 64 + h * 32), u);
+                        if (j == BN / 128 - 1 && h == 1) { tc_fence_before(); mbar_arrive(&sm.acc_empty2[buf]); }
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(silu_mul(__uint_as_float(g[i]), __uint_as_float(u[i])));
+                        const int o = o0 + j * 64 + h * 32;
+                        if (p < M && o < N / 2) store_row<TO>(C + (size_t)p * ldc + o, g, N / 2 - o, aligned);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -539,6 +697,26 @@ int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* w
     return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
+template <int BN, int STAGES, int EPI, typename TO>
+int launch_persistent(const CUtensorMap& m_a, const CUtensorMap& m_w, TO* C, int M, int N, int K, long long ldc,
+                      int w_is_static, int* err, cudaStream_t stream) {
+    const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+    static int sms = 0;
+    if (sms == 0) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES, EPI, TO>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return CELLM_ERR_ARG;
+    }
+    const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    dim3 grid((unsigned)(tiles < sms ? tiles : sms));
+    cudaError_t e = cellm_launch(gemm_tcgen05_persistent_kernel<BN, STAGES, EPI, TO>, grid, dim3(192), smem, stream, m_a,
+                                 m_w, C, M, N, K, ldc, w_is_static, err);
+    return e == cudaSuccess ? CELLM_OK : (int)e;
+}
+
 }  // namespace
 
 // Most tiles a product may have when K is split (one counter each).
@@ -599,6 +777,18 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
     const CUtensorMap& m_rows = swap ? map_w : map_a;
     const CUtensorMap& m_cols = swap ? map_a : map_w;
     int rc = CELLM_ERR_SIZE;
+    // Large unsplit products with plain tiles of 128 or 256 columns run the persistent kernel.
+    if (!swap && split == 1 && narrow >= 128) {
+#define GOP(BN_, ST_, EP_)                                                                                          \
+    do {                                                                                                            \
+        if (out_dtype == CELLM_F32) rc = launch_persistent<BN_, ST_, EP_, float>(map_a, map_w, (float*)C, M, N, K, ldc, w_is_static, err, stream); \
+        else rc = launch_persistent<BN_, ST_, EP_, __nv_bfloat16>(map_a, map_w, (__nv_bfloat16*)C, M, N, K, ldc, w_is_static, err, stream); \
+    } while (0)
+        if (narrow == 128) { if (epilogue == 0) GOP(128, 6, 0); else GOP(128, 6, 1); }
+        else { if (epilogue == 0) GOP(256, 4, 0); else GOP(256, 4, 1); }
+#undef GOP
+        return rc;
+    }
 #define GO2(BN_, ST_, SW_, EP_)                                                                                       \
     do {                                                                                                              \
         if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, EP_, float>(m_rows, m_cols, (float*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
