@@ -68,6 +68,9 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     const int my_begin = kb_begin + split * per, my_end = min(kb_end, my_begin + per);
     const int* bt = block_table + (size_t)b * bt_stride;
     const size_t page_elems = (size_t)nkv * page_size * HD;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;   // -1: not a power of two
+    auto page_of = [&](int j) { return page_shift >= 0 ? (j >> page_shift) : (j / page_size); };
+    auto slot_of = [&](int j) { return page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size); };
 
     for (int i = threadIdx.x; i < 16 * CH; i += NW * 32) {
         const int row = i / CH, chunk = i % CH;
@@ -86,7 +89,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 #pragma unroll
         for (int it = 0; it < KV_ITERS; ++it) {
             const int i = threadIdx.x + it * THREADS, j = kb * BN + i / CH;
-            pages[it] = (i < BN * CH && j >= key_begin && j < key_end) ? bt[j / page_size] : -1;
+            pages[it] = (i < BN * CH && j >= key_begin && j < key_end) ? bt[page_of(j)] : -1;
         }
 #pragma unroll
         for (int it = 0; it < KV_ITERS; ++it) {
@@ -95,7 +98,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
             const int row = i / CH, chunk = i % CH, j = kb * BN + row;
             int page = pages[it];
             if (j >= key_begin && j < key_end && (page < 0 || page >= num_pages)) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
-            const size_t off = page >= 0 ? (size_t)page * page_elems + ((size_t)kvh * page_size + j % page_size) * HD + chunk * 8 : 0;
+            const size_t off = page >= 0 ? (size_t)page * page_elems + ((size_t)kvh * page_size + slot_of(j)) * HD + chunk * 8 : 0;
             cp_async16(ks + tile_offset<HD>(row, chunk), k_pool + off, page >= 0 ? 16 : 0);
             cp_async16(vs + tile_offset<HD>(row, chunk), v_pool + off, page >= 0 ? 16 : 0);
         }

@@ -27,7 +27,7 @@
 namespace {
 
 template <int HD, int NWARPS>
-__global__ void __launch_bounds__(NWARPS * 32)
+__global__ void __launch_bounds__(NWARPS * 32, (HD <= 64 && NWARPS == 4) ? 4 : 1)
 attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                        const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ cu_seqlens,
@@ -66,6 +66,9 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
     const int my_begin = kb_begin + split * per, my_end = min(kb_end, my_begin + per);
     const int* bt = block_table + (size_t)b * bt_stride;
     const size_t page_elems = (size_t)nkv * page_size * HD;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;   // -1: not a power of two
+    auto page_of = [&](int j) { return page_shift >= 0 ? (j >> page_shift) : (j / page_size); };
+    auto slot_of = [&](int j) { return page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size); };
 
     // Q tile
     for (int i = threadIdx.x; i < BM * CH; i += THREADS) {
@@ -84,7 +87,7 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
 #pragma unroll
         for (int it = 0; it < KV_ITERS; ++it) {
             const int i = threadIdx.x + it * THREADS, j = kb * BN + i / CH;
-            pages[it] = (i < BN * CH && j >= key_begin && j < key_end) ? bt[j / page_size] : -1;
+            pages[it] = (i < BN * CH && j >= key_begin && j < key_end) ? bt[page_of(j)] : -1;
         }
 #pragma unroll
         for (int it = 0; it < KV_ITERS; ++it) {
@@ -93,7 +96,7 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
             const int row = i / CH, chunk = i % CH, j = kb * BN + row;
             int page = pages[it];
             if (j >= key_begin && j < key_end && (page < 0 || page >= num_pages)) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
-            const size_t off = page >= 0 ? (size_t)page * page_elems + ((size_t)kvh * page_size + j % page_size) * HD + chunk * 8 : 0;
+            const size_t off = page >= 0 ? (size_t)page * page_elems + ((size_t)kvh * page_size + slot_of(j)) * HD + chunk * 8 : 0;
             cp_async16(ks + tile_offset<HD>(row, chunk), k_pool + off, page >= 0 ? 16 : 0);
             cp_async16(vs + tile_offset<HD>(row, chunk), v_pool + off, page >= 0 ? 16 : 0);
         }
@@ -150,8 +153,6 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
         if (open_block) {
 #pragma unroll
             for (int n = 0; n < BN / 8; ++n) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) s[n][e] *= scale_log2e;
                 mx_a = fmaxf(mx_a, fmaxf(s[n][0], s[n][1]));
                 mx_b = fmaxf(mx_b, fmaxf(s[n][2], s[n][3]));
             }
@@ -161,8 +162,8 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int j = j0 + n * 8 + e;
-                    const float va = (j <= pos_a && j >= lo_a) ? s[n][e] * scale_log2e : -INFINITY;
-                    const float vb = (j <= pos_b && j >= lo_b) ? s[n][2 + e] * scale_log2e : -INFINITY;
+                    const float va = (j <= pos_a && j >= lo_a) ? s[n][e] : -INFINITY;
+                    const float vb = (j <= pos_b && j >= lo_b) ? s[n][2 + e] : -INFINITY;
                     s[n][e] = va;
                     s[n][2 + e] = vb;
                     mx_a = fmaxf(mx_a, va);
@@ -174,7 +175,8 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
         mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        // scores stay raw; the scale (positive) enters with the subtraction of the maximum: 2^(s*c - m)
+        const float mn_a = fmaxf(m_a, mx_a * scale_log2e), mn_b = fmaxf(m_b, mx_b * scale_log2e);
         const float use_a = mn_a == -INFINITY ? 0.f : mn_a, use_b = mn_b == -INFINITY ? 0.f : mn_b;
         const float corr_a = fast_exp2(m_a - use_a), corr_b = fast_exp2(m_b - use_b);
         m_a = mn_a;
@@ -183,8 +185,8 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
         uint32_t pf[BN / 16][4];
 #pragma unroll
         for (int n = 0; n < BN / 8; ++n) {
-            const float p0 = fast_exp2(s[n][0] - use_a), p1 = fast_exp2(s[n][1] - use_a);
-            const float p2 = fast_exp2(s[n][2] - use_b), p3 = fast_exp2(s[n][3] - use_b);
+            const float p0 = fast_exp2(fmaf(s[n][0], scale_log2e, -use_a)), p1 = fast_exp2(fmaf(s[n][1], scale_log2e, -use_a));
+            const float p2 = fast_exp2(fmaf(s[n][2], scale_log2e, -use_b)), p3 = fast_exp2(fmaf(s[n][3], scale_log2e, -use_b));
             sum_a += p0 + p1;
             sum_b += p2 + p3;
             pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);

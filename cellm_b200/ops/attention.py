@@ -93,7 +93,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, 
     with a head size the tensor-core kernel is built for runs there; everything
     else (32-bit, other head sizes) runs the plain kernel."""
     hd = k_pool.shape[3]
-    if q.dtype == torch.bfloat16 and hd in _FLASH_HEAD_SIZES:
+    if q.dtype == torch.bfloat16 and hd in _FLASH_HEAD_SIZES and scale > 0:
         from .gemm_bf16 import _sms
         G = nh // k_pool.shape[1]
         if ctx.max_q_len * G <= 16:
