@@ -220,7 +220,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 // pieces in the order of the splits, writes the output and sets the counter
 // back to zero. No CTA waits for another.
 template <int BN, int STAGES, bool SWAP, int EPI, typename TO>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(192, SWAP ? 2 : 1)      // swapped tiles: two CTAs an SM, so the next product's can move in early
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                     TO* __restrict__ C, float* __restrict__ ws, int* __restrict__ counters, int M, int N, int K,
                     long long ldc, int kblocks_per_split, int w_is_static, int* __restrict__ err) {
@@ -412,7 +412,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                             float g[8], u[8];
 #pragma unroll
                             for (int j = 0; j < 8; ++j) g[j] = u[j] = 0.f;
-#pragma unroll 4
+#pragma unroll 2
                             for (int sp = 0; sp < splits; ++sp) {
                                 const float* src = ws + (size_t)sp * slice + (size_t)q * N;
 #pragma unroll
