@@ -50,6 +50,9 @@ def lib():
             "cellm_sched_plan_preempted": ([LP, c_int], c_int),
             "cellm_sched_plan_admitted": ([LP, IP, c_int], c_int),
             "cellm_sched_step_done": ([c_void_p], c_int),
+            "cellm_sched_plan_shape": ([IP], c_int),
+            "cellm_sched_plan_fill": ([c_void_p, c_void_p, c_int, c_int, c_int], c_int),
+            "cellm_sched_append_rows": ([c_void_p, c_void_p, c_void_p, c_void_p, c_int], c_int),
             "cellm_sched_append": ([c_void_p, c_longlong, c_int, c_int], c_int),
             "cellm_sched_cancel": ([c_void_p, c_longlong], c_int),
             "cellm_sched_forget": ([c_void_p, c_longlong], c_int),

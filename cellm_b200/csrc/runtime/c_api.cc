@@ -2,6 +2,7 @@
 // from Python through ctypes. Every function returns a status (0 or a count
 // on success, negative on error); the message of the last error of the calling
 // thread is read with cellm_last_error().
+#include <algorithm>
 #include <cstring>
 #include <string>
 
@@ -155,6 +156,74 @@ API int cellm_sched_plan_admitted(long long* ids, int* slots, int cap) {
     if (n > cap) return -3;
     for (int i = 0; i < n; ++i) { ids[i] = g_plan.admitted[(size_t)i].first; slots[i] = g_plan.admitted[(size_t)i].second; }
     return n;
+}
+// Shape of the planned step: out[0..4] = entries, tokens, wanted rows, most tokens a
+// request will hold after the step, 1 if every entry is one token whose logits are wanted.
+API int cellm_sched_plan_shape(int* out) {
+    int T = 0, R = 0, max_total = 0, all_decode = 1;
+    for (const auto& e : g_plan.entries) {
+        T += e.count;
+        R += e.wants_logits ? 1 : 0;
+        max_total = std::max(max_total, e.start + e.count);
+        if (e.count != 1 || !e.wants_logits) all_decode = 0;
+    }
+    out[0] = (int)g_plan.entries.size(); out[1] = T; out[2] = R; out[3] = max_total; out[4] = all_decode;
+    return 0;
+}
+// Writes the planned step's index arrays into buf, in the order the step function
+// reads them: token ids [T], positions [T], entry of each token [T], cumulative
+// lengths [B+1], tokens already cached [B], state slots [B], wanted rows [R], then one
+// block table [B][width] per paged group (-1 where there is no page). Returns the
+// number of ints written.
+API int cellm_sched_plan_fill(void* s, int* buf, int cap, int width, int n_groups) {
+    return guarded([&] {
+        auto* sc = static_cast<cellm::Scheduler*>(s);
+        const int B = (int)g_plan.entries.size();
+        int T = 0, R = 0;
+        for (const auto& e : g_plan.entries) { T += e.count; R += e.wants_logits ? 1 : 0; }
+        const long long need = 3LL * T + (B + 1) + 2LL * B + R + (long long)n_groups * B * width;
+        if (need > cap) { g_error = "scheduler: index buffer too small"; return -3; }
+        int* ids = buf; int* pos = ids + T; int* seq = pos + T; int* cu = seq + T; int* ctx = cu + B + 1;
+        int* slot = ctx + B; int* rows = slot + B; int* tabs = rows + R;
+        int t = 0, r = 0;
+        cu[0] = 0;
+        for (int b = 0; b < B; ++b) {
+            const auto& e = g_plan.entries[(size_t)b];
+            const auto& rq = sc->request(e.id);
+            const auto& rc = sc->cache().request(e.id);
+            for (int i = 0; i < e.count; ++i, ++t) {
+                ids[t] = rq.tokens[(size_t)(e.start + i)];
+                pos[t] = e.start + i;
+                seq[t] = b;
+            }
+            cu[b + 1] = t;
+            ctx[b] = e.start;
+            slot[b] = rc.slot;
+            if (e.wants_logits) rows[r++] = t - 1;
+            for (int g = 0; g < n_groups; ++g) {
+                int* row = tabs + ((size_t)g * B + b) * width;
+                const auto& blocks = rc.blocks.at((size_t)g);
+                if ((int)blocks.size() > width) { g_error = "scheduler: block table wider than the buffer"; return -3; }
+                for (int i = 0; i < width; ++i) row[i] = i < (int)blocks.size() ? blocks[(size_t)i] : -1;
+            }
+        }
+        return (int)need;
+    });
+}
+// Appends one sampled token per wanted row of the planned step, in the order of the
+// entries; stops[i] != 0 ends request i. finished[i] becomes 1 where a request ended.
+API int cellm_sched_append_rows(void* s, const int* tokens, const int* stops, int* finished, int n) {
+    return guarded([&] {
+        auto* sc = static_cast<cellm::Scheduler*>(s);
+        int r = 0;
+        for (const auto& e : g_plan.entries) {
+            if (!e.wants_logits) continue;
+            if (r >= n) { g_error = "scheduler: fewer tokens than wanted rows"; return -3; }
+            finished[r] = sc->append_token(e.id, tokens[r], stops[r] != 0) ? 1 : 0;
+            ++r;
+        }
+        return r;
+    });
 }
 API int cellm_sched_step_done(void* s) {
     return guarded([&] { static_cast<cellm::Scheduler*>(s)->step_done(g_plan); return 0; });

@@ -79,6 +79,7 @@ public:
     void forget(int64_t id);  // drops a finished request's record
 
     const Request& request(int64_t id) const;
+    const CacheManager& cache() const { return *cache_; }
     bool has(int64_t id) const { return requests_.count(id) != 0; }
     int num_waiting() const { return (int)waiting_.size(); }
     int num_running() const { return (int)running_.size(); }

@@ -95,36 +95,31 @@ class Engine:
     def step(self) -> list[tuple[int, int]]:
         """Runs one batch; returns (request, new token) for every request that
         produced a token in it."""
-        plan = self.scheduler.schedule()
-        for rid, slot in plan.admitted:
+        rows, preempted, admitted, n_entries = self.scheduler.schedule_rows()
+        for rid, slot in admitted:
             self.cache.zero_slot(slot)
-        if not plan.entries or plan.preempted:
+        if n_entries == 0 or preempted:
             for rid in list(self._outputs):
                 if not self._outputs[rid].finished and self.scheduler.has(rid) \
                         and self.scheduler.info(rid)["state"] == "finished":
                     self._finish(rid)     # the scheduler gave the request up (cannot fit)
-        if not plan.entries:
+        if n_entries == 0:
             return []
-        entries, rows = [], []
-        for e in plan.entries:
-            toks = self.scheduler.tokens(e.request_id, e.start, e.count)
-            entries.append(StepEntry(e.request_id, toks, [e.count - 1] if e.wants_logits else []))
-            if e.wants_logits:
-                rows.append(e.request_id)
-        logits = self.runner.run(entries, self.max_layers)
+        logits = self.runner.run_planned(self.scheduler, self.max_layers)
         self.scheduler.step_done()
         produced = []
         if rows:
-            tokens = sample_rows(logits, [self._samplers[r] for r in rows])
-            self.runner.check()
+            samplers = [self._samplers[r] for r in rows]
+            tokens = sample_rows(logits, samplers)
+            self.runner.check_rarely()
             eos = self.plan.eos_token_id
-            for rid, tok in zip(rows, tokens):
-                s = self._samplers[rid]
+            stops = [s.params.stop_eos and eos is not None and tok == eos for s, tok in zip(samplers, tokens)]
+            finished = self.scheduler.append_rows(tokens, stops)
+            for rid, s, tok, fin in zip(rows, samplers, tokens, finished):
                 s.history.append(tok)
                 self._outputs[rid].tokens.append(tok)
-                stop = s.params.stop_eos and eos is not None and tok == eos
                 produced.append((rid, tok))
-                if self.scheduler.append_token(rid, tok, stop):
+                if fin:
                     self._finish(rid)
         return produced
 

@@ -67,6 +67,42 @@ class Scheduler:
         admitted = [(self._ids[i], self._a[i]) for i in range(n)]
         return StepPlan(entries, preempted, admitted)
 
+    def plan_shape(self) -> tuple[int, int, int, int, bool]:
+        """(entries, tokens, wanted rows, most tokens of a request after the step, all
+        entries are single decoded tokens) of the step planned last."""
+        buf = (ctypes.c_int * 5)()
+        lib().cellm_sched_plan_shape(buf)
+        return buf[0], buf[1], buf[2], buf[3], bool(buf[4])
+
+    def plan_fill(self, buf_address: int, capacity: int, width: int, n_groups: int) -> int:
+        """Has the runtime write the planned step's index arrays (ids, positions,
+        entry of token, cumulative lengths, cached lengths, slots, wanted rows, block
+        tables) straight into an int32 buffer; returns how many ints were written."""
+        return checked(lib().cellm_sched_plan_fill(self._h, buf_address, int(capacity), int(width), int(n_groups)),
+                       SchedulerError)
+
+    def append_rows(self, tokens, stops) -> list[bool]:
+        """One sampled token per wanted row of the planned step; returns which requests finished."""
+        n = len(tokens)
+        fin = (ctypes.c_int * max(n, 1))()
+        checked(lib().cellm_sched_append_rows(self._h, int_array(list(tokens)), int_array([1 if x else 0 for x in stops]),
+                                              fin, n), SchedulerError)
+        return [bool(fin[i]) for i in range(n)]
+
+    def schedule_rows(self):
+        """Plans the next step like schedule(), but returns only what the engine needs
+        per step: (ids of the requests whose logits are wanted, in row order;
+        preempted requests; newly admitted (request, slot) pairs; number of entries)."""
+        l = lib()
+        n_entries = checked(l.cellm_sched_schedule(self._h), SchedulerError)
+        n = checked(l.cellm_sched_plan_entries(self._ids, self._a, self._b, self._c, self._cap), SchedulerError)
+        rows = [self._ids[i] for i in range(n) if self._c[i]]
+        n = checked(l.cellm_sched_plan_preempted(self._ids, self._cap), SchedulerError)
+        preempted = [self._ids[i] for i in range(n)] if n else []
+        n = checked(l.cellm_sched_plan_admitted(self._ids, self._a, self._cap), SchedulerError)
+        admitted = [(self._ids[i], self._a[i]) for i in range(n)] if n else []
+        return rows, preempted, admitted, n_entries
+
     def step_done(self) -> None:
         """Marks the tokens of the last planned step as cached."""
         checked(lib().cellm_sched_step_done(self._h), SchedulerError)

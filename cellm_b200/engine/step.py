@@ -180,24 +180,7 @@ class StepRunner:
         ev.record()
         self._events[self._flip] = ev
         if "graph" not in g:
-            ctx, tabs, logit_rows = self._context(g["meta"], spans, tables, q_lens, ctx_lens, width * ps)
-            bindings = self.cache.bindings(tabs)
-            # One eager run loads every kernel this shape uses; fixed-size state is
-            # put back afterwards, because the captured run will update it again.
-            slot_idx = torch.tensor(slots, dtype=torch.long, device=self.device)
-            saved = [s[:, slot_idx].clone() for s in self.cache.states]
-            self.model.forward(ctx, bindings, logit_rows)
-            for s, keep in zip(self.cache.states, saved):
-                s[:, slot_idx] = keep
-            torch.cuda.synchronize(self.device)
-            from ..ops._lib import LAUNCHES
-            graph = torch.cuda.CUDAGraph()
-            before = LAUNCHES[0]
-            with torch.cuda.graph(graph):
-                g["logits"] = self.model.forward(ctx, bindings, logit_rows)
-            g["graph"] = graph
-            g["launches"] = LAUNCHES[0] - before     # kernels one replay runs
-            LAUNCHES[0] = before
+            self._capture(g, spans, tables, q_lens, ctx_lens, width * ps, slots)
         from ..ops._lib import LAUNCHES
         g["graph"].replay()
         LAUNCHES[0] += g["launches"]
@@ -206,6 +189,89 @@ class StepRunner:
         self.steps += 1
         self.tokens += B
         return g["logits"]
+
+    def _layout(self, B: int, T: int, R: int, width: int):
+        """Offsets of the index arrays for a step of this shape (the order `_fill` and
+        the runtime's plan_fill write them in)."""
+        o = 0
+        spans = {}
+        for name, n in (("ids", T), ("pos", T), ("seq", T), ("cu", B + 1), ("ctx", B), ("slot", B), ("rows", R)):
+            spans[name] = (o, n)
+            o += n
+        tables = []
+        for _ in range(len(self.cache.paged_keys)):
+            tables.append((o, B, width))
+            o += B * width
+        return spans, tables, o
+
+    def run_planned(self, scheduler, max_layers: Optional[int] = None) -> Optional[torch.Tensor]:
+        """Runs the step the scheduler planned last. The runtime writes the index
+        arrays itself (tokens, positions, slots, block tables), so the host's share of
+        a step is a handful of calls whatever the batch. The scheduler has reserved
+        the pages; its step_done() records the new lengths."""
+        B, T, R, max_total, all_decode = scheduler.plan_shape()
+        if B == 0:
+            return None
+        ps = self.cache.page_size
+        need = (max_total + ps - 1) // ps
+        graph = self.use_graphs and all_decode and max_layers is None
+        width = -(-need // self.graph_width_step) * self.graph_width_step if graph else need
+        spans, tables, n_meta = self._layout(B, T, R, width)
+        stage = self._staging(n_meta)
+        scheduler.plan_fill(stage.data_ptr(), n_meta, width, len(self.cache.paged_keys))
+        buf = stage.numpy()
+        if all_decode:
+            q_lens, ctx_lens = [1] * B, None
+        else:
+            cu = buf[spans["cu"][0]:spans["cu"][0] + B + 1]
+            q_lens = np.diff(cu).tolist()
+        self.steps += 1
+        self.tokens += T
+        if graph:
+            key = (B, width)
+            g = self._graphs.get(key)
+            if g is None:
+                g = {"meta": torch.empty(n_meta, dtype=torch.int32, device=self.device)}
+                self._graphs[key] = g
+            g["meta"].copy_(stage[:n_meta], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._events[self._flip] = ev
+            if "graph" not in g:
+                slots = buf[spans["slot"][0]:spans["slot"][0] + B].tolist()
+                self._capture(g, spans, tables, q_lens, [0] * B, width * ps, slots)
+            from ..ops._lib import LAUNCHES
+            g["graph"].replay()
+            LAUNCHES[0] += g["launches"]
+            return g["logits"]
+        dev = stage[:n_meta].to(self.device, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[self._flip] = ev
+        ctx_lens = buf[spans["ctx"][0]:spans["ctx"][0] + B].tolist()
+        ctx, tabs, logit_rows = self._context(dev, spans, tables, q_lens, ctx_lens, max_total)
+        return self.model.forward(ctx, self.cache.bindings(tabs), logit_rows, max_layers)
+
+    def _capture(self, g: dict, spans, tables, q_lens, ctx_lens, max_total_len: int, slots) -> None:
+        """Captures the forward pass over g["meta"] as a CUDA graph (see _run_decode_graph)."""
+        from ..ops._lib import LAUNCHES
+        ctx, tabs, logit_rows = self._context(g["meta"], spans, tables, q_lens, ctx_lens, max_total_len)
+        bindings = self.cache.bindings(tabs)
+        # One eager run loads every kernel this shape uses; fixed-size state is
+        # put back afterwards, because the captured run will update it again.
+        slot_idx = torch.tensor(slots, dtype=torch.long, device=self.device)
+        saved = [s[:, slot_idx].clone() for s in self.cache.states]
+        self.model.forward(ctx, bindings, logit_rows)
+        for s, keep in zip(self.cache.states, saved):
+            s[:, slot_idx] = keep
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = LAUNCHES[0]
+        with torch.cuda.graph(graph):
+            g["logits"] = self.model.forward(ctx, bindings, logit_rows)
+        g["graph"] = graph
+        g["launches"] = LAUNCHES[0] - before     # kernels one replay runs
+        LAUNCHES[0] = before
 
     def run(self, entries: Sequence[StepEntry], max_layers: Optional[int] = None) -> Optional[torch.Tensor]:
         """Runs one step; returns float32 logits [number of wanted places, vocab] in
@@ -220,6 +286,13 @@ class StepRunner:
         self.steps += 1
         self.tokens += ctx.T
         return logits
+
+    def check_rarely(self, every: int = 64) -> None:
+        """check() once in `every` calls: reading the error word back costs a
+        round trip to the device, and a fault does not go away."""
+        self._check_calls = getattr(self, "_check_calls", 0) + 1
+        if self._check_calls % every == 1:
+            self.check()
 
     def check(self) -> None:
         """Raises if a kernel flagged a fault since the last check (synchronises)."""
