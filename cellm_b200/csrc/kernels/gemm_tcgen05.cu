@@ -86,6 +86,24 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
 }
 
+// ---- thread-block clusters: barrier over all threads of all CTAs, and reads of a peer's shared memory
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ float ld_peer_shared(const float* local, uint32_t rank) {
+    uint32_t addr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -151,10 +169,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int BN, int STAGES>
+// RED: floats of a tile kept for the sum of K-split pieces inside a thread-block cluster.
+template <int BN, int STAGES, int RED = 0>
 struct alignas(1024) GemmSmem {
     uint8_t a[STAGES][BM * BK * 2];
     uint8_t b[STAGES][BN * BK * 2];
+    float red[RED > 0 ? RED : 1];
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_full;
@@ -219,13 +239,21 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 // its piece is written; the CTA that finds the counter at split_k - 1 sums all
 // pieces in the order of the splits, writes the output and sets the counter
 // back to zero. No CTA waits for another.
-template <int BN, int STAGES, bool SWAP, int EPI, typename TO>
+//
+// CLUSTER (swapped tiles only): the CTAs of a tile's K split form one thread-block
+// cluster (gridDim.z of them, at most 8). Each keeps its piece in its own shared
+// memory; after a cluster barrier every CTA sums, in the order of the ranks, the
+// pieces of its share of the tile's tokens, reading the peers' memory directly, and
+// writes those outputs. No workspace, no counter, no fence to global memory.
+template <int BN, int STAGES, bool SWAP, int EPI, bool CLUSTER, typename TO>
 __global__ void __launch_bounds__(192, SWAP ? 2 : 1)      // swapped tiles: two CTAs an SM, so the next product's can move in early
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                     TO* __restrict__ C, float* __restrict__ ws, int* __restrict__ counters, int M, int N, int K,
                     long long ldc, int kblocks_per_split, int w_is_static, int* __restrict__ err) {
+    static_assert(!CLUSTER || SWAP, "the cluster reduction serves swapped tiles");
     extern __shared__ uint8_t smem_raw[];
-    auto& sm = *reinterpret_cast<GemmSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    using Smem = GemmSmem<BN, STAGES, CLUSTER ? BN * BM : 0>;
+    auto& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p0 = (SWAP ? blockIdx.x : blockIdx.y) * BM;    // first row of the 128-row operand
@@ -311,8 +339,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         const int pl = qtr * 32 + lane;               // row of the tile this thread holds
         const int p = p0 + pl;
         const uint32_t lane_addr = tmem + ((uint32_t)(qtr * 32) << 16);
-        const bool through_ws = splits > 1 || (EPI == 1 && SWAP);
-        if (ok && !through_ws) {
+        const bool through_ws = !CLUSTER && (splits > 1 || (EPI == 1 && SWAP));
+        if constexpr (CLUSTER) {
+            // this CTA's piece, token-major: red[token of the tile][row of the tile]
+            constexpr int W = BN < 32 ? 16 : 32;
+#pragma unroll 1
+            for (int c = 0; c < BN / W; ++c) {
+                uint32_t r[W];
+                if (ok) {
+                    if constexpr (W == 16) tmem_ld16(lane_addr + (uint32_t)(c * W), r);
+                    else tmem_ld32(lane_addr + (uint32_t)(c * W), r);
+                }
+#pragma unroll
+                for (int j = 0; j < W; ++j) sm.red[(c * W + j) * BM + pl] = ok ? __uint_as_float(r[j]) : 0.f;
+            }
+        }
+        if (ok && !through_ws && !CLUSTER) {
             if constexpr (EPI == 0 && !SWAP) {
                 const bool aligned = ((reinterpret_cast<uintptr_t>(C) | (uintptr_t)(ldc * sizeof(TO))) & 15) == 0 &&
                                      ((q0 * sizeof(TO)) & 15) == 0;
@@ -471,6 +513,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 }
             }
         }
+    }
+    if constexpr (CLUSTER) {
+        cluster_sync_all();                     // every piece is in its CTA's shared memory
+        if (warp >= 2 && !*abort_flag) {
+            const int pl = (warp & 3) * 32 + lane, p = p0 + pl;
+            const uint32_t rank = cluster_rank();
+            const int q_end = min(Q, q0 + BN);
+            // tokens rank, rank + splits, ... of the tile are summed and written by this CTA
+            for (int q = q0 + (int)rank; q < q_end; q += splits) {
+                const float* mine = &sm.red[(q - q0) * BM + pl];
+                if constexpr (EPI == 0) {
+                    float acc = 0.f;
+                    for (int r = 0; r < splits; ++r) acc += ld_peer_shared(mine, (uint32_t)r);
+                    if (p < P) C[(size_t)q * ldc + p] = from_float<TO>(acc);
+                } else {
+                    if (pl < 64) {
+                        float g = 0.f, u = 0.f;
+                        for (int r = 0; r < splits; ++r) { g += ld_peer_shared(mine, (uint32_t)r); u += ld_peer_shared(mine + 64, (uint32_t)r); }
+                        if (p + 64 < P) C[(size_t)q * ldc + (p0 / 2 + pl)] = from_float<TO>(silu_mul(g, u));
+                    }
+                }
+            }
+        }
+        cluster_sync_all();                     // nobody leaves while a peer may still read its memory
     }
     tc_fence_before();
     __syncthreads();
@@ -679,21 +745,38 @@ bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
     return true;
 }
 
-template <int BN, int STAGES, bool SWAP, int EPI, typename TO>
+template <int BN, int STAGES, bool SWAP, int EPI, bool CLUSTER, typename TO>
 int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* ws, int* counters, int M, int N, int K,
            long long ldc, int split_k, int kblocks_per_split, int w_is_static, int* err, cudaStream_t stream) {
-    const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+    const size_t smem = sizeof(GemmSmem<BN, STAGES, CLUSTER ? BN * BM : 0>) + 1024;
     static bool configured = false;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, EPI, CLUSTER, TO>;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, SWAP, EPI, TO>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid = SWAP ? dim3((unsigned)((N + BM - 1) / BM), (unsigned)((M + BN - 1) / BN), (unsigned)split_k)
                      : dim3((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)split_k);
-    cudaError_t e = cellm_launch(gemm_tcgen05_kernel<BN, STAGES, SWAP, EPI, TO>, grid, dim3(192), smem, stream, m_rows,
-                                 m_cols, C, ws, counters, M, N, K, ldc, kblocks_per_split, w_is_static, err);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = cellm_pdl_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (CLUSTER) {      // the K split of a tile is one cluster along z
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 1;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = (unsigned)split_k;
+        cfg.numAttrs = 2;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, m_rows, m_cols, C, ws, counters, M, N, K, ldc, kblocks_per_split,
+                                       w_is_static, err);
     return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
@@ -762,10 +845,14 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
     long long ws_floats;
     int split;
     cellm_gemm_tcgen05_plan(M, N, K, bn, split_k, epilogue, &ws_floats, &split);
+    static const bool use_cluster = [] { const char* e = std::getenv("CELLM_B200_CLUSTER_REDUCE"); return !(e && e[0] == '0'); }();
+    // swapped tiles whose K split fits a cluster (2..8 CTAs, one token tile) sum their pieces through shared memory
+    const bool in_cluster = swap && split >= 2 && split <= 8 && M <= narrow && use_cluster;
+    if (in_cluster) ws_floats = 0;
     const int kblocks = (K + BK - 1) / BK;
     const int per = (kblocks + split - 1) / split;
     if (ws_floats > 0 && workspace == nullptr) return CELLM_ERR_ARG;
-    if (split > 1) {
+    if (split > 1 && !in_cluster) {
         if (counters == nullptr) return CELLM_ERR_ARG;
         const long long tiles = swap ? (long long)((N + BM - 1) / BM) * ((M + narrow - 1) / narrow)
                                      : (long long)((N + narrow - 1) / narrow) * ((M + BM - 1) / BM);
@@ -789,10 +876,17 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
 #undef GOP
         return rc;
     }
-#define GO2(BN_, ST_, SW_, EP_)                                                                                       \
+#define GO3(BN_, ST_, SW_, EP_, CL_)                                                                                  \
     do {                                                                                                              \
-        if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, EP_, float>(m_rows, m_cols, (float*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
-        else rc = launch<BN_, ST_, SW_, EP_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
+        if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, EP_, CL_, float>(m_rows, m_cols, (float*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
+        else rc = launch<BN_, ST_, SW_, EP_, CL_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
+    } while (0)
+#define GO2(BN_, ST_, SW_, EP_) GO3(BN_, ST_, SW_, EP_, false)
+    // swapped: ST_ stages without, CST_ stages with the cluster's reduction buffer (two CTAs must still fit an SM)
+#define GOS(BN_, ST_, CST_)                                                                                           \
+    do {                                                                                                              \
+        if (in_cluster) { if (epilogue == 0) GO3(BN_, CST_, true, 0, true); else GO3(BN_, CST_, true, 1, true); }      \
+        else { if (epilogue == 0) GO3(BN_, ST_, true, 0, false); else GO3(BN_, ST_, true, 1, false); }                 \
     } while (0)
 #define GO(BN_, ST_, SW_)                           \
     do {                                            \
@@ -800,9 +894,9 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
         else GO2(BN_, ST_, SW_, 1);                 \
     } while (0)
     if (swap) {
-        if (narrow == 16) GO(16, 5, true);
-        else if (narrow == 32) GO(32, 5, true);
-        else GO(64, 4, true);
+        if (narrow == 16) GOS(16, 5, 4);
+        else if (narrow == 32) GOS(32, 5, 4);
+        else GOS(64, 4, 3);
     } else {
         if (narrow == 64) GO2(64, 8, false, 0);
         else if (narrow == 128) GO(128, 6, false);
@@ -810,5 +904,7 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
     }
 #undef GO
 #undef GO2
+#undef GO3
+#undef GOS
     return rc;
 }

@@ -2,6 +2,8 @@
 tile shape and K split for the sizes at hand."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ._lib import check, fn, ptr, stream_of, tag
@@ -12,6 +14,7 @@ _WORKSPACE: dict[torch.device, torch.Tensor] = {}
 _COUNTERS: dict[torch.device, torch.Tensor] = {}
 _ERR: dict[torch.device, torch.Tensor] = {}
 MAX_COUNTERS = 65536
+_CLUSTER_REDUCE = os.environ.get("CELLM_B200_CLUSTER_REDUCE", "1") != "0"
 
 
 def _sms(device) -> int:
@@ -61,7 +64,7 @@ def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
         tiles = (N + 127) // 128
         # about one CTA per SM (its stage ring alone keeps ~90 KB of loads in flight), at
         # least four K blocks each; few splits keep the final sum of the pieces short
-        split = max(1, min(sms // tiles, kblocks // 4))
+        split = max(1, min(sms // tiles, kblocks // 4, 8))     # at most 8: the split of a tile is one cluster
         return -narrow, split
     bn = 256 if N >= 256 else (128 if N > 64 else 64)
     tiles = ((N + bn - 1) // bn) * ((M + 127) // 128)
@@ -87,9 +90,12 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bn: i
     N = w.shape[0]
     c = torch.empty((M, N // 2 if epilogue else N), dtype=out_dtype, device=a.device)
     split = _effective_split(K, split_k)
-    through_ws = split > 1 or (epilogue == 1 and bn < 0)
+    # swapped tiles whose K split is one thread-block cluster (2..8 CTAs) sum their pieces
+    # through shared memory: no workspace, no counters
+    in_cluster = bn < 0 and 2 <= split <= 8 and M <= -bn and _CLUSTER_REDUCE
+    through_ws = not in_cluster and (split > 1 or (epilogue == 1 and bn < 0))
     ws = _workspace(a.device, split * M * N) if through_ws else None
-    counters = _counters(a.device) if split > 1 else None
+    counters = _counters(a.device) if (split > 1 and not in_cluster) else None
     err = err if err is not None else error_word(a.device)
     check(fn("gemm_tcgen05", "cellm_gemm_tcgen05")(
         ptr(c), ptr(a), ptr(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), tag(out_dtype), int(bn),
