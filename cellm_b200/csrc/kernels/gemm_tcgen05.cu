@@ -298,8 +298,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             }
             // Static weights beyond the ring are asked into L2 meanwhile, so that after
             // the wait they stream from there; up to 64 blocks (1 MiB of weights) a CTA.
-            if (w_is_static)
-                for (int i = early; i < nkb && i < early + 64; ++i) tma_prefetch_l2_2d(map_w, (kb0 + i) * BK, w0);
+            if (w_is_static > 1)
+                for (int i = early; i < nkb && i < early + w_is_static; ++i) tma_prefetch_l2_2d(map_w, (kb0 + i) * BK, w0);
             pdl_wait();
             for (int i = 0; i < early; ++i)
                 tma_load_2d(SWAP ? (void*)sm.b[i] : (void*)sm.a[i], map_x, (kb0 + i) * BK, x0, &sm.full[i]);
@@ -826,7 +826,8 @@ CELLM_API int cellm_gemm_tcgen05_plan(int M, int N, int K, int bn, int split_k, 
 // [M, N/2]. bn > 0: plain tiles of 128 rows of A by bn (64, 128, 256) rows of W;
 // bn < 0: swapped tiles of 128 rows of W by -bn (16, 32, 64) rows of A.
 // w_is_static: W is a weight that no kernel on the stream writes, so its loads may
-// start before the preceding kernel has finished.
+// start before the preceding kernel has finished (a value n > 1 also asks up to n
+// further K blocks of the CTA's weights into L2 while it waits).
 // workspace: as many floats as cellm_gemm_tcgen05_plan says; counters: GEMM_MAX_COUNTERS
 // zeroed ints that products on one stream may share (each product leaves them zero).
 CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
@@ -847,7 +848,8 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
     cellm_gemm_tcgen05_plan(M, N, K, bn, split_k, epilogue, &ws_floats, &split);
     static const bool use_cluster = [] { const char* e = std::getenv("CELLM_B200_CLUSTER_REDUCE"); return !(e && e[0] == '0'); }();
     // swapped tiles whose K split fits a cluster (2..8 CTAs, one token tile) sum their pieces through shared memory
-    const bool in_cluster = swap && split >= 2 && split <= 8 && M <= narrow && use_cluster;
+    // (an unsplit SwiGLU tile takes the same road as a cluster of one: gate and up meet in shared memory)
+    const bool in_cluster = swap && M <= narrow && use_cluster && ((split >= 2 && split <= 8) || (split == 1 && epilogue == 1));
     if (in_cluster) ws_floats = 0;
     const int kblocks = (K + BK - 1) / BK;
     const int per = (kblocks + split - 1) / split;

@@ -14,6 +14,7 @@ _WORKSPACE: dict[torch.device, torch.Tensor] = {}
 _COUNTERS: dict[torch.device, torch.Tensor] = {}
 _ERR: dict[torch.device, torch.Tensor] = {}
 MAX_COUNTERS = 65536
+_STATIC_FLAG = max(1, int(os.environ.get("CELLM_B200_L2_PREFETCH_BLOCKS", "1")))
 _CLUSTER_REDUCE = os.environ.get("CELLM_B200_CLUSTER_REDUCE", "1") != "0"
 
 
@@ -62,9 +63,15 @@ def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
     if M <= 64:
         narrow = 16 if M <= 16 else (32 if M <= 32 else 64)
         tiles = (N + 127) // 128
-        # about one CTA per SM (its stage ring alone keeps ~90 KB of loads in flight), at
-        # least four K blocks each; few splits keep the final sum of the pieces short
-        split = max(1, min(sms // tiles, kblocks // 4, 8))     # at most 8: the split of a tile is one cluster
+        # Enough CTAs to fill the SMs, and no CTA with much more than ~300 KB of weights to
+        # stream by itself; at most 8 (the split of a tile is one thread-block cluster) and
+        # at least four K blocks each. Products with tiles to spare are not split.
+        if tiles >= 2 * sms:
+            split = 1
+        else:
+            fill = -(-(sms * 85 // 100) // tiles)
+            stream = -(-(128 * K * 2) // (300 * 1024))
+            split = max(1, min(max(fill, stream), kblocks // 4, 8))
         return -narrow, split
     bn = 256 if N >= 256 else (128 if N > 64 else 64)
     tiles = ((N + bn - 1) // bn) * ((M + 127) // 128)
@@ -92,14 +99,14 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bn: i
     split = _effective_split(K, split_k)
     # swapped tiles whose K split is one thread-block cluster (2..8 CTAs) sum their pieces
     # through shared memory: no workspace, no counters
-    in_cluster = bn < 0 and 2 <= split <= 8 and M <= -bn and _CLUSTER_REDUCE
+    in_cluster = bn < 0 and M <= -bn and _CLUSTER_REDUCE and (2 <= split <= 8 or (split == 1 and epilogue == 1))
     through_ws = not in_cluster and (split > 1 or (epilogue == 1 and bn < 0))
     ws = _workspace(a.device, split * M * N) if through_ws else None
     counters = _counters(a.device) if (split > 1 and not in_cluster) else None
     err = err if err is not None else error_word(a.device)
     check(fn("gemm_tcgen05", "cellm_gemm_tcgen05")(
         ptr(c), ptr(a), ptr(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), tag(out_dtype), int(bn),
-        int(split_k), int(epilogue), 1 if w_is_static else 0, ptr(ws), ptr(counters), ptr(err), stream_of(a)),
+        int(split_k), int(epilogue), _STATIC_FLAG if w_is_static else 0, ptr(ws), ptr(counters), ptr(err), stream_of(a)),
         "gemm_tcgen05")
     return c
 
