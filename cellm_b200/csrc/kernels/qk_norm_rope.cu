@@ -98,6 +98,74 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
     }
 }
 
+// Fast form for long batches of bfloat16 rows with 64-wide heads turned whole in the
+// "half" layout: one warp takes one token and walks its heads; a lane holds values
+// 2l, 2l+1 of a head, whose rotation partners (+-32) sit in lane l ^ 16, so a head
+// needs no shared memory: one 4-byte load, five shuffles for the norm, one for the
+// partner, one 4-byte store.
+template <typename TW>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_hd64_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv, long long row_stride,
+                         const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
+                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                         const int* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ k_pool,
+                         __nv_bfloat16* __restrict__ v_pool, int num_pages, int page_size, int T, int nh, int nkv,
+                         const float* __restrict__ inv_freq, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const int pos = positions[t];
+    // this lane's two frequencies: f = (2l mod 32) + {0, 1}
+    const int f0 = (2 * lane) & 31;
+    float cs[2], sn[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const float hi = inv_freq[2 * (f0 + j)], lo = inv_freq[2 * (f0 + j) + 1], fp = (float)pos;
+        const float a = fp * hi;
+        const float e = fmaf(fp, hi, -a) + fp * lo;
+        float s, c, se, ce;
+        sincosf(a, &s, &c);
+        sincosf(e, &se, &ce);
+        cs[j] = c * ce - s * se;
+        sn[j] = s * ce + c * se;
+    }
+    const float sign = lane < 16 ? -1.f : 1.f;        // first half: x0 cos - x1 sin; second half: x1 cos + x0 sin
+    float wq[2] = {1.f, 1.f}, wk[2] = {1.f, 1.f};
+    if (q_w) { wq[0] = to_float(q_w[2 * lane]); wq[1] = to_float(q_w[2 * lane + 1]); wk[0] = to_float(k_w[2 * lane]); wk[1] = to_float(k_w[2 * lane + 1]); }
+    long long page_base = -1;
+    if (nkv > 0) {
+        const int b = seq_of_token[t];
+        const int page = block_table[(size_t)b * bt_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) { if (lane == 0) atomicOr(err, CELLM_DEV_BAD_PAGE); }
+        else page_base = (long long)page * nkv * page_size * 64 + (long long)(pos % page_size) * 64;
+    }
+    const __nv_bfloat16* row = qkv + (size_t)t * row_stride;
+    // blockIdx.y takes a run of the query and key heads (the last run also copies the values)
+    const int per = (nh + nkv + gridDim.y - 1) / gridDim.y;
+    const int h_begin = blockIdx.y * per, h_end = min(nh + nkv, h_begin + per);
+#pragma unroll 4
+    for (int hh = h_begin; hh < h_end; ++hh) {
+        const bool is_q = hh < nh;
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + (size_t)hh * 64 + 2 * lane));
+        float n0 = v.x, n1 = v.y;
+        if (q_w) {
+            const float inv = 1.0f / sqrtf(warp_sum(v.x * v.x + v.y * v.y) / 64.f + eps);
+            n0 = v.x * inv * (is_q ? wq[0] : wk[0]);
+            n1 = v.y * inv * (is_q ? wq[1] : wk[1]);
+        }
+        const float p0 = __shfl_xor_sync(0xffffffffu, n0, 16), p1 = __shfl_xor_sync(0xffffffffu, n1, 16);
+        const __nv_bfloat162 o = __floats2bfloat162_rn(n0 * cs[0] + sign * p0 * sn[0], n1 * cs[1] + sign * p1 * sn[1]);
+        if (is_q) *reinterpret_cast<__nv_bfloat162*>(q_out + (size_t)t * nh * 64 + (size_t)hh * 64 + 2 * lane) = o;
+        else if (page_base >= 0) *reinterpret_cast<__nv_bfloat162*>(k_pool + page_base + (long long)(hh - nh) * page_size * 64 + 2 * lane) = o;
+    }
+    if (page_base >= 0 && blockIdx.y == gridDim.y - 1)
+        for (int hh = 0; hh < nkv; ++hh)
+            *reinterpret_cast<uint32_t*>(v_pool + page_base + (long long)hh * page_size * 64 + 2 * lane) =
+                *reinterpret_cast<const uint32_t*>(row + (size_t)(nh + nkv + hh) * 64 + 2 * lane);
+}
+
 // qkv: [T, row_stride] rows holding nh query heads, then nkv key heads, then nkv
 // value heads (nkv = 0: queries only, nothing is written to the cache).
 // q_w, k_w: [hd] norm weights or null (no norm). inv_freq: [rot/2] pairs of floats
@@ -111,6 +179,22 @@ CELLM_API int cellm_qk_norm_rope(void* q_out, const void* qkv, long long row_str
     if (T <= 0) return CELLM_OK;
     if (rot < 0 || rot > hd || (rot & 1)) return CELLM_ERR_SIZE;
     if ((q_w == nullptr) != (k_w == nullptr)) return CELLM_ERR_ARG;
+    if (act_dtype == CELLM_BF16 && hd == 64 && rot == 64 && !interleaved && T >= 256 && (row_stride & 1) == 0 &&
+        (((uintptr_t)q_out | (uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) & 3) == 0) {
+        const dim3 blocks((unsigned)((T + 3) / 4), (unsigned)((nh + nkv + 7) / 8));
+        if (w_dtype == CELLM_BF16 || q_w == nullptr)
+            CELLM_RUN(qk_norm_rope_hd64_kernel<__nv_bfloat16>, blocks, 128, 0, stream, (__nv_bfloat16*)q_out,
+                      (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, eps,
+                      positions, seq_of_token, block_table, bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+                      num_pages, page_size, T, nh, nkv, inv_freq, err);
+        else if (w_dtype == CELLM_F32)
+            CELLM_RUN(qk_norm_rope_hd64_kernel<float>, blocks, 128, 0, stream, (__nv_bfloat16*)q_out,
+                      (const __nv_bfloat16*)qkv, row_stride, (const float*)q_w, (const float*)k_w, eps, positions,
+                      seq_of_token, block_table, bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, num_pages,
+                      page_size, T, nh, nkv, inv_freq, err);
+        else return CELLM_ERR_DTYPE;
+        return CELLM_OK;
+    }
     const int threads = 128;
     // few tokens: spread each token's heads over blocks of four (one per warp); many tokens: one block each
     const int heads_all = nh + 2 * nkv;

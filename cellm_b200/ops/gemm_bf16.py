@@ -74,6 +74,13 @@ def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
             split = max(1, min(max(fill, stream), kblocks // 4, 8))
         return -narrow, split
     bn = 256 if N >= 256 else (128 if N > 64 else 64)
+    if bn == 256:
+        # 128-wide tiles cost about 0.55 of a 256-wide one; take them when their waves finish sooner
+        mt = (M + 127) // 128
+        waves256 = -(-(mt * ((N + 255) // 256)) // sms)
+        waves128 = -(-(mt * ((N + 127) // 128)) // sms)
+        if waves128 * 0.55 < waves256 * 0.95:
+            bn = 128
     tiles = ((N + bn - 1) // bn) * ((M + 127) // 128)
     split = 1
     if tiles < sms // 2:

@@ -166,6 +166,33 @@ def test_qk_norm_rope_and_page_write(dtype, hd, rot, inter):
     assert e.item() == 2
 
 
+@pytest.mark.parametrize("wdt", [torch.bfloat16, torch.float32])
+def test_qk_norm_rope_long_batches_of_64_wide_heads(wdt):
+    """300 tokens of 64-wide heads take the one-warp-per-token form; it must agree
+    with the general kernel's result on the same rows (forced by feeding them in
+    pieces shorter than 256)."""
+    from cellm_b200 import ops
+    from cellm_b200.parts.rope import split_inv_freq
+    nh, nkv, hd, ps, T = 6, 2, 64, 16, 300
+    pos = torch.arange(T, dtype=torch.int32, device=DEV) + 5
+    seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    pages = (T + 5 + ps - 1) // ps
+    bt = torch.randperm(pages).int().reshape(1, -1).to(DEV)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).bfloat16()
+    qw, kw = (torch.rand(hd, device=DEV) + 0.5).to(wdt), (torch.rand(hd, device=DEV) + 0.5).to(wdt)
+    inv = split_inv_freq(1e6, hd).to(DEV)
+    outs = []
+    for pieces in ([slice(0, T)], [slice(0, 100), slice(100, 200), slice(200, T)]):
+        kp = torch.zeros(pages, nkv, ps, hd, device=DEV, dtype=torch.bfloat16)
+        vp = torch.zeros_like(kp)
+        e = err_word()
+        q = torch.cat([ops.qk_norm_rope(qkv[sl], qw, kw, 1e-5, pos[sl], seq[sl], bt, kp, vp, ps, nh, nkv, hd, hd, False, inv, e) for sl in pieces])
+        assert e.item() == 0
+        outs.append((q, kp, vp))
+    for a, b in zip(outs[0], outs[1]):
+        assert float((a.float() - b.float()).abs().max()) <= 2 ** -7 * float(b.float().abs().max())     # one bfloat16 step
+
+
 def test_rotation_angles_stay_exact_far_out():
     """At positions in the hundreds of thousands a float angle is off by whole
     hundredths of a radian; the kernel's split arithmetic is not."""
