@@ -38,6 +38,7 @@ LIBRARIES: dict[str, tuple[str, list[str], list[str]]] = {
     "gemm_tcgen05": ("nvcc", ["kernels/gemm_tcgen05.cu"], []),
     "attention_flash": ("nvcc", ["kernels/attention_flash.cu"], []),
     "attention_decode": ("nvcc", ["kernels/attention_decode.cu"], []),
+    "attention_tc": ("nvcc", ["kernels/attention_tc.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -27,7 +27,8 @@ enum {
     CELLM_DEV_BAD_TOKEN = 1,   // token id outside the vocabulary
     CELLM_DEV_BAD_PAGE = 2,    // page id outside the pool
     CELLM_DEV_BAD_SLOT = 4,    // state slot outside the pool
-    CELLM_DEV_WAIT_TIMEOUT = 8 // a bounded wait inside a kernel gave up
+    CELLM_DEV_WAIT_TIMEOUT = 8,// a bounded wait inside a kernel gave up
+    CELLM_DEV_BAD_LAYOUT = 16  // shared memory not aligned as the kernel's tiles need
 };
 
 __device__ __forceinline__ float to_float(float v) { return v; }

@@ -34,7 +34,8 @@ class DeviceFault(RuntimeError):
 
 
 _ERR_BITS = {1: "token id outside the vocabulary", 2: "page id outside the pool",
-             4: "state slot outside the pool", 8: "a bounded wait inside a kernel gave up"}
+             4: "state slot outside the pool", 8: "a bounded wait inside a kernel gave up",
+             16: "shared memory not aligned as a kernel's tiles need"}
 
 
 class StepRunner:

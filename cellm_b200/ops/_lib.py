@@ -34,6 +34,10 @@ _SIGNATURES = {
     "attention_decode": {
         "cellm_attention_decode": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
     },
+    "attention_tc": {
+        "cellm_attention_tc": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
+        "cellm_attention_tc_supports": [I, I, I, I],
+    },
     "attention_flash": {
         "cellm_attention_flash": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P],
         "cellm_attention_flash_supports": [I],

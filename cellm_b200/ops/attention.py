@@ -6,6 +6,9 @@ from ._lib import check, count_launch, fn, ptr, require_cuda, stream_of
 from .basic import attention_plain
 
 _FLASH_HEAD_SIZES = (32, 64, 128)
+# When prompt portions go to the tcgen05 kernel: at least `min_ctas` CTAs (None: one per SM)
+# and at least `min_fill` of the tiles' rows in use. Tests lower both to drive small cases there.
+TC_POLICY = {"min_ctas": None, "min_fill": 0.5}
 _WORKSPACE: dict[torch.device, torch.Tensor] = {}
 
 
@@ -87,11 +90,42 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     return out
 
 
+def attention_tc_supports(hd: int, nh: int, nkv: int, page_size: int) -> bool:
+    """Sizes the tcgen05 prompt kernel takes: heads of 64, a group size that divides 128,
+    pages of 8 to 128 tokens (powers of two)."""
+    if hd != 64 or nkv <= 0 or nh % nkv:
+        return False
+    g = nh // nkv
+    return g <= 128 and 128 % g == 0 and page_size in (8, 16, 32, 64, 128)
+
+
+def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, cu_seqlens: torch.Tensor,
+                 ctx_lens: torch.Tensor, block_table: torch.Tensor, q_lens: list[int], nh: int, scale: float,
+                 window: int, err: torch.Tensor) -> torch.Tensor:
+    """Attention for prompt portions on the tcgen05 tensor cores (scores and outputs in
+    tensor memory): bfloat16, heads of 64; arguments as attention_flash."""
+    require_cuda(q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, err)
+    pages, nkv, page_size, hd = k_pool.shape
+    if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or q.shape[1] != nh * hd \
+            or not attention_tc_supports(hd, nh, nkv, page_size) or scale <= 0:
+        raise ValueError("attention_tc: bfloat16, heads of 64, a group size dividing 128, pages of 8..128 tokens")
+    tok_per_tile = 128 // (nh // nkv)
+    n_tiles = sum((n + tok_per_tile - 1) // tok_per_tile for n in q_lens)
+    out = torch.empty_like(q)
+    check(fn("attention_tc", "cellm_attention_tc")(
+        ptr(out), ptr(q), ptr(k_pool), ptr(v_pool), ptr(cu_seqlens), ptr(ctx_lens), ptr(block_table),
+        block_table.stride(0), len(q_lens), q.shape[0], n_tiles, pages, page_size, nh, nkv, hd, float(scale),
+        int(window), ptr(err), stream_of(q)), "attention_tc")
+    return out
+
+
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, block_table: torch.Tensor,
               nh: int, scale: float, window: int) -> torch.Tensor:
     """Attention of every token of the step over its request's pages. bfloat16
-    with a head size the tensor-core kernel is built for runs there; everything
-    else (32-bit, other head sizes) runs the plain kernel."""
+    with a head size the tensor-core kernels are built for runs there (decoded
+    tokens in the decode kernel, large batches of prompt tokens with heads of 64
+    on tcgen05, the rest on mma.sync); everything else (32-bit, other head sizes)
+    runs the plain kernel."""
     hd = k_pool.shape[3]
     if q.dtype == torch.bfloat16 and hd in _FLASH_HEAD_SIZES and scale > 0:
         from .gemm_bf16 import _sms
@@ -101,6 +135,14 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, 
             nsplit = max(1, min(4 * _sms(q.device) // (ctx.B * k_pool.shape[1]), blocks // 4))
             return attention_decode(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.B, nh, scale,
                                     window, ctx.err, nsplit)
+        # prompt portions that fill the 128-row tiles of the tcgen05 kernel and at least one CTA per SM
+        if attention_tc_supports(hd, nh, k_pool.shape[1], k_pool.shape[2]):
+            per_tile = 128 // G
+            tc_tiles = sum((n + per_tile - 1) // per_tile for n in ctx.q_lens)
+            min_ctas = _sms(q.device) if TC_POLICY["min_ctas"] is None else TC_POLICY["min_ctas"]
+            if tc_tiles * k_pool.shape[1] >= min_ctas and ctx.T >= TC_POLICY["min_fill"] * tc_tiles * per_tile:
+                return attention_tc(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.q_lens, nh,
+                                    scale, window, ctx.err)
         wide = ctx.max_q_len * G > 16
         bm = 64 if wide else 16
         n_tiles = sum((n * G + bm - 1) // bm for n in ctx.q_lens)

@@ -267,13 +267,13 @@ def test_attention_plain(dtype, nh, nkv, hd, ps, window):
     close(out, attention_reference(c, nh, nkv, hd, hd ** -0.5, window), dtype)
 
 
-@pytest.mark.parametrize("kernel", ["plain32", "plain16", "flash", "decode"])
+@pytest.mark.parametrize("kernel", ["plain32", "plain16", "flash", "decode", "tc"])
 def test_a_far_key_among_hundreds_is_found(kernel):
     """One early key is scaled so that its score towers over 600 others: the
     output must be that key's value. A kernel that skips a page, stops short or
     reads a neighbour's page cannot pass."""
     from cellm_b200 import ops
-    from cellm_b200.ops.attention import attention_decode, attention_flash
+    from cellm_b200.ops.attention import attention_decode, attention_flash, attention_tc
     dtype = torch.float32 if kernel == "plain32" else torch.bfloat16
     nh, nkv, hd, ps = 4, 2, 64, 16
     for far in (0, 15, 16, 337):                       # a page's first and last slot, and the middle of nowhere
@@ -285,6 +285,8 @@ def test_a_far_key_among_hundreds_is_found(kernel):
             out = attention_flash(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], nh, 1.0, 0, e, nsplit=3)
         elif kernel == "decode":
             out = attention_decode(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], 2, nh, 1.0, 0, e, nsplit=3)
+        elif kernel == "tc":
+            out = attention_tc(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], nh, 1.0, 0, e)
         else:
             out = ops.attention_plain(c["q"], c["kp"], c["vp"], c["pos"], c["seq"], c["bt"], nh, 1.0, 0, e)
         assert e.item() == 0
@@ -306,6 +308,34 @@ def test_attention_flash(hd, ps, nh, nkv, window):
     out = attention_flash(d["q"], d["kp"], d["vp"], d["cu"], d["ctx"], d["bt"], d["q_lens"], nh, hd ** -0.5, window, e, 4, False)
     close(out, attention_reference(d, nh, nkv, hd, hd ** -0.5, window), torch.bfloat16, "decode")
     assert e.item() == 0
+
+
+@pytest.mark.parametrize("ps,nh,nkv", [(16, 8, 2), (8, 2, 2), (32, 16, 1), (128, 32, 8), (64, 3, 3)])
+@pytest.mark.parametrize("window", [0, 33, 300])
+def test_attention_tc(ps, nh, nkv, window):
+    """The tcgen05 prompt kernel: portions that end inside a tile, start after a
+    context, span several key blocks; single tokens beside them; a window that
+    skips whole blocks. With scale 1 the scores spread so far that the lazy
+    rescaling of the accumulator runs."""
+    from cellm_b200.ops.attention import attention_tc, attention_tc_supports
+    hd = 64
+    assert attention_tc_supports(hd, nh, nkv, ps)
+    c = paged_case([300, 1, 33, 129], [0, 500, 59, 640], nh, nkv, hd, ps, torch.bfloat16, seed=6)
+    e = err_word()
+    for scale in (hd ** -0.5, 1.0):
+        for _ in range(2):
+            out = attention_tc(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], nh, scale, window, e)
+            close(out, attention_reference(c, nh, nkv, hd, scale, window), torch.bfloat16, f"scale {scale}")
+    assert e.item() == 0
+
+
+def test_attention_tc_refuses_what_it_does_not_take():
+    from cellm_b200.ops.attention import attention_tc, attention_tc_supports
+    assert not attention_tc_supports(128, 4, 4, 16) and not attention_tc_supports(64, 6, 2, 16)
+    assert not attention_tc_supports(64, 4, 2, 4) and not attention_tc_supports(64, 4, 2, 24)
+    c = paged_case([40], [0], 6, 2, 64, 16, torch.bfloat16, seed=1)
+    with pytest.raises(ValueError):
+        attention_tc(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], 6, 0.125, 0, err_word())
 
 
 @pytest.mark.parametrize("hd,ps,nh,nkv", [(32, 8, 3, 1), (64, 16, 8, 2), (128, 32, 4, 4), (64, 4, 32, 8), (64, 16, 16, 1)])
@@ -331,9 +361,10 @@ def test_window_edge():
     the key just inside does."""
     from cellm_b200 import ops
     from cellm_b200.ops.attention import attention_flash
-    nh, nkv, hd, ps, window = 2, 1, 32, 8, 24
-    from cellm_b200.ops.attention import attention_decode
-    for dtype, kernel in ((torch.float32, "plain"), (torch.bfloat16, "plain"), (torch.bfloat16, "flash"), (torch.bfloat16, "decode")):
+    nh, nkv, hd, ps, window = 2, 1, 64, 8, 24
+    from cellm_b200.ops.attention import attention_decode, attention_tc
+    for dtype, kernel in ((torch.float32, "plain"), (torch.bfloat16, "plain"), (torch.bfloat16, "flash"), (torch.bfloat16, "decode"),
+                          (torch.bfloat16, "tc")):
         for edge, inside in ((100 - window, False), (100 - window + 1, True)):
             c = paged_case([1], [100], nh, nkv, hd, ps, dtype, seed=4)
             kh = c["k_seq"][0][edge, 0]
@@ -343,6 +374,8 @@ def test_window_edge():
                 out = attention_flash(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], nh, 1.0, window, e)
             elif kernel == "decode":
                 out = attention_decode(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], 1, nh, 1.0, window, e, 2)
+            elif kernel == "tc":
+                out = attention_tc(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], c["q_lens"], nh, 1.0, window, e)
             else:
                 out = ops.attention_plain(c["q"], c["kp"], c["vp"], c["pos"], c["seq"], c["bt"], nh, 1.0, window, e)
             hit = float((out[0, :hd].float().cpu() - c["v_seq"][0][edge, 0]).abs().max()) < 0.05

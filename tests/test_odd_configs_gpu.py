@@ -61,6 +61,36 @@ def test_odd_configuration_in_every_cutting(tmp_path, name, dtype):
             check_close(traces.as_matrix(got[r], len(t)), ref[r], dtype, f"{name} {dtype} {make.__name__} {r}")
 
 
+@pytest.mark.parametrize("name,page", [("g16", 16), ("g16", 8), ("hd64g2", 32)])
+def test_prompt_attention_on_tcgen05_in_every_cutting(tmp_path, monkeypatch, name, page):
+    """Small portions are sent to the tcgen05 prompt kernel (which otherwise takes
+    only batches that fill the GPU): same traces, same plain implementation."""
+    import importlib
+    from cellm_b200.replay import Replayer
+    from cellm_b200.weights import write_random_model
+    att = importlib.import_module("cellm_b200.ops.attention")        # the module, not the function of that name
+    monkeypatch.setitem(att.TC_POLICY, "min_ctas", 0)
+    monkeypatch.setitem(att.TC_POLICY, "min_fill", 0.0)
+    calls = []
+    real = att.attention_tc
+    monkeypatch.setattr(att, "attention_tc", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    config = ODD["g16"][0] if name == "g16" else cfg(
+        vocab_size=900, hidden_size=192, num_hidden_layers=3, layer_types=["full_attention", "conv", "full_attention"],
+        num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=320)
+    folder = write_random_model(str(tmp_path / name), config, seed=32, dtype="bfloat16", init=TEST_INIT)
+    c, w = plain.load_folder(folder)
+    rng = np.random.default_rng(8)
+    reqs = {f"r{i}": rng.integers(0, config["vocab_size"], n).tolist() for i, n in enumerate((150, 9, 300, 67))}
+    ref = {r: plain.forward(c, w, t).numpy() for r, t in reqs.items()}
+    for make in (traces.whole, traces.tail_one_by_one, traces.portions, traces.mixed):
+        steps = make(reqs)
+        rp = Replayer(folder, "bfloat16", traces.max_live_tokens(steps), page, 4)
+        got = traces.collect(steps, [rp.step(s["entries"], s["end"]) for s in steps])
+        for r, t in reqs.items():
+            check_close(traces.as_matrix(got[r], len(t)), ref[r], "bfloat16", f"{name} tc {make.__name__} {r}")
+    assert calls
+
+
 def test_odd_configuration_generates(tmp_path):
     from cellm_b200 import Engine, SamplingParams
     from cellm_b200.weights import write_random_model
