@@ -1,22 +1,29 @@
 // Attention for prompt portions on the 5th-generation tensor cores (tcgen05),
 // over the paged cache: bfloat16, heads of 64, causal, optional window.
 //
-// One CTA takes a tile of 128 rows, the rows being (token, query head) pairs of
+// One CTA takes two tiles of 128 rows, the rows being (token, query head) pairs of
 // the heads that share one key/value head (row r = token * G + head, G heads per
-// key/value head, G a divisor of 128), and walks the request's keys in blocks of
-// 128:
-//   warp 0      TMA: the Q tile once (a 3-D box over [token][head][64]), then per
+// key/value head, G a divisor of 128; the second tile holds the next 128 / G
+// tokens), and walks the request's keys in blocks of 128; both tiles use each block
+// of K and V, which is brought in once:
+//   warp 0      TMA: the Q tiles once (3-D boxes over [token][head][64]), then per
 //               block the K and V pages through the block table (one box per page),
-//               into a two-stage ring, 128-byte swizzle;
-//   warp 1      MMA: S = Q.K^T (M 128, N 128, K 64) into one of two score buffers in
-//               tensor memory, and O += P.V (M 128, N 64, K 128) with P read from
-//               shared memory (K-major) and V as it lies in its pages (MN-major);
-//   warps 2..5  softmax, one row per thread: scores from tensor memory, mask,
-//               running maximum and sum in 32-bit, P = 2^(s*c - m) rounded to
-//               bfloat16 into shared memory in the swizzled layout the MMA reads.
-// The output accumulator stays in tensor memory; it is rescaled (read, multiplied,
-// written back) only when a row's maximum has grown by more than 2^8 since the
-// last rescale, so most blocks skip that pass; the stale maximum only scales P.
+//               into rings of three stages each, 128-byte swizzle;
+//   warp 1      MMA: per tile S = Q.K^T (M 128, N 128, K 64) into the tile's score
+//               columns of tensor memory, and O += P.V (M 128, N 64, K 128) with P read
+//               from tensor memory and V as it lies in its pages (MN-major);
+//   warps 2..5  softmax of the first tile, warps 6..9 of the second, one row per
+//               thread: the 128 scores from tensor memory into registers (the next
+//               block's product may then overwrite them), mask, running maximum and sum
+//               in 32-bit, P = 2^(s*c - m) rounded to bfloat16 into tensor memory, two keys
+//               a column, where the MMA reads it as its A operand (shared memory carries
+//               only Q, K and V: its bandwidth is what the tensor cores' operands need).
+//               Two threads a row (eight warps a tile) were measured slower: the loads
+//               from tensor memory and the exponentials of four warps a scheduler collide.
+// While one tile's softmax runs, the tensor cores work on the other tile. The output
+// accumulators stay in tensor memory; one is rescaled (read, multiplied, written
+// back) only when a row's maximum has grown by more than 2^8 since the last rescale,
+// so most blocks skip that pass; the stale maximum only scales P.
 //
 // Every wait on an mbarrier is bounded, as in gemm_tcgen05.cu: a role that gives up
 // sets CELLM_DEV_WAIT_TIMEOUT and an abort flag; the CTA frees its tensor memory and
@@ -112,6 +119,14 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with A read from tensor memory (row = lane, two bfloat16 of K in a column)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -139,6 +154,18 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -163,25 +190,35 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-constexpr int KV_STAGES = 2;
-constexpr int TMEM_COLS = 256;       // scores in columns 0..127, the output accumulator in 128..191
-constexpr int O_COL = 128;
+constexpr int KV_STAGES = 3;
+constexpr int TMEM_TN = 512;       // scores of tile 0 and 1 in columns 0 and 128, their outputs in 256 and 320,
+constexpr int O_COL = 256;           // their P (bfloat16, two keys a column) in 384 and 448
+constexpr int P_COL = 384;
+constexpr int THREADS = 320;         // warp 0 TMA, warp 1 MMA, warps 2..5 softmax of tile 0, warps 6..9 of tile 1
 
-// 112 KB and a few words: two CTAs share an SM (and its 512 columns of tensor memory).
-struct alignas(1024) TcSmem {
-    uint8_t q[TM * HD * 2];                      // 16 KB
+// 128 KB and a few words: one CTA per SM (it holds all 512 columns of tensor memory).
+struct TcSmem {                                  // starts on a 1024-byte boundary (checked in the kernel)
+    uint8_t q[2][TM * HD * 2];                   // 16 KB each
     uint8_t k[KV_STAGES][TN * HD * 2];           // 16 KB each
     uint8_t v[KV_STAGES][TN * HD * 2];
-    uint8_t p[2][TM * 64 * 2];                   // [keys 0-63 | 64-127]: 32 KB
     uint64_t q_full;
     uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
     uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
-    uint64_t s_full, s_empty, p_full, pv_done;
+    uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2];
     uint32_t tmem_base;
     int abort_flag;
 };
 
-__global__ void __launch_bounds__(192, 2)
+// The key blocks one tile of 128 rows needs: [lo, hi) in units of TN keys, and its rows' tokens.
+struct TileRange {
+    int tok0;        // first token of the tile within the portion
+    int lo, hi;      // key blocks
+    bool has;        // the tile holds at least one token
+};
+
+// Launched with 320 threads. A scheduler holds three of the ten warps and 16384 registers: 168 a thread at
+// most, which the bound of 384 threads makes the compiler keep.
+__global__ void __launch_bounds__(384, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                     const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens,
@@ -191,7 +228,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     TcSmem& sm = *reinterpret_cast<TcSmem*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = nh / nkv, kvh = blockIdx.y;
-    const int tok_per_tile = TM / G;
+    const int tok_per_tile = TM / G, tok_per_cta = 2 * tok_per_tile;
     if (smem_u32(smem_raw) & 1023u) {            // the swizzled tiles need 1024-byte alignment
         if (threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_LAYOUT);
         return;
@@ -203,19 +240,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1);
             mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1);
         }
-        mbar_init(&sm.s_full, 1);  mbar_init(&sm.s_empty, 128);
-        mbar_init(&sm.p_full, 128); mbar_init(&sm.pv_done, 1);
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&sm.s_full[t], 1);  mbar_init(&sm.s_empty[t], 128);
+            mbar_init(&sm.p_full[t], 128); mbar_init(&sm.pv_done[t], 1);
+        }
         sm.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     }
-    // K and V stages start as zeros: keys that are never loaded must not carry NaN bits into P.V (0 * NaN)
-    for (int i = threadIdx.x; i < (int)(sizeof(sm.k) + sizeof(sm.v)) / 16; i += blockDim.x)
-        reinterpret_cast<uint4*>(sm.k)[i] = make_uint4(0, 0, 0, 0);
+    // V stages start as zeros: rows that are never loaded must not carry NaN bits into P.V (0 * NaN);
+    // what K rows hold there does not matter, their scores are masked
+    for (int i = threadIdx.x; i < (int)sizeof(sm.v) / 16; i += blockDim.x)
+        reinterpret_cast<uint4*>(sm.v)[i] = make_uint4(0, 0, 0, 0);
     proxy_fence();
-    if (warp == 1) tmem_alloc(&sm.tmem_base, TMEM_COLS);
+    if (warp == 1) tmem_alloc(&sm.tmem_base, TMEM_TN);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -224,35 +264,49 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t tmem = sm.tmem_base;
     volatile int* abort_flag = &sm.abort_flag;
 
-    // which request this tile belongs to (tiles from the last to the first: longest first)
-    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    // which request this pair of tiles belongs to (from the last to the first: longest first)
+    const int item = (int)gridDim.x - 1 - (int)blockIdx.x;
     int b = 0, base = 0;
     for (; b < B; ++b) {
-        const int nt = (cu_seqlens[b + 1] - cu_seqlens[b] + tok_per_tile - 1) / tok_per_tile;
-        if (tile < base + nt) break;
+        const int nt = (cu_seqlens[b + 1] - cu_seqlens[b] + tok_per_cta - 1) / tok_per_cta;
+        if (item < base + nt) break;
         base += nt;
     }
     const bool live = b < B;
-    int t_base = 0, q_len = 0, ctx = 0, tok0 = 0, nblk = 0, key_begin = 0, key_end = 0, kb0 = 0;
+    int t_base = 0, q_len = 0, ctx = 0;
+    TileRange tr[2] = {{0, 0, 0, false}, {0, 0, 0, false}};
+    int kb0 = 0, nblk = 0, key_begin = 0, key_end = 0;
     if (live) {
         t_base = cu_seqlens[b];
         q_len = cu_seqlens[b + 1] - t_base;
         ctx = ctx_lens[b];
-        tok0 = (tile - base) * tok_per_tile;                       // first token of the tile within the portion
-        const int tok1 = min(tok0 + tok_per_tile, q_len) - 1;      // last one
-        key_end = ctx + tok1 + 1;
-        key_begin = window > 0 ? max(0, ctx + tok0 - window + 1) : 0;
-        kb0 = key_begin / TN;
-        nblk = (key_end + TN - 1) / TN - kb0;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            tr[t].tok0 = (item - base) * tok_per_cta + t * tok_per_tile;
+            tr[t].has = tr[t].tok0 < q_len;
+            if (tr[t].has) {
+                const int tok1 = min(tr[t].tok0 + tok_per_tile, q_len) - 1;
+                const int kb = window > 0 ? max(0, ctx + tr[t].tok0 - window + 1) : 0;
+                tr[t].lo = kb / TN;
+                tr[t].hi = (ctx + tok1 + 1 + TN - 1) / TN;
+                if (t == 0) key_begin = kb;
+                key_end = ctx + tok1 + 1;
+            }
+        }
+        // tile 1 holds later tokens: its blocks start and end no earlier than tile 0's
+        kb0 = tr[0].lo;
+        nblk = (tr[1].has ? tr[1].hi : tr[0].hi) - kb0;
     }
     const int* bt = block_table + (size_t)(live ? b : 0) * bt_stride;
     const int pages_per_block = TN / page_size;
+    auto active = [&](int t, int j) { return tr[t].has && kb0 + j >= tr[t].lo && kb0 + j < tr[t].hi; };
 
     if (warp == 0) {
         if (live) {
             if (lane == 0) {
-                mbar_expect_tx(&sm.q_full, TM * HD * 2);
-                tma_load_3d(sm.q, &map_q, 0, kvh * G, t_base + tok0, &sm.q_full);
+                mbar_expect_tx(&sm.q_full, (tr[1].has ? 2 : 1) * TM * HD * 2);
+                tma_load_3d(sm.q[0], &map_q, 0, kvh * G, t_base + tr[0].tok0, &sm.q_full);
+                if (tr[1].has) tma_load_3d(sm.q[1], &map_q, 0, kvh * G, t_base + tr[1].tok0, &sm.q_full);
             }
             for (int j = 0; j < nblk; ++j) {
                 const int st = j % KV_STAGES;
@@ -286,68 +340,82 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (live && lane == 0) {
             const uint32_t idesc_s = umma_idesc(TM, TN, false);      // S[128 x 128] = Q (K-major) . K^T (K-major)
             const uint32_t idesc_o = umma_idesc(TM, HD, true);       // O[128 x 64] += P (K-major) . V (MN-major)
-            const uint32_t tmem_o = tmem + O_COL;
+            int n_s[2] = {0, 0}, n_pv[2] = {0, 0};                   // products issued so far, per tile
             bool ok = mbar_wait(&sm.q_full, 0, abort_flag);
-            const uint64_t dq = umma_desc(smem_u32(sm.q));
-            const uint64_t dp0 = umma_desc(smem_u32(sm.p[0])), dp1 = umma_desc(smem_u32(sm.p[1]));
-            auto issue_s = [&](int j) {
+            // scores of block j for the tiles that need it; the softmax warps of a tile must have taken
+            // the tile's last scores out of tensor memory first
+            auto issue_s = [&](int j) -> bool {
                 const int st = j % KV_STAGES;
-                tc_fence_after();
+                if (!mbar_wait(&sm.k_full[st], (uint32_t)(j / KV_STAGES) & 1u, abort_flag)) return false;
                 const uint64_t dk = umma_desc(smem_u32(sm.k[st]));
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks)
-                    umma_bf16(tmem, dq + (uint64_t)(ks * 2), dk + (uint64_t)(ks * 2), idesc_s, ks != 0 ? 1u : 0u);
+                for (int t = 0; t < 2; ++t) {
+                    if (!active(t, j)) continue;
+                    if (n_s[t] > 0 && !mbar_wait(&sm.s_empty[t], (uint32_t)(n_s[t] - 1) & 1u, abort_flag)) return false;
+                    tc_fence_after();
+                    const uint64_t dq = umma_desc(smem_u32(sm.q[t]));
+#pragma unroll
+                    for (int ks = 0; ks < HD / 16; ++ks)
+                        umma_bf16(tmem + (uint32_t)(t * TN), dq + (uint64_t)(ks * 2), dk + (uint64_t)(ks * 2), idesc_s, ks != 0 ? 1u : 0u);
+                    umma_commit(&sm.s_full[t]);
+                    ++n_s[t];
+                }
                 umma_commit(&sm.k_empty[st]);
-                umma_commit(&sm.s_full);
+                return true;
             };
-            if (ok) ok = mbar_wait(&sm.k_full[0], 0, abort_flag);
-            if (ok) issue_s(0);
+            if (ok && nblk > 0) ok = issue_s(0);
             for (int j = 0; ok && j < nblk; ++j) {
                 const int st = j % KV_STAGES;
-                const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-                if (j + 1 < nblk) {
-                    // the scores of block j are in the softmax warps' registers: block j+1 may overwrite them
-                    ok = mbar_wait(&sm.k_full[(j + 1) % KV_STAGES], (uint32_t)((j + 1) / KV_STAGES) & 1u, abort_flag) &&
-                         mbar_wait(&sm.s_empty, (uint32_t)j & 1u, abort_flag);
-                    if (!ok) break;
-                    issue_s(j + 1);
-                }
-                ok = mbar_wait(&sm.v_full[st], ph, abort_flag) && mbar_wait(&sm.p_full, (uint32_t)j & 1u, abort_flag);
+                if (j + 1 < nblk) { ok = issue_s(j + 1); if (!ok) break; }
+                ok = mbar_wait(&sm.v_full[st], (uint32_t)(j / KV_STAGES) & 1u, abort_flag);
                 if (!ok) break;
-                tc_fence_after();
                 const uint64_t dv = umma_desc(smem_u32(sm.v[st]));
 #pragma unroll
-                for (int ks = 0; ks < TN / 16; ++ks) {
-                    const uint64_t da = (ks < 4 ? dp0 : dp1) + (uint64_t)((ks & 3) * 2);     // 16 keys = 32 bytes along a row of P
-                    const uint64_t db = dv + (uint64_t)(ks * 16 * HD * 2 / 16);               // 16 keys = 16 rows of V
-                    umma_bf16(tmem_o, da, db, idesc_o, (j | ks) != 0 ? 1u : 0u);
+                for (int t = 0; t < 2; ++t) {
+                    if (!active(t, j)) continue;
+                    ok = mbar_wait(&sm.p_full[t], (uint32_t)n_pv[t] & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < TN / 16; ++ks) {
+                        const uint32_t pa = tmem + (uint32_t)(P_COL + t * (TN / 2) + ks * 8);     // 16 keys = 8 columns of P
+                        const uint64_t db = dv + (uint64_t)(ks * 16 * HD * 2 / 16);               // 16 keys = 16 rows of V
+                        umma_bf16_ts(tmem + (uint32_t)(O_COL + t * HD), pa, db, idesc_o, (n_pv[t] | ks) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&sm.pv_done[t]);
+                    ++n_pv[t];
                 }
+                if (!ok) break;
                 umma_commit(&sm.v_empty[st]);
-                umma_commit(&sm.pv_done);
             }
             if (!ok) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); }
         }
-    } else if (live) {
-        const int r = (warp & 3) * 32 + lane;                         // row of the tile = lane of tensor memory
-        const int tok = tok0 + r / G;                                 // token within the portion
+    } else if (live && tr[(warp - 2) >> 2].has) {
+        const int t = (warp - 2) >> 2;                                // which tile
+        const int qt = warp & 3;                                      // quarter of the tile's rows = of tensor memory's lanes
+        const int r = qt * 32 + lane;                                 // row of the tile = lane of tensor memory
+        const int tok = tr[t].tok0 + r / G;                           // token within the portion
         const bool row_ok = tok < q_len;
         const int pos = row_ok ? ctx + tok : -1;
         const int lo = window > 0 ? pos - window + 1 : 0;
-        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        uint8_t* const p_row = sm.p[0] + (size_t)(r >> 3) * 1024 + (size_t)(r & 7) * 128;
+        const uint32_t lane_base = tmem + ((uint32_t)(qt * 32) << 16);
+        const uint32_t s_col = (uint32_t)(t * TN);
+        const uint32_t o_col = (uint32_t)(O_COL + t * HD);
+        const uint32_t p_col = (uint32_t)(P_COL + t * (TN / 2));
+        const int n_blocks = tr[t].hi - tr[t].lo;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < nblk; ++j) {
-            ok = mbar_wait(&sm.s_full, (uint32_t)j & 1u, abort_flag);
+        for (int it = 0; it < n_blocks; ++it) {
+            ok = mbar_wait(&sm.s_full[t], (uint32_t)it & 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
             uint32_t s[TN];
 #pragma unroll
-            for (int c = 0; c < TN / 32; ++c) tmem_ld32_nowait(lane_base + (uint32_t)(c * 32), s + c * 32);
+            for (int c = 0; c < TN / 32; ++c) tmem_ld32_nowait(lane_base + s_col + (uint32_t)(c * 32), s + c * 32);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(&sm.s_empty);                                 // the scores are in registers now
-            const int jbase = (kb0 + j) * TN;
+            mbar_arrive(&sm.s_empty[t]);                              // the scores are in registers now
+            const int jbase = (tr[t].lo + it) * TN;
             const bool open_block = row_ok && jbase + TN - 1 <= pos && (window <= 0 || jbase >= lo);
             if (!open_block) {
 #pragma unroll
@@ -363,52 +431,55 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 mx2 = fmaxf(mx2, __uint_as_float(s[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
             }
             const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2e);
-            // the P buffer (and, for a rescale, the accumulator) is free once the last block's P.V is done
-            if (j > 0) {
-                ok = mbar_wait(&sm.pv_done, (uint32_t)(j - 1) & 1u, abort_flag);
-                if (!ok) break;
-            }
-            // rescale O only when the maximum has grown much (or nothing has been accumulated with it yet)
+            // rescale O only when the maximum has grown much (or nothing has been accumulated with it yet);
+            // the accumulator (and below, P) is free once the last block's P.V is done
             const bool want = m_new > m + RESCALE_STEP || (m == -INFINITY && m_new != -INFINITY);
+            bool pv_seen = it == 0;
             if (__any_sync(0xffffffffu, want)) {
-                if (j > 0) {
+                if (it > 0) {
+                    ok = mbar_wait(&sm.pv_done[t], (uint32_t)(it - 1) & 1u, abort_flag);
+                    if (!ok) break;
+                    pv_seen = true;
                     tc_fence_after();
                     const float corr = want ? (m == -INFINITY ? 0.f : fast_exp2(m - m_new)) : 1.0f;
 #pragma unroll 1
                     for (int c = 0; c < HD / 32; ++c) {
                         uint32_t o[32];
-                        tmem_ld32(lane_base + (uint32_t)(O_COL + c * 32), o);
+                        tmem_ld32(lane_base + o_col + (uint32_t)(c * 32), o);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                        tmem_st32(lane_base + (uint32_t)(O_COL + c * 32), o);
+                        tmem_st32(lane_base + o_col + (uint32_t)(c * 32), o);
                     }
                     if (want) l *= corr;
                 }
                 if (want) m = m_new;
             }
-            const float use = m == -INFINITY ? 0.f : m;
-            // P = 2^(s*c - m), rounded to bfloat16, into shared memory as the MMA reads it (-inf gives 0)
-            float sum0 = 0.f, sum1 = 0.f;
+            // P = 2^(s*c - m) in place (-inf gives 0), then rounded to bfloat16 pairs (in place again)
+            const float neg_use = m == -INFINITY ? 0.f : -m;
 #pragma unroll
-            for (int c8 = 0; c8 < TN / 8; ++c8) {
-                uint32_t pk[4];
+            for (int i = 0; i < TN; ++i) s[i] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2e, neg_use)));
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float a = fast_exp2(fmaf(__uint_as_float(s[c8 * 8 + 2 * i]), scale_log2e, -use));
-                    const float bq = fast_exp2(fmaf(__uint_as_float(s[c8 * 8 + 2 * i + 1]), scale_log2e, -use));
-                    sum0 += a; sum1 += bq;
-                    pk[i] = pack_bf16(a, bq);
-                }
-                // keys c8*8 .. +7 of this row: 16-byte piece (c8 & 7) of the row's 128-byte line in half c8 / 8
-                *reinterpret_cast<uint4*>(p_row + (size_t)(c8 >> 3) * (TM * 64 * 2) + (((c8 & 7) ^ (r & 7)) << 4)) =
-                    make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            for (int i = 0; i < TN / 2; i += 2) {
+                const float a0 = __uint_as_float(s[2 * i]), a1 = __uint_as_float(s[2 * i + 1]);
+                const float a2 = __uint_as_float(s[2 * i + 2]), a3 = __uint_as_float(s[2 * i + 3]);
+                sum0 += a0; sum1 += a1; sum2 += a2; sum3 += a3;
+                s[i] = pack_bf16(a0, a1);
+                s[i + 1] = pack_bf16(a2, a3);
             }
-            l += sum0 + sum1;
-            proxy_fence();                 // the MMA reads P through the async proxy
+            l += (sum0 + sum1) + (sum2 + sum3);
+            if (!pv_seen) {
+                ok = mbar_wait(&sm.pv_done[t], (uint32_t)(it - 1) & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+            }
+#pragma unroll
+            for (int c = 0; c < TN / 64; ++c) tmem_st32_nowait(lane_base + p_col + (uint32_t)(c * 32), s + c * 32);
+            tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&sm.p_full);
+            mbar_arrive(&sm.p_full[t]);
         }
-        if (ok && nblk > 0) ok = mbar_wait(&sm.pv_done, (uint32_t)(nblk - 1) & 1u, abort_flag);
+        if (ok && n_blocks > 0) ok = mbar_wait(&sm.pv_done[t], (uint32_t)(n_blocks - 1) & 1u, abort_flag);
         if (!ok && lane == 0) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); }
         if (ok) {
             tc_fence_after();
@@ -417,7 +488,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t o[32];
-                tmem_ld32(lane_base + (uint32_t)(O_COL + c * 32), o);
+                tmem_ld32(lane_base + o_col + (uint32_t)(c * 32), o);
                 if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -433,7 +504,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+    if (warp == 1) tmem_dealloc(tmem, TMEM_TN);
 }
 
 // ---------------------------------------------------------------- host side
@@ -474,7 +545,7 @@ CELLM_API int cellm_attention_tc_supports(int hd, int nh, int nkv, int page_size
 }
 
 // out, q: [T, nh*64] bf16; pools: one layer's [pages][nkv][page_size][64] bf16. n_tiles = sum over the
-// requests of ceil(q_len / (128 / (nh/nkv))).
+// requests of ceil(q_len / (256 / (nh/nkv))): a CTA takes two tiles of 128 rows that share their keys.
 CELLM_API int cellm_attention_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
                                  const int* cu_seqlens, const int* ctx_lens, const int* block_table, int bt_stride,
                                  int B, int T, int n_tiles, int num_pages, int page_size, int nh, int nkv, int hd,
@@ -504,7 +575,7 @@ CELLM_API int cellm_attention_tc(void* out, const void* q, const void* k_pool, c
         configured = true;
     }
     dim3 grid((unsigned)n_tiles, (unsigned)nkv);
-    CELLM_RUN(attention_tc_kernel, grid, 192, smem, stream, mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens, ctx_lens,
-              block_table, bt_stride, B, num_pages, page_size, nh, nkv, scale * 1.4426950408889634f, window, err);
+    CELLM_RUN(attention_tc_kernel, grid, THREADS, smem, stream, mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens,
+              ctx_lens, block_table, bt_stride, B, num_pages, page_size, nh, nkv, scale * 1.4426950408889634f, window, err);
     return CELLM_OK;
 }

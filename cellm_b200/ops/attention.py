@@ -6,7 +6,7 @@ from ._lib import check, count_launch, fn, ptr, require_cuda, stream_of
 from .basic import attention_plain
 
 _FLASH_HEAD_SIZES = (32, 64, 128)
-# When prompt portions go to the tcgen05 kernel: at least `min_ctas` CTAs (None: one per SM)
+# When prompt portions go to the tcgen05 kernel: at least `min_ctas` CTAs (None: one for every other SM)
 # and at least `min_fill` of the tiles' rows in use. Tests lower both to drive small cases there.
 TC_POLICY = {"min_ctas": None, "min_fill": 0.5}
 _WORKSPACE: dict[torch.device, torch.Tensor] = {}
@@ -109,8 +109,8 @@ def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, cu
     if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or q.shape[1] != nh * hd \
             or not attention_tc_supports(hd, nh, nkv, page_size) or scale <= 0:
         raise ValueError("attention_tc: bfloat16, heads of 64, a group size dividing 128, pages of 8..128 tokens")
-    tok_per_tile = 128 // (nh // nkv)
-    n_tiles = sum((n + tok_per_tile - 1) // tok_per_tile for n in q_lens)
+    tok_per_cta = 256 // (nh // nkv)             # a CTA takes two tiles of 128 (token, head) rows
+    n_tiles = sum((n + tok_per_cta - 1) // tok_per_cta for n in q_lens)
     out = torch.empty_like(q)
     check(fn("attention_tc", "cellm_attention_tc")(
         ptr(out), ptr(q), ptr(k_pool), ptr(v_pool), ptr(cu_seqlens), ptr(ctx_lens), ptr(block_table),
@@ -135,11 +135,11 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, 
             nsplit = max(1, min(4 * _sms(q.device) // (ctx.B * k_pool.shape[1]), blocks // 4))
             return attention_decode(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.B, nh, scale,
                                     window, ctx.err, nsplit)
-        # prompt portions that fill the 128-row tiles of the tcgen05 kernel and at least one CTA per SM
+        # prompt portions that fill the tcgen05 kernel's pairs of 128-row tiles and enough CTAs
         if attention_tc_supports(hd, nh, k_pool.shape[1], k_pool.shape[2]):
-            per_tile = 128 // G
+            per_tile = 256 // G
             tc_tiles = sum((n + per_tile - 1) // per_tile for n in ctx.q_lens)
-            min_ctas = _sms(q.device) if TC_POLICY["min_ctas"] is None else TC_POLICY["min_ctas"]
+            min_ctas = _sms(q.device) // 2 if TC_POLICY["min_ctas"] is None else TC_POLICY["min_ctas"]
             if tc_tiles * k_pool.shape[1] >= min_ctas and ctx.T >= TC_POLICY["min_fill"] * tc_tiles * per_tile:
                 return attention_tc(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.q_lens, nh,
                                     scale, window, ctx.err)
