@@ -4,7 +4,7 @@
 // heads that share the key/value head are the rows of one 16-row tile (at most
 // 16 / group-size tokens per request, so a request's portion must be that
 // short). The CTA walks its keys in blocks of 64 that all its threads bring in
-// with cp.async (two stages); within a block every warp takes its own run of
+// with cp.async (a ring of ST stages); within a block every warp takes its own run of
 // 64 / NW keys and keeps an online-softmax state of its own, so the work of a
 // block is spread over the warps and a CTA needs only one ring of shared memory
 // (several CTAs fit an SM). The warps' partial results (maximum, sum,
@@ -15,6 +15,14 @@
 // (request, key/value head); the CTA that finds the counter at gridDim.z - 1
 // combines the pieces in the order of the splits, writes the output and sets
 // the counter back to zero. No CTA waits for another, and no second kernel runs.
+//
+// Programmatic dependent launch: the keys and values that were in the cache before
+// this step (every block below the request's context length) are written by no
+// kernel of this step, so their copies (and the look-ups of the block table, which
+// the step's first copy from the host filled) go out before the wait on the kernel
+// before this one; only the queries and the blocks that hold this step's tokens
+// come after it. Most of a request's cache is on its way, or there, when the
+// queries arrive.
 //
 // Scores, mask and softmax are as in the flash kernel for prompts
 // (attention_flash.cu): q.k * scale, key <= the token's position, optional
@@ -28,12 +36,14 @@ namespace {
 template <int HD, int NW>
 struct DecodeSmem {
     static constexpr int KV_BYTES = FA_BN * HD * 2;
+    static constexpr int ST = HD <= 64 ? 3 : 2;                           // stages of the ring
     static constexpr size_t q_off = 0;
-    static constexpr size_t kv_off = 16 * HD * 2;                         // [2 stages][K | V]
-    static constexpr size_t o_off = kv_off + (size_t)2 * 2 * KV_BYTES;    // [NW][16][HD] float
-    static constexpr size_t ml_off = o_off + (size_t)NW * 16 * HD * 4;    // [NW][16][2] float
+    static constexpr size_t kv_off = 16 * HD * 2;                         // [ST stages][K | V]
+    static constexpr size_t o_off = kv_off;                               // [NW][16][HD] float, over the ring once the keys are done
+    static constexpr size_t ml_off = kv_off + (size_t)ST * 2 * KV_BYTES;  // [NW][16][2] float
     static constexpr size_t flag_off = ml_off + (size_t)NW * 16 * 2 * 4;
     static constexpr size_t total = flag_off + 16;
+    static_assert((size_t)NW * 16 * HD * 4 <= (size_t)ST * 2 * KV_BYTES, "the warps' outputs must fit the ring");
 };
 
 template <int HD, int NW>
@@ -57,8 +67,8 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     constexpr int THREADS = NW * 32;
     const int G = nh / nkv;
     const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+    constexpr int ST = L::ST;
     pdl_trigger();
-    pdl_wait();
     const int t_base = cu_seqlens[b], q_len = cu_seqlens[b + 1] - t_base, rows = q_len * G;   // rows <= 16
     const int ctx = ctx_lens[b];
     const int key_end = ctx + q_len;
@@ -72,13 +82,6 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     auto page_of = [&](int j) { return page_shift >= 0 ? (j >> page_shift) : (j / page_size); };
     auto slot_of = [&](int j) { return page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size); };
 
-    for (int i = threadIdx.x; i < 16 * CH; i += NW * 32) {
-        const int row = i / CH, chunk = i % CH;
-        const bool ok = row < rows;
-        const __nv_bfloat16* src = q + (size_t)(t_base + (ok ? row / G : 0)) * nh * HD + (size_t)(kvh * G + (ok ? row % G : 0)) * HD + chunk * 8;
-        cp_async16(q_s + tile_offset<HD>(row, chunk), src, ok ? 16 : 0);
-    }
-    cp_async_commit();
     // By all threads. The pages of a thread's keys are looked up first, all at once,
     // so that the copies that follow do not each wait for a load of the block table.
     constexpr int KV_ITERS = (BN * CH + THREADS - 1) / THREADS;
@@ -103,9 +106,27 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
             cp_async16(vs + tile_offset<HD>(row, chunk), v_pool + off, page >= 0 ? 16 : 0);
         }
     };
-    if (my_begin < my_end) load_kv(my_begin, 0);
+    const int n_blk = max(0, my_end - my_begin);
+    const int first = min(n_blk, ST);            // blocks that fill the ring before the walk starts
+    const int old_end = ctx / BN;                // blocks below hold only keys that were in the cache before this step
+    int issued = 0;
+    for (; issued < first && my_begin + issued < old_end; ++issued) {
+        load_kv(my_begin + issued, issued);
+        cp_async_commit();
+    }
+    pdl_wait();                                  // the queries and this step's keys are the work of the kernels before
+    for (int i = threadIdx.x; i < 16 * CH; i += NW * 32) {
+        const int row = i / CH, chunk = i % CH;
+        const bool ok = row < rows;
+        const __nv_bfloat16* src = q + (size_t)(t_base + (ok ? row / G : 0)) * nh * HD + (size_t)(kvh * G + (ok ? row % G : 0)) * HD + chunk * 8;
+        cp_async16(q_s + tile_offset<HD>(row, chunk), src, ok ? 16 : 0);
+    }
     cp_async_commit();
-    cp_async_wait<1>();          // the Q tile (this thread's share)
+    for (; issued < first; ++issued) {
+        load_kv(my_begin + issued, issued);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();          // the Q tile and the first blocks (this thread's share)
     __syncthreads();             // everybody's share
     uint32_t qf[HD / 16][4];
 #pragma unroll
@@ -121,10 +142,9 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
     for (int kb = my_begin, it = 0; kb < my_end; ++kb, ++it) {
-        const int stage = it & 1;
-        if (kb + 1 < my_end) load_kv(kb + 1, stage ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
+        const int stage = it % ST;
+        // block `it` was committed ST groups ago (one group per block walked since)
+        cp_async_wait<ST - 1>();
         __syncthreads();
         const uint8_t* ks_ = kv_s + (size_t)stage * 2 * L::KV_BYTES;
         const uint8_t* vs_ = ks_ + L::KV_BYTES;
@@ -192,6 +212,8 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
             }
         }
         __syncthreads();
+        if (kb + ST < my_end) load_kv(kb + ST, stage);       // the stage is free: the block ST further on moves in
+        cp_async_commit();
     }
     cp_async_wait<0>();
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
