@@ -183,33 +183,7 @@ struct alignas(1024) GemmSmem {
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
-    float row_scale[BN];       // folded norm: 1 / rms of each token of the tile
-    float sumsq[4];            // folded norm: the epilogue warps' sums of squares of one token
 };
-
-// A norm folded into the products around it (swapped tiles; the pieces of a K split summed in a
-// cluster, or no split). RMSNorm of a row is a scale of the row, and a scale of a row of A scales the
-// same row of A.W^T, so the norm's two halves can move into the products before and after it:
-//   the product before (resid != nullptr) adds its output to the 32-bit residual stream in place,
-//     writes v * w (v the stream's new value, w the norm's weight) as its bfloat16 output, and for every
-//     token the sum of v^2 over its tile's 128 columns into part_out[token][tile];
-//   the product after (part_in != nullptr) takes that output as its A and multiplies each token's
-//     results by 1 / sqrt(sum of the token's n_parts partial sums / norm_dim + eps) (before silu(g) * u).
-// The partial sums are added in the order of the tiles: nothing depends on timing.
-struct NormFold {
-    float* resid;            // [M, N], 32-bit, updated in place
-    const void* next_w;      // [N], the following norm's weight
-    int next_w_is_f32;       // else bfloat16
-    float* part_out;         // [M, number of column tiles]
-    const float* part_in;    // [M, n_parts]
-    int n_parts;
-    int norm_dim;
-    float eps;
-};
-__device__ __forceinline__ float fold_weight(const NormFold& f, int i) {
-    return f.next_w_is_f32 ? static_cast<const float*>(f.next_w)[i]
-                           : __bfloat162float(static_cast<const __nv_bfloat16*>(f.next_w)[i]);
-}
 
 template <typename TO> __device__ __forceinline__ void store_row(TO* dst, const uint32_t* r, int valid, bool aligned);
 template <> __device__ __forceinline__ void store_row<float>(float* dst, const uint32_t* r, int valid, bool aligned) {
@@ -275,7 +249,7 @@ template <int BN, int STAGES, bool SWAP, int EPI, bool CLUSTER, typename TO>
 __global__ void __launch_bounds__(192, SWAP ? 2 : 1)      // swapped tiles: two CTAs an SM, so the next product's can move in early
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                     TO* __restrict__ C, float* __restrict__ ws, int* __restrict__ counters, int M, int N, int K,
-                    long long ldc, int kblocks_per_split, int w_is_static, const NormFold fold, int* __restrict__ err) {
+                    long long ldc, int kblocks_per_split, int w_is_static, int* __restrict__ err) {
     static_assert(!CLUSTER || SWAP, "the cluster reduction serves swapped tiles");
     extern __shared__ uint8_t smem_raw[];
     using Smem = GemmSmem<BN, STAGES, CLUSTER ? BN * BM : 0>;
@@ -307,13 +281,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     pdl_trigger();
     const uint32_t tmem = sm.tmem_base;
     volatile int* abort_flag = &sm.abort_flag;
-    // folded norm: the stream's old values of this thread's first tokens and the next norm's weight of its column,
-    // fetched by the epilogue warps while the products are still running
-    constexpr int FOLD_EARLY = 8;
-    float fold_old[FOLD_EARLY];
-    float fold_w = 0.f;
-    const int fold_q0 = q0 + (CLUSTER ? (int)cluster_rank() : 0);        // this thread's tokens: fold_q0, + fold_dq, ...
-    const int fold_dq = CLUSTER ? splits : 1;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -364,56 +331,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             if (ok) umma_commit(&sm.acc_full);
         }
     } else {
-        const int qtr = warp & 3;                     // the quarter of the lanes this warp may read
-        const int pl = qtr * 32 + lane;               // row of the tile this thread holds
-        const int p = p0 + pl;
-        if constexpr (SWAP) {
-            // what a folded norm needs of the kernel before is fetched while the products run
-            if (fold.part_in != nullptr || fold.resid != nullptr) pdl_wait();
-            if (fold.part_in != nullptr) {
-                // 1 / rms of the tile's tokens from the partial sums of the product before
-                if (pl < BN) {
-                    const int q = q0 + pl;
-                    float ssum = 0.f;
-                    if (q < Q)
-                        for (int t = 0; t < fold.n_parts; ++t) ssum += fold.part_in[(size_t)q * fold.n_parts + t];
-                    sm.row_scale[pl] = rsqrtf(ssum / (float)fold.norm_dim + fold.eps);
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-            }
-            if (fold.resid != nullptr && p < P) {
-                fold_w = fold_weight(fold, p);
-#pragma unroll
-                for (int i = 0; i < FOLD_EARLY; ++i) {
-                    const int q = fold_q0 + i * fold_dq;
-                    fold_old[i] = q < min(Q, q0 + BN) ? fold.resid[(size_t)q * N + p] : 0.f;
-                }
-            }
-        }
         const bool ok = mbar_wait(&sm.acc_full, 0, abort_flag);
         if (!ok && lane == 0) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); }
         tc_fence_after();
         pdl_wait();     // global writes below must not pass the kernel before this one
+        const int qtr = warp & 3;                     // the quarter of the lanes this warp may read
+        const int pl = qtr * 32 + lane;               // row of the tile this thread holds
+        const int p = p0 + pl;
         const uint32_t lane_addr = tmem + ((uint32_t)(qtr * 32) << 16);
         const bool through_ws = !CLUSTER && (splits > 1 || (EPI == 1 && SWAP));
-        // adds `acc` of token q and column p to the stream, stores the pre-scaled output, and leaves the tile's
-        // sum of squares for the token; all 128 epilogue threads call it together
-        auto fold_out = [&](int q, float acc, float old) {
-            float v = 0.f;
-            if (p < P) {
-                // the output joins the stream rounded as it would be stored without the fold
-                v = old + to_float(from_float<TO>(acc));
-                fold.resid[(size_t)q * N + p] = v;
-                C[(size_t)q * ldc + p] = from_float<TO>(v * fold_w);
-            }
-            float ss = v * v;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (lane == 0) sm.sumsq[qtr] = ss;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (pl == 0) fold.part_out[(size_t)q * gridDim.x + blockIdx.x] = (sm.sumsq[0] + sm.sumsq[1]) + (sm.sumsq[2] + sm.sumsq[3]);
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        };
         if constexpr (CLUSTER) {
             // this CTA's piece, token-major: red[token of the tile][row of the tile]
             constexpr int W = BN < 32 ? 16 : 32;
@@ -441,25 +367,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 }
             } else if constexpr (EPI == 0 && SWAP) {
                 constexpr int W = BN < 32 ? 16 : 32;
-#pragma unroll
+#pragma unroll 1
                 for (int c = 0; c < BN / W; ++c) {
                     uint32_t r[W];
                     if constexpr (W == 16) tmem_ld16(lane_addr + (uint32_t)(c * W), r);
                     else tmem_ld32(lane_addr + (uint32_t)(c * W), r);
+                    if (p < P) {
 #pragma unroll
-                    for (int j = 0; j < W; ++j) {
-                        const int q = q0 + c * W + j;
-                        if (q < Q) {                       // the same for all threads
-                            float acc = __uint_as_float(r[j]);
-                            if (fold.part_in != nullptr) acc *= sm.row_scale[q - q0];
-                            if (fold.resid != nullptr) {
-                                float old = 0.f;
-                                if (c * W + j < FOLD_EARLY) old = fold_old[(c * W + j) < FOLD_EARLY ? (c * W + j) : 0];
-                                else if (p < P) old = fold.resid[(size_t)q * N + p];
-                                fold_out(q, acc, old);
-                            } else if (p < P) {
-                                C[(size_t)q * ldc + p] = from_float<TO>(acc);
-                            }
+                        for (int j = 0; j < W; ++j) {
+                            const int q = q0 + c * W + j;
+                            if (q < Q) C[(size_t)q * ldc + p] = from_float<TO>(__uint_as_float(r[j]));
                         }
                     }
                 }
@@ -604,43 +521,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             const uint32_t rank = cluster_rank();
             const int q_end = min(Q, q0 + BN);
             // tokens rank, rank + splits, ... of the tile are summed and written by this CTA
-#pragma unroll
-            for (int i = 0; i < BN; ++i) {
-                const int q = q0 + (int)rank + i * splits;
-                if (q >= q_end) break;
+            for (int q = q0 + (int)rank; q < q_end; q += splits) {
                 const float* mine = &sm.red[(q - q0) * BM + pl];
-                const float scale = fold.part_in != nullptr ? sm.row_scale[q - q0] : 1.0f;
                 if constexpr (EPI == 0) {
                     float acc = 0.f;
                     for (int r = 0; r < splits; ++r) acc += ld_peer_shared(mine, (uint32_t)r);
-                    acc *= scale;
-                    if (fold.resid != nullptr) {
-                        // the stream takes the output; what is stored is the next norm's input times its weight,
-                        // and the tile's share of the token's sum of squares (all 128 threads pass here together)
-                        float v = 0.f;
-                        if (p < P) {
-                            const float old = i < FOLD_EARLY ? fold_old[i < FOLD_EARLY ? i : 0] : fold.resid[(size_t)q * N + p];
-                            // the output joins the stream rounded as it would be stored without the fold
-                            v = old + to_float(from_float<TO>(acc));
-                            fold.resid[(size_t)q * N + p] = v;
-                            C[(size_t)q * ldc + p] = from_float<TO>(v * fold_w);
-                        }
-                        float ss = v * v;
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                        if (lane == 0) sm.sumsq[warp & 3] = ss;
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (pl == 0)
-                            fold.part_out[(size_t)q * gridDim.x + blockIdx.x] = (sm.sumsq[0] + sm.sumsq[1]) + (sm.sumsq[2] + sm.sumsq[3]);
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                    } else if (p < P) {
-                        C[(size_t)q * ldc + p] = from_float<TO>(acc);
-                    }
+                    if (p < P) C[(size_t)q * ldc + p] = from_float<TO>(acc);
                 } else {
                     if (pl < 64) {
                         float g = 0.f, u = 0.f;
                         for (int r = 0; r < splits; ++r) { g += ld_peer_shared(mine, (uint32_t)r); u += ld_peer_shared(mine + 64, (uint32_t)r); }
-                        if (p + 64 < P) C[(size_t)q * ldc + (p0 / 2 + pl)] = from_float<TO>(silu_mul(g * scale, u * scale));
+                        if (p + 64 < P) C[(size_t)q * ldc + (p0 / 2 + pl)] = from_float<TO>(silu_mul(g, u));
                     }
                 }
             }
@@ -856,8 +747,7 @@ bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
 
 template <int BN, int STAGES, bool SWAP, int EPI, bool CLUSTER, typename TO>
 int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* ws, int* counters, int M, int N, int K,
-           long long ldc, int split_k, int kblocks_per_split, int w_is_static, const NormFold& fold, int* err,
-           cudaStream_t stream) {
+           long long ldc, int split_k, int kblocks_per_split, int w_is_static, int* err, cudaStream_t stream) {
     const size_t smem = sizeof(GemmSmem<BN, STAGES, CLUSTER ? BN * BM : 0>) + 1024;
     static bool configured = false;
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, EPI, CLUSTER, TO>;
@@ -886,7 +776,7 @@ int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* w
         cfg.numAttrs = 2;
     }
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, m_rows, m_cols, C, ws, counters, M, N, K, ldc, kblocks_per_split,
-                                       w_is_static, fold, err);
+                                       w_is_static, err);
     return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
@@ -940,16 +830,9 @@ CELLM_API int cellm_gemm_tcgen05_plan(int M, int N, int K, int bn, int split_k, 
 // further K blocks of the CTA's weights into L2 while it waits).
 // workspace: as many floats as cellm_gemm_tcgen05_plan says; counters: GEMM_MAX_COUNTERS
 // zeroed ints that products on one stream may share (each product leaves them zero).
-//
-// A norm folded into the product (see NormFold; swapped tiles of one token tile, unsplit or summed in a cluster):
-// resid [M, N] float with next_w [N] (next_w_dtype: the tag of float or bfloat16) and part_out [M, ceil(N / 128)]
-// make this product the one before the norm (epilogue 0, bfloat16 output); part_in [M, n_parts] with norm_dim
-// and eps make it the one after. Null pointers: a plain product.
 CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
                                  long long ldw, long long ldc, int out_dtype, int bn, int split_k, int epilogue,
-                                 int w_is_static, float* workspace, int* counters, float* resid, const void* next_w,
-                                 int next_w_dtype, float* part_out, const float* part_in, int n_parts, int norm_dim,
-                                 float eps, int* err, cudaStream_t stream) {
+                                 int w_is_static, float* workspace, int* counters, int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return CELLM_OK;
     if (K <= 0 || (K & 7)) return CELLM_ERR_SIZE;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((lda * 2) & 15) || ((ldw * 2) & 15)) return CELLM_ERR_ALIGN;
@@ -968,18 +851,6 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
     // (an unsplit SwiGLU tile takes the same road as a cluster of one: gate and up meet in shared memory)
     const bool in_cluster = swap && M <= narrow && use_cluster && ((split >= 2 && split <= 8) || (split == 1 && epilogue == 1));
     if (in_cluster) ws_floats = 0;
-    NormFold fold = {};
-    if (resid != nullptr || part_in != nullptr) {
-        // only where a tile's outputs are finished by the threads that own them, without the workspace
-        if (!swap || M > narrow || !(in_cluster || (split == 1 && epilogue == 0))) return CELLM_ERR_ARG;
-        if (resid != nullptr) {
-            if (epilogue != 0 || out_dtype != CELLM_BF16 || next_w == nullptr || part_out == nullptr) return CELLM_ERR_ARG;
-            if (next_w_dtype != CELLM_F32 && next_w_dtype != CELLM_BF16) return CELLM_ERR_DTYPE;
-        }
-        if (part_in != nullptr && (n_parts <= 0 || norm_dim <= 0)) return CELLM_ERR_ARG;
-        fold.resid = resid; fold.next_w = next_w; fold.next_w_is_f32 = next_w_dtype == CELLM_F32; fold.part_out = part_out;
-        fold.part_in = part_in; fold.n_parts = n_parts; fold.norm_dim = norm_dim; fold.eps = eps;
-    }
     const int kblocks = (K + BK - 1) / BK;
     const int per = (kblocks + split - 1) / split;
     if (ws_floats > 0 && workspace == nullptr) return CELLM_ERR_ARG;
@@ -1009,8 +880,8 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
     }
 #define GO3(BN_, ST_, SW_, EP_, CL_)                                                                                  \
     do {                                                                                                              \
-        if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, EP_, CL_, float>(m_rows, m_cols, (float*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, fold, err, stream); \
-        else rc = launch<BN_, ST_, SW_, EP_, CL_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, fold, err, stream); \
+        if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, EP_, CL_, float>(m_rows, m_cols, (float*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
+        else rc = launch<BN_, ST_, SW_, EP_, CL_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
     } while (0)
 #define GO2(BN_, ST_, SW_, EP_) GO3(BN_, ST_, SW_, EP_, false)
     // swapped: ST_ stages without, CST_ stages with the cluster's reduction buffer (two CTAs must still fit an SM)

@@ -71,10 +71,7 @@ class DecoderModel:
         residual = Residual(ops.embed(self.embedding, ctx.token_ids, ctx.err))
         order = self.plan.order if max_layers is None else self.plan.order[:max_layers]
         for i, e in enumerate(order):
-            # the norm that reads the stream after this block, if its reader can take what a folded product leaves
-            nxt = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
-            next_norm = nxt.first_norm() if nxt is not None and getattr(nxt, "first_takes_prescaled", lambda: False)() else None
-            self.blocks[e.layer].forward(residual, ctx, bindings[i], next_norm=next_norm)
+            self.blocks[e.layer].forward(residual, ctx, bindings[i])
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         xf = self.final_norm.forward(residual, rows=logit_rows)

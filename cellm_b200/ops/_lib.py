@@ -43,7 +43,7 @@ _SIGNATURES = {
         "cellm_attention_flash_supports": [I],
     },
     "gemm_tcgen05": {
-        "cellm_gemm_tcgen05": [P, P, P, I, I, I, L, L, L, I, I, I, I, I, P, P, P, P, I, P, P, I, I, F, P, P],
+        "cellm_gemm_tcgen05": [P, P, P, I, I, I, L, L, L, I, I, I, I, I, P, P, P, P],
     },
 }
 

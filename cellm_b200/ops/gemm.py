@@ -21,13 +21,11 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None =
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-         w_is_static: bool = False, before=None, after=None):
+         w_is_static: bool = False) -> torch.Tensor:
     """The product a . w^T by the kernel that serves the operands' element type:
     32-bit operands run the plain 32-bit kernel; bfloat16 operands run the
-    tensor-core kernels (which alone take a norm's halves, `before` / `after`)."""
+    tensor-core kernels."""
     if a.dtype == torch.float32:
-        if before is not None or after is not None:
-            raise ValueError("gemm: a norm folds only into bfloat16 products")
         return gemm_plain(a, w, out_dtype)
     from .gemm_bf16 import gemm_bf16
-    return gemm_bf16(a, w, out_dtype, w_is_static, before, after)
+    return gemm_bf16(a, w, out_dtype, w_is_static)

@@ -3,7 +3,6 @@ tile shape and K split for the sizes at hand."""
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass
 
 import torch
 
@@ -96,61 +95,15 @@ def _effective_split(K: int, split_k: int) -> int:
     return (kblocks + per - 1) // per
 
 
-@dataclass
-class FoldBefore:
-    """Makes a product the one before an RMSNorm: its output is added to the 32-bit
-    stream `resid` [M, N] in place; what it returns is (stream * next_w) in bfloat16
-    and, per token, partial sums of the stream's squares (one per 128 columns)."""
-    resid: torch.Tensor
-    next_w: torch.Tensor
-
-
-@dataclass
-class FoldAfter:
-    """Makes a product the one after that norm: its input is FoldBefore's output;
-    every token's results are multiplied by 1 / sqrt(sum(parts) / norm_dim + eps)."""
-    parts: torch.Tensor
-    norm_dim: int
-    eps: float
-
-
-def _finished_in_place(M: int, bn: int, split: int, epilogue: int) -> bool:
-    """Whether the kernel finishes a tile's outputs in the threads that own them
-    (swapped tiles of one token tile: the K split summed in a cluster, or none)."""
-    in_cluster = bn < 0 and M <= -bn and _CLUSTER_REDUCE and (2 <= split <= 8 or (split == 1 and epilogue == 1))
-    return bn < 0 and M <= -bn and (in_cluster or (split == 1 and epilogue == 0))
-
-
-def can_fold(M: int, N: int, K: int, device, epilogue: int = 0) -> bool:
-    """Whether a product of these sizes can take a norm's half (FoldBefore / FoldAfter)."""
-    if M > 64 or K % 8:
-        return False
-    bn, split = plan_tiles(M, N, K, _sms(device))
-    return _finished_in_place(M, bn, _effective_split(K, split), epilogue)
-
-
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bn: int, split_k: int,
-                 err: torch.Tensor | None = None, epilogue: int = 0, w_is_static: bool = False,
-                 before: FoldBefore | None = None, after: FoldAfter | None = None):
+                 err: torch.Tensor | None = None, epilogue: int = 0, w_is_static: bool = False) -> torch.Tensor:
     """The tensor-core kernel with a given tile shape and split. epilogue 1: `w`
     holds blocks of 64 gate rows followed by their 64 up rows and the result is
-    silu(gate) * up, [M, N/2]. With `before` the result is (output, partial sums)."""
+    silu(gate) * up, [M, N/2]."""
     M, K = a.shape
     N = w.shape[0]
     c = torch.empty((M, N // 2 if epilogue else N), dtype=out_dtype, device=a.device)
     split = _effective_split(K, split_k)
-    parts_out = None
-    if before is not None or after is not None:
-        if not _finished_in_place(M, bn, split, epilogue):
-            raise ValueError("gemm_tcgen05: a norm folds only into swapped tiles that are unsplit or summed in a cluster")
-        if before is not None:
-            if before.resid.dtype != torch.float32 or before.resid.shape != (M, N) or not before.resid.is_contiguous() \
-                    or before.next_w.numel() != N or epilogue or out_dtype != torch.bfloat16:
-                raise ValueError("gemm_tcgen05: the stream must be float32 [M, N], the norm's weight [N], the output bfloat16")
-            parts_out = torch.empty((M, (N + 127) // 128), dtype=torch.float32, device=a.device)
-        if after is not None and (after.parts.dtype != torch.float32 or after.parts.shape[0] != M
-                                  or not after.parts.is_contiguous()):
-            raise ValueError("gemm_tcgen05: partial sums must be float32 [M, parts]")
     # swapped tiles whose K split is one thread-block cluster (2..8 CTAs) sum their pieces
     # through shared memory: no workspace, no counters
     in_cluster = bn < 0 and M <= -bn and _CLUSTER_REDUCE and (2 <= split <= 8 or (split == 1 and epilogue == 1))
@@ -160,13 +113,9 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bn: i
     err = err if err is not None else error_word(a.device)
     check(fn("gemm_tcgen05", "cellm_gemm_tcgen05")(
         ptr(c), ptr(a), ptr(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), tag(out_dtype), int(bn),
-        int(split_k), int(epilogue), _STATIC_FLAG if w_is_static else 0, ptr(ws), ptr(counters),
-        ptr(before.resid) if before else None, ptr(before.next_w) if before else None,
-        tag(before.next_w) if before else 0, ptr(parts_out), ptr(after.parts) if after else None,
-        after.parts.shape[1] if after else 0, after.norm_dim if after else 0, float(after.eps) if after else 0.0,
-        ptr(err), stream_of(a)),
+        int(split_k), int(epilogue), _STATIC_FLAG if w_is_static else 0, ptr(ws), ptr(counters), ptr(err), stream_of(a)),
         "gemm_tcgen05")
-    return c if before is None else (c, parts_out)
+    return c
 
 
 def tensor_core_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -176,27 +125,23 @@ def tensor_core_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-              w_is_static: bool = False, before: FoldBefore | None = None, after: FoldAfter | None = None):
+              w_is_static: bool = False) -> torch.Tensor:
     """a [M, K] . w [N, K]^T for bfloat16 operands, 32-bit accumulation, output
     bfloat16 or float32. Sizes the tensor-core kernel does not take (K not a
     multiple of 8, unaligned rows) go to the plain kernel. `w_is_static`: w is a
-    weight that nothing on the stream writes (its loads may then start early).
-    `before` / `after`: a norm's halves (the caller has asked `can_fold`)."""
+    weight that nothing on the stream writes (its loads may then start early)."""
     out_dtype = out_dtype or a.dtype
     if not tensor_core_ok(a, w):
-        if before is not None or after is not None:
-            raise ValueError("gemm_bf16: a norm cannot fold into a product that the tensor-core kernel does not take")
         return gemm_plain(a, w, out_dtype)
     bn, split = plan_tiles(a.shape[0], w.shape[0], a.shape[1], _sms(a.device))
-    return gemm_tcgen05(a, w, out_dtype, bn, split, w_is_static=w_is_static, before=before, after=after)
+    return gemm_tcgen05(a, w, out_dtype, bn, split, w_is_static=w_is_static)
 
 
-def gemm_swiglu_bf16(a: torch.Tensor, w_blocked: torch.Tensor, w_is_static: bool = False,
-                     after: FoldAfter | None = None) -> torch.Tensor:
+def gemm_swiglu_bf16(a: torch.Tensor, w_blocked: torch.Tensor, w_is_static: bool = False) -> torch.Tensor:
     """silu(a . w1^T) * (a . w3^T) in one kernel; `w_blocked` is w1 and w3 cut into
     blocks of 64 rows and laid out gate block, up block, gate block, ...; the
     caller has checked `tensor_core_ok` and that the width is a multiple of 64."""
     bn, split = plan_tiles(a.shape[0], w_blocked.shape[0], a.shape[1], _sms(a.device))
     if bn == 64:
         bn = 128
-    return gemm_tcgen05(a, w_blocked, a.dtype, bn, split, epilogue=1, w_is_static=w_is_static, after=after)
+    return gemm_tcgen05(a, w_blocked, a.dtype, bn, split, epilogue=1, w_is_static=w_is_static)

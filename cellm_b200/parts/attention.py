@@ -61,11 +61,7 @@ class AttentionMixer(Mixer):
         pos: PartSpec | None = params.get("position")
         self.position = part_class("position", pos.kind)(pos.params, dev) if pos is not None else None
 
-    takes_prescaled = True       # the q/k/v product can apply the scale of the norm before it
-    feeds_sink = True            # out_proj can add to the residual stream itself
-
-    def forward(self, x, ctx: StepContext, cache: CacheBinding):
-        sink, ctx.sink = ctx.sink, None
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         nh, nkv, hd = self.nh, (self.nkv if cache.writes else 0), self.hd
         qkv = self.qkv(x) if cache.writes else self.q_only(x)
         rot = self.position.rotation() if self.position is not None else (0, False, None)
@@ -93,7 +89,7 @@ class AttentionMixer(Mixer):
                 ops.qk_norm_rope(kv, None, None, 0.0, ctx.positions, ctx.seq_of_token, bt, kp, vp,
                                  cache.page_size, 0, nkv, hd, 0, False, None, ctx.err)
         o = ops.attention(q, cache.k, cache.v, ctx, cache.block_table, nh, self.scale, self.window)
-        return self.out_proj(o, sink=sink)
+        return self.out_proj(o)
 
 
 register_mixer("attention", AttentionMixer)

@@ -9,16 +9,6 @@ the loader found for it. It never sees the model's configuration or name.
   FeedForward     forward(x, ctx) -> [T, hidden]
   Block           forward(residual, ctx, cache): the arrangement of the above in a layer
 
-Folding a norm into the products around it (optional; small batches in bfloat16).
-A norm between two matrix products can give its sum of squares to the product before
-it and its scale to the product after it, so that no norm kernel runs:
-  - a block that knows which norm comes after a mixer or feed-forward offers it a
-    `ResidualSink` in `ctx.sink`; a part that says `feeds_sink = True` hands the sink
-    to its last `Linear`, which may add its output to the stream itself and return None;
-  - the norm then returns a `Prescaled` instead of a tensor to a part that says
-    `takes_prescaled = True`; that part hands it to its first `Linear`.
-A part that says neither sees plain tensors, as before.
-
 `weight_specs(params)` lists the tensors a part reads, with the shape each
 must have in the file and the class of values a random model gives it.
 """
@@ -79,7 +69,6 @@ class StepContext:
     max_q_len: int = 0
     max_total_len: int = 0
     extras: dict[str, Any] = field(default_factory=dict)  # per-step scratch shared between parts
-    sink: Optional["ResidualSink"] = None                  # see "Folding a norm" above; set and cleared by the block
 
     @property
     def stream(self) -> int:
@@ -102,49 +91,20 @@ class CacheBinding:
     num_slots: int = 0
 
 
-@dataclass
-class Prescaled:
-    """A norm's output that is not formed: `u` is the stream times the norm's weight
-    [T, dim], `parts` [T, n] partial sums of the stream's squares. The normed rows
-    are u[t] / sqrt(sum(parts[t]) / dim + eps); `materialize()` forms them."""
-    u: torch.Tensor
-    parts: torch.Tensor
-    dim: int
-    eps: float
-    materialize: Any
-
-
-class ResidualSink:
-    """An offer to a part's last product: add your output to this stream yourself,
-    for the norm `norm` (an object with .weight, .eps, .dim) that comes next."""
-
-    def __init__(self, residual: "Residual", norm):
-        self.residual, self.norm = residual, norm
-
-    def delivered(self, u: torch.Tensor, parts: torch.Tensor) -> None:
-        self.residual.folded = (self.norm, u, parts)
-
-
 class Residual:
     """The 32-bit residual stream with one pending addend.
 
     A mixer's or feed-forward's output is not added at once: it waits until the
-    next norm, which adds and normalises in one kernel. `folded` is set instead
-    when a product has already added its output (see ResidualSink)."""
+    next norm, which adds and normalises in one kernel."""
 
     def __init__(self, x: torch.Tensor):
         assert x.dtype == torch.float32
         self.x = x
         self.pending: Optional[torch.Tensor] = None
-        self.folded: Optional[tuple] = None      # (norm, u, parts) left by a product for exactly that norm
 
-    def add(self, delta: Optional[torch.Tensor]) -> None:
-        """delta None: the part has delivered its output through the sink."""
-        if delta is None:
-            return
+    def add(self, delta: torch.Tensor) -> None:
         if self.pending is not None:
             self.flush()
-        self.folded = None
         self.pending = delta
 
     def flush(self) -> torch.Tensor:
@@ -169,15 +129,10 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, residual: Residual, rows: Optional[torch.Tensor] = None, prescaled_ok: bool = False):
+    def forward(self, residual: Residual, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Adds the pending addend into the stream and returns the normed rows
-        (all rows, or the given row indices without touching the stream). With
-        `prescaled_ok` it may return a Prescaled when the product before has left one."""
+        (all rows, or the given row indices without touching the stream)."""
         raise NotImplementedError
-
-    def sink(self, residual: Residual, T: int) -> Optional[ResidualSink]:
-        """A sink for the product before this norm, or None if this norm does not fold."""
-        return None
 
 
 class Position(Part):
@@ -209,10 +164,5 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    def forward(self, residual: Residual, ctx: StepContext, cache: CacheBinding, next_norm: Optional[Norm] = None) -> None:
-        """`next_norm`: the norm that will read the stream after this block, if the caller knows it."""
+    def forward(self, residual: Residual, ctx: StepContext, cache: CacheBinding) -> None:
         raise NotImplementedError
-
-    def first_norm(self) -> Optional[Norm]:
-        """The norm this block begins with (what a block before it may fold into)."""
-        return None

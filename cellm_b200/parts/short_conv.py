@@ -43,15 +43,11 @@ class ShortConvMixer(Mixer):
         if params.get("bias"):
             self.conv_b = weights["conv_bias"].to(self.conv_w.dtype).contiguous()
 
-    takes_prescaled = True       # in_proj can apply the scale of the norm before it
-    feeds_sink = True            # out_proj can add to the residual stream itself
-
-    def forward(self, x, ctx: StepContext, cache: CacheBinding):
-        sink, ctx.sink = ctx.sink, None
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         bcx = self.in_proj(x)
         y = ops.short_conv(bcx, self.conv_w, self.conv_b, cache.state, ctx.slot_ids, ctx.seq_of_token,
                            ctx.cu_seqlens, ctx.err, ctx.max_q_len)
-        return self.out_proj(y, sink=sink)
+        return self.out_proj(y)
 
 
 register_mixer("short_conv", ShortConvMixer)

@@ -7,14 +7,12 @@ import torch
 
 from .. import ops
 from .base import FeedForward, StepContext, TensorSpec
-from .linear import Linear, fold_after, stack_rows
+from .linear import Linear, stack_rows
 from .registry import register_feed_forward
 
 
 class SwiGLU(FeedForward):
     graph_safe = True
-    takes_prescaled = True       # the gate / up product can apply the scale of the norm before it
-    feeds_sink = True            # the down product can add to the residual stream itself
 
     """params: hidden_size, ff_dim. weights: w1, w3 [ff, H]; w2 [H, ff]."""
 
@@ -42,14 +40,12 @@ class SwiGLU(FeedForward):
             self.gate_up = Linear(stack_rows(w1, w3), dtype)
         self.down = Linear(weights["w2"], dtype)
 
-    def forward(self, x, ctx: StepContext):
-        sink, ctx.sink = ctx.sink, None
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        if self.fused and x.dtype == torch.bfloat16 and ops.tensor_core_ok(x, self.gate_up.weight):
+            return self.down(ops.gemm_swiglu_bf16(x, self.gate_up.weight, w_is_static=True))
         if self.fused:
-            x, after = fold_after(x, self.gate_up.weight, epilogue=1)
-            if x.dtype == torch.bfloat16 and ops.tensor_core_ok(x, self.gate_up.weight):
-                return self.down(ops.gemm_swiglu_bf16(x, self.gate_up.weight, w_is_static=True, after=after), sink=sink)
             raise ValueError("swiglu: activations do not fit the fused kernel (bfloat16, 16-byte aligned rows)")
-        return self.down(ops.swiglu(self.gate_up(x)), sink=sink)
+        return self.down(ops.swiglu(self.gate_up(x)))
 
 
 register_feed_forward("swiglu", SwiGLU)

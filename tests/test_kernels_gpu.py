@@ -431,62 +431,6 @@ def test_gemm_tcgen05_swiglu_epilogue(M, ff, K, bn, split):
     assert float((h.double() - ref).abs().max()) <= 6e-3 * (1 + float(ref.abs().max()))
 
 
-@pytest.mark.parametrize("wdt", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("M,H,K1,N2,bn,split1,split2,swiglu", [
-    (8, 2048, 2048, 6144, -16, 8, 3, False),      # the sizes of a decode step: both splits are clusters
-    (3, 256, 128, 128, -16, 1, 1, False),         # no split at all: tiles finished straight from tensor memory
-    (16, 384, 512, 256, -16, 2, 4, True),         # the product after is the gate / up product
-    (20, 640, 256, 200, -32, 4, 1, False),        # 32-token tiles, ragged widths (640 = 5 tiles, 200 = 1.6 tiles)
-    (50, 192, 1024, 128, -64, 8, 2, True)])
-def test_gemm_tcgen05_with_a_norm_folded_in(M, H, K1, N2, bn, split1, split2, swiglu, wdt):
-    """h = a . W1^T joins the stream, RMSNorm, then . W2^T (or the gate / up product):
-    the norm's sum of squares is taken in the first product's epilogue, its scale is
-    applied in the second's; no norm kernel runs."""
-    from cellm_b200.ops.gemm_bf16 import FoldAfter, FoldBefore, error_word, gemm_tcgen05
-    g = torch.Generator(device=DEV).manual_seed(M * H)
-    rnd = lambda *shape: torch.randn(*shape, device=DEV, generator=g)
-    a, w1 = (rnd(M, K1) * 0.5).bfloat16(), (rnd(H, K1) * K1 ** -0.5).bfloat16()
-    resid = rnd(M, H) * 3
-    resid[0] *= 40                                        # rows of very different size: the scale is per row
-    nw = (1 + 0.3 * rnd(H)).to(wdt)
-    eps = 1e-5
-    # the output joins the stream rounded to bfloat16, as it does when it is stored and added by the norm kernel
-    stream = resid.double() + (a.double() @ w1.double().T).bfloat16().double()
-    normed = stream / torch.sqrt((stream ** 2).mean(1, keepdim=True) + eps) * nw.double()
-    u, parts = gemm_tcgen05(a, w1, torch.bfloat16, bn, split1, before=FoldBefore(resid, nw))
-    # (a value that lies next to a rounding boundary may fall to the other side: one unit of bfloat16 of the output)
-    h_size = float((a.double() @ w1.double().T).abs().max())
-    assert float((resid.double() - stream).abs().max()) <= 2e-5 * float(stream.abs().max()) + 2.0 ** -8 * h_size
-    assert float((resid.double() - stream).abs().median()) <= 2e-6 * float(stream.abs().max())
-    assert tuple(parts.shape) == (M, (H + 127) // 128)
-    rel = float(((parts.double().sum(1) - (stream ** 2).sum(1)) / (stream ** 2).sum(1)).abs().max())
-    assert rel < 1e-5
-    after = FoldAfter(parts, H, eps)
-    if swiglu:
-        ff = N2
-        wg, wu = (rnd(ff, H) * H ** -0.5).bfloat16(), (rnd(ff, H) * H ** -0.5).bfloat16()
-        blocked = torch.stack([wg.reshape(ff // 64, 64, H), wu.reshape(ff // 64, 64, H)], dim=1).reshape(2 * ff, H).contiguous()
-        y = gemm_tcgen05(u, blocked, torch.bfloat16, bn, split2, epilogue=1, after=after)
-        gg, uu = normed @ wg.double().T, normed @ wu.double().T
-        ref = gg * torch.sigmoid(gg) * uu
-    else:
-        w2 = (rnd(N2, H) * H ** -0.5).bfloat16()
-        y = gemm_tcgen05(u, w2, torch.bfloat16, bn, split2, after=after)
-        ref = normed @ w2.double().T
-    torch.cuda.synchronize()
-    assert error_word(a.device).item() == 0
-    # one rounding of the inputs (v * w) and one of the output to bfloat16
-    assert float((y.double() - ref).abs().max()) <= 1.2e-2 * (1 + float(ref.abs().max()))
-
-
-def test_gemm_fold_refuses_tiles_it_cannot_finish_in_place():
-    from cellm_b200.ops.gemm_bf16 import FoldAfter, can_fold, gemm_tcgen05
-    a, w = torch.randn(200, 64, device=DEV).bfloat16(), torch.randn(128, 64, device=DEV).bfloat16()
-    assert not can_fold(200, 128, 64, a.device)
-    with pytest.raises(ValueError):
-        gemm_tcgen05(a, w, torch.bfloat16, 128, 1, after=FoldAfter(torch.zeros(200, 1, device=DEV), 64, 1e-5))
-
-
 def test_gemm_dispatch_covers_every_size():
     from cellm_b200 import ops
     for M, N, K in ((3, 50, 20), (3, 50, 24), (200, 333, 40), (64, 2048, 2048), (65, 64, 64)):
