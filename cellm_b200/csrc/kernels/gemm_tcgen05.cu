@@ -100,7 +100,7 @@ __device__ __forceinline__ float ld_peer_shared(const float* local, uint32_t ran
     uint32_t addr;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
     float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
     return v;
 }
 
@@ -523,14 +523,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             // tokens rank, rank + splits, ... of the tile are summed and written by this CTA
             for (int q = q0 + (int)rank; q < q_end; q += splits) {
                 const float* mine = &sm.red[(q - q0) * BM + pl];
+                // all the peers' pieces of a token are asked for at once (a cluster has at most 8 CTAs), then
+                // added in the order of the ranks
                 if constexpr (EPI == 0) {
+                    float v[8];
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) v[r] = r < splits ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
                     float acc = 0.f;
-                    for (int r = 0; r < splits; ++r) acc += ld_peer_shared(mine, (uint32_t)r);
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) acc += v[r];
                     if (p < P) C[(size_t)q * ldc + p] = from_float<TO>(acc);
                 } else {
                     if (pl < 64) {
+                        float vg[8], vu[8];
+#pragma unroll
+                        for (int r = 0; r < 8; ++r) {
+                            vg[r] = r < splits ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
+                            vu[r] = r < splits ? ld_peer_shared(mine + 64, (uint32_t)r) : 0.f;
+                        }
                         float g = 0.f, u = 0.f;
-                        for (int r = 0; r < splits; ++r) { g += ld_peer_shared(mine, (uint32_t)r); u += ld_peer_shared(mine + 64, (uint32_t)r); }
+#pragma unroll
+                        for (int r = 0; r < 8; ++r) { g += vg[r]; u += vu[r]; }
                         if (p + 64 < P) C[(size_t)q * ldc + (p0 / 2 + pl)] = from_float<TO>(silu_mul(g, u));
                     }
                 }
