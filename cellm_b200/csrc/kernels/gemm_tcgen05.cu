@@ -860,9 +860,9 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
     int split;
     cellm_gemm_tcgen05_plan(M, N, K, bn, split_k, epilogue, &ws_floats, &split);
     static const bool use_cluster = [] { const char* e = std::getenv("CELLM_B200_CLUSTER_REDUCE"); return !(e && e[0] == '0'); }();
-    // swapped tiles whose K split fits a cluster (2..8 CTAs, one token tile) sum their pieces through shared memory
+    // swapped tiles whose K split fits a cluster (2..8 CTAs) sum their pieces through shared memory
     // (an unsplit SwiGLU tile takes the same road as a cluster of one: gate and up meet in shared memory)
-    const bool in_cluster = swap && M <= narrow && use_cluster && ((split >= 2 && split <= 8) || (split == 1 && epilogue == 1));
+    const bool in_cluster = swap && use_cluster && ((split >= 2 && split <= 8) || (split == 1 && epilogue == 1));
     if (in_cluster) ws_floats = 0;
     const int kblocks = (K + BK - 1) / BK;
     const int per = (kblocks + split - 1) / split;

@@ -6,7 +6,7 @@ from ._lib import check, count_launch, fn, ptr, require_cuda, stream_of
 from .basic import attention_plain
 
 _FLASH_HEAD_SIZES = (32, 64, 128)
-# When prompt portions go to the tcgen05 kernel: at least `min_ctas` CTAs (None: one for every other SM)
+# When prompt portions go to the tcgen05 kernel: at least `min_ctas` CTAs (None: an eighth of the SMs; below that the mma.sync kernel with its split over the keys fills the GPU better)
 # and at least `min_fill` of the tiles' rows in use. Tests lower both to drive small cases there.
 TC_POLICY = {"min_ctas": None, "min_fill": 0.5}
 _WORKSPACE: dict[torch.device, torch.Tensor] = {}
@@ -139,7 +139,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, 
         if attention_tc_supports(hd, nh, k_pool.shape[1], k_pool.shape[2]):
             per_tile = 256 // G
             tc_tiles = sum((n + per_tile - 1) // per_tile for n in ctx.q_lens)
-            min_ctas = _sms(q.device) // 2 if TC_POLICY["min_ctas"] is None else TC_POLICY["min_ctas"]
+            min_ctas = _sms(q.device) // 8 if TC_POLICY["min_ctas"] is None else TC_POLICY["min_ctas"]
             if tc_tiles * k_pool.shape[1] >= min_ctas and ctx.T >= TC_POLICY["min_fill"] * tc_tiles * per_tile:
                 return attention_tc(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.q_lens, nh,
                                     scale, window, ctx.err)

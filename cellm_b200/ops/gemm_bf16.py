@@ -82,10 +82,13 @@ def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
         if waves128 * 0.55 < waves256 * 0.95:
             bn = 128
     tiles = ((N + bn - 1) // bn) * ((M + 127) // 128)
-    split = 1
     if tiles < sms // 2:
-        split = max(1, min(sms // tiles, kblocks // 4))
-    return bn, split
+        # Too few plain tiles to fill the GPU (a few hundred tokens, or a narrow product): swapped tiles of 128
+        # weight rows by 64 tokens, several token tiles side by side, the K split of each summed in a cluster.
+        stiles = ((N + 127) // 128) * ((M + 63) // 64)
+        split = 1 if stiles >= sms * 85 // 100 else max(1, min(-(-(sms * 85 // 100) // stiles), kblocks // 4, 8))
+        return -64, split
+    return bn, 1
 
 
 def _effective_split(K: int, split_k: int) -> int:
@@ -106,7 +109,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bn: i
     split = _effective_split(K, split_k)
     # swapped tiles whose K split is one thread-block cluster (2..8 CTAs) sum their pieces
     # through shared memory: no workspace, no counters
-    in_cluster = bn < 0 and M <= -bn and _CLUSTER_REDUCE and (2 <= split <= 8 or (split == 1 and epilogue == 1))
+    in_cluster = bn < 0 and _CLUSTER_REDUCE and (2 <= split <= 8 or (split == 1 and epilogue == 1))
     through_ws = not in_cluster and (split > 1 or (epilogue == 1 and bn < 0))
     ws = _workspace(a.device, split * M * N) if through_ws else None
     counters = _counters(a.device) if (split > 1 and not in_cluster) else None
