@@ -424,7 +424,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 }
             }
             bool last = true;
-            if (splits > 1) {
+            if (splits > 1 && counters == nullptr) {
+                last = false;          // the pieces are summed by a kernel of their own (splitk_sum_kernel)
+            } else if (splits > 1) {
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (threadIdx.x == 64) {
@@ -554,6 +556,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// Sum of the K-split pieces of a product with plain tiles, ws[split][M][N], in the order of the splits; one
+// thread for four neighbouring outputs. EPI as in the product's kernel (1: gate and up blocks of 64 columns).
+template <int EPI, typename TO>
+__global__ void splitk_sum_kernel(const float* __restrict__ ws, TO* __restrict__ C, int M, int N, long long ldc, int splits) {
+    pdl_trigger();
+    pdl_wait();
+    const int NO = EPI == 1 ? N / 2 : N;                       // output columns
+    const long long groups = (long long)M * ((NO + 3) / 4);
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= groups) return;
+    const int m = (int)(g / ((NO + 3) / 4)), o0 = (int)(g % ((NO + 3) / 4)) * 4;
+    const size_t slice = (size_t)M * (size_t)N;
+    float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+    // input column of output column o: itself, or the gate of block o / 64 (its up lies 64 further on)
+    const int c0 = EPI == 1 ? (o0 / 64) * 128 + (o0 % 64) : o0;
+    const bool vec = (N & 3) == 0 && o0 + 3 < NO;              // four columns never straddle a block of 64
+    for (int sp = 0; sp < splits; ++sp) {
+        const float* src = ws + (size_t)sp * slice + (size_t)m * N + c0;
+        if (vec) {
+            const float4 v = *reinterpret_cast<const float4*>(src);
+            a[0] += v.x; a[1] += v.y; a[2] += v.z; a[3] += v.w;
+            if (EPI == 1) {
+                const float4 u = *reinterpret_cast<const float4*>(src + 64);
+                b[0] += u.x; b[1] += u.y; b[2] += u.z; b[3] += u.w;
+            }
+        } else {
+            for (int j = 0; j < 4 && o0 + j < NO; ++j) {
+                a[j] += src[j];
+                if (EPI == 1) b[j] += src[64 + j];
+            }
+        }
+    }
+    for (int j = 0; j < 4 && o0 + j < NO; ++j)
+        C[(size_t)m * ldc + o0 + j] = from_float<TO>(EPI == 1 ? silu_mul(a[j], b[j]) : a[j]);
 }
 
 // Persistent form for large products (plain tiles, no K split): one CTA per SM walks
@@ -867,7 +905,10 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
     const int kblocks = (K + BK - 1) / BK;
     const int per = (kblocks + split - 1) / split;
     if (ws_floats > 0 && workspace == nullptr) return CELLM_ERR_ARG;
-    if (split > 1 && !in_cluster) {
+    // Plain tiles without counters: the pieces go to the workspace and a second kernel sums them, all SMs at work
+    // (with counters the last CTA of a tile sums its pieces alone, which is slow for tiles of 128 tokens).
+    const bool sum_later = split > 1 && !in_cluster && !swap && counters == nullptr;
+    if (split > 1 && !in_cluster && !sum_later) {
         if (counters == nullptr) return CELLM_ERR_ARG;
         const long long tiles = swap ? (long long)((N + BM - 1) / BM) * ((M + narrow - 1) / narrow)
                                      : (long long)((N + narrow - 1) / narrow) * ((M + BM - 1) / BM);
@@ -921,5 +962,14 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
 #undef GO2
 #undef GO3
 #undef GOS
+    if (rc == CELLM_OK && sum_later) {
+        const int NO = epilogue == 1 ? N / 2 : N;
+        const long long groups = (long long)M * ((NO + 3) / 4);
+        const unsigned blocks = (unsigned)((groups + 255) / 256);
+        if (epilogue == 0 && out_dtype == CELLM_F32) CELLM_RUN((splitk_sum_kernel<0, float>), blocks, 256, 0, stream, workspace, (float*)C, M, N, ldc, split);
+        else if (epilogue == 0) CELLM_RUN((splitk_sum_kernel<0, __nv_bfloat16>), blocks, 256, 0, stream, workspace, (__nv_bfloat16*)C, M, N, ldc, split);
+        else if (out_dtype == CELLM_F32) CELLM_RUN((splitk_sum_kernel<1, float>), blocks, 256, 0, stream, workspace, (float*)C, M, N, ldc, split);
+        else CELLM_RUN((splitk_sum_kernel<1, __nv_bfloat16>), blocks, 256, 0, stream, workspace, (__nv_bfloat16*)C, M, N, ldc, split);
+    }
     return rc;
 }

@@ -83,11 +83,17 @@ def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
             bn = 128
     tiles = ((N + bn - 1) // bn) * ((M + 127) // 128)
     if tiles < sms // 2:
-        # Too few plain tiles to fill the GPU (a few hundred tokens, or a narrow product): swapped tiles of 128
-        # weight rows by 64 tokens, several token tiles side by side, the K split of each summed in a cluster.
-        stiles = ((N + 127) // 128) * ((M + 63) // 64)
-        split = 1 if stiles >= sms * 85 // 100 else max(1, min(-(-(sms * 85 // 100) // stiles), kblocks // 4, 8))
-        return -64, split
+        # Too few plain tiles to fill the GPU (a few hundred tokens, or a narrow product).
+        if M <= 128:
+            # up to two token tiles: swapped tiles of 128 weight rows by 64 tokens, the K split summed in a cluster
+            stiles = ((N + 127) // 128) * ((M + 63) // 64)
+            split = 1 if stiles >= sms * 85 // 100 else max(1, min(-(-(sms * 85 // 100) // stiles), kblocks // 4, 8))
+            return -64, split
+        # more tokens: tiles of 128 x 128 with K split until the SMs are filled; the pieces go through the
+        # workspace and a second kernel sums them (measured at 512 tokens: 23 us against 29 us for swapped tiles)
+        bn = 128 if N > 64 else 64
+        tiles = ((N + bn - 1) // bn) * ((M + 127) // 128)
+        return bn, max(1, min(-(-(sms * 85 // 100) // tiles), kblocks // 4, 16))
     return bn, 1
 
 
@@ -112,7 +118,9 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bn: i
     in_cluster = bn < 0 and _CLUSTER_REDUCE and (2 <= split <= 8 or (split == 1 and epilogue == 1))
     through_ws = not in_cluster and (split > 1 or (epilogue == 1 and bn < 0))
     ws = _workspace(a.device, split * M * N) if through_ws else None
-    counters = _counters(a.device) if (split > 1 and not in_cluster) else None
+    # plain tiles leave the sum of their K-split pieces to a second kernel (no counters); swapped tiles outside a
+    # cluster let the last CTA of a tile sum them
+    counters = _counters(a.device) if (split > 1 and not in_cluster and bn < 0) else None
     err = err if err is not None else error_word(a.device)
     check(fn("gemm_tcgen05", "cellm_gemm_tcgen05")(
         ptr(c), ptr(a), ptr(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), tag(out_dtype), int(bn),

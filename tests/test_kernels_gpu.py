@@ -399,6 +399,7 @@ def test_gemm_plain(dtype, out, M, N, K):
     (129, 257, 72, 256, 1), (1, 1000, 224, -16, 1), (8, 512, 2048, -16, 4), (17, 130, 8192, -32, 8),
     (40, 1000, 224, -64, 1), (64, 96, 96, -64, 2), (70, 300, 4096, 64, 4),
     (130, 300, 1024, -64, 4), (500, 2048, 2048, -64, 1), (70, 520, 512, -32, 2),     # swapped tiles, several token tiles side by side
+    (512, 2048, 2048, 128, 4), (300, 330, 1024, 128, 16), (200, 72, 4096, 64, 8),     # plain tiles, pieces summed by a second kernel
     (1500, 4000, 256, 256, 1), (2100, 2500, 192, 128, 1)])      # more tiles than SMs: CTAs of the persistent kernel loop
 def test_gemm_tcgen05(out, M, N, K, bn, split):
     from cellm_b200.ops.gemm_bf16 import error_word, gemm_tcgen05
@@ -416,7 +417,7 @@ def test_gemm_tcgen05(out, M, N, K, bn, split):
 
 
 @pytest.mark.parametrize("M,ff,K,bn,split", [(8, 192, 64, -16, 1), (3, 128, 2048, -16, 4), (40, 320, 96, -64, 1), (64, 64, 512, -64, 2),
-                                              (150, 256, 512, -64, 1), (100, 128, 1024, -64, 4),
+                                              (150, 256, 512, -64, 1), (100, 128, 1024, -64, 4), (400, 192, 2048, 128, 8),
                                               (130, 192, 64, 128, 1), (300, 256, 1024, 256, 1), (70, 128, 4096, 128, 4), (200, 384, 2048, 256, 2),
                                               (1300, 2560, 128, 256, 1), (2500, 1152, 64, 128, 1)])
 def test_gemm_tcgen05_swiglu_epilogue(M, ff, K, bn, split):
