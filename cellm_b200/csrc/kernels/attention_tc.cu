@@ -34,7 +34,6 @@
 #include <cuda.h>
 
 #include <mutex>
-#include <unordered_map>
 
 #include "common.cuh"
 
