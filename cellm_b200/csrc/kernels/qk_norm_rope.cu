@@ -99,10 +99,12 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
 }
 
 // Fast form for long batches of bfloat16 rows with 64-wide heads turned whole in the
-// "half" layout: one warp takes one token and walks its heads; a lane holds values
-// 2l, 2l+1 of a head, whose rotation partners (+-32) sit in lane l ^ 16, so a head
-// needs no shared memory: one 4-byte load, five shuffles for the norm, one for the
-// partner, one 4-byte store.
+// "half" layout. One warp takes one token and a run of its heads (query, key and
+// value heads alike), four heads at a time: a lane holds eight neighbouring values
+// of a head (one 16-byte load and store), eight lanes a head. The token's 32
+// cosines and sines are computed once per warp (lane l: frequency l) and passed
+// through shared memory; a head's sum of squares takes three shuffles, and the
+// rotation partners (+-32 values) sit four lanes away.
 template <typename TW>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_hd64_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv, long long row_stride,
@@ -111,29 +113,35 @@ qk_norm_rope_hd64_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16*
                          const int* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ k_pool,
                          __nv_bfloat16* __restrict__ v_pool, int num_pages, int page_size, int T, int nh, int nkv,
                          const float* __restrict__ inv_freq, int* __restrict__ err) {
+    __shared__ float trig[4][64];            // per warp: 32 cosines, 32 sines
     pdl_trigger();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
     if (t >= T) return;
     const int pos = positions[t];
-    // this lane's two frequencies: f = (2l mod 32) + {0, 1}
-    const int f0 = (2 * lane) & 31;
-    float cs[2], sn[2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const float hi = inv_freq[2 * (f0 + j)], lo = inv_freq[2 * (f0 + j) + 1], fp = (float)pos;
+    {
+        const float hi = inv_freq[2 * lane], lo = inv_freq[2 * lane + 1], fp = (float)pos;
         const float a = fp * hi;
         const float e = fmaf(fp, hi, -a) + fp * lo;
         float s, c, se, ce;
         sincosf(a, &s, &c);
         sincosf(e, &se, &ce);
-        cs[j] = c * ce - s * se;
-        sn[j] = s * ce + c * se;
+        trig[warp][lane] = c * ce - s * se;
+        trig[warp][32 + lane] = s * ce + c * se;
     }
-    const float sign = lane < 16 ? -1.f : 1.f;        // first half: x0 cos - x1 sin; second half: x1 cos + x0 sin
-    float wq[2] = {1.f, 1.f}, wk[2] = {1.f, 1.f};
-    if (q_w) { wq[0] = to_float(q_w[2 * lane]); wq[1] = to_float(q_w[2 * lane + 1]); wk[0] = to_float(k_w[2 * lane]); wk[1] = to_float(k_w[2 * lane + 1]); }
+    __syncwarp();
+    const int chunk = lane & 7;              // values 8 * chunk .. 8 * chunk + 7 of the head
+    const int f0 = (chunk & 3) * 8;          // their frequencies (value i turns with frequency i mod 32)
+    float cs[8], sn[8], wq[8], wk[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        cs[j] = trig[warp][f0 + j];
+        sn[j] = trig[warp][32 + f0 + j];
+        wq[j] = q_w ? to_float(q_w[chunk * 8 + j]) : 1.f;
+        wk[j] = k_w ? to_float(k_w[chunk * 8 + j]) : 1.f;
+    }
+    const float sign = chunk < 4 ? -1.f : 1.f;     // first half: x0 cos - x1 sin; second half: x1 cos + x0 sin
     long long page_base = -1;
     if (nkv > 0) {
         const int b = seq_of_token[t];
@@ -142,28 +150,56 @@ qk_norm_rope_hd64_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16*
         else page_base = (long long)page * nkv * page_size * 64 + (long long)(pos % page_size) * 64;
     }
     const __nv_bfloat16* row = qkv + (size_t)t * row_stride;
-    // blockIdx.y takes a run of the query and key heads (the last run also copies the values)
-    const int per = (nh + nkv + gridDim.y - 1) / gridDim.y;
-    const int h_begin = blockIdx.y * per, h_end = min(nh + nkv, h_begin + per);
-#pragma unroll 4
-    for (int hh = h_begin; hh < h_end; ++hh) {
-        const bool is_q = hh < nh;
-        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + (size_t)hh * 64 + 2 * lane));
-        float n0 = v.x, n1 = v.y;
-        if (q_w) {
-            const float inv = 1.0f / sqrtf(warp_sum(v.x * v.x + v.y * v.y) / 64.f + eps);
-            n0 = v.x * inv * (is_q ? wq[0] : wk[0]);
-            n1 = v.y * inv * (is_q ? wq[1] : wk[1]);
+    // blockIdx.y takes a run of the token's heads: queries, then keys, then values
+    const int all = nh + 2 * nkv;
+    const int per = ((all + gridDim.y - 1) / gridDim.y + 3) / 4 * 4;
+    const int h_begin = blockIdx.y * per, h_end = min(all, h_begin + per);
+#pragma unroll 2
+    for (int h0 = h_begin; h0 < h_end; h0 += 4) {
+        const int hh = h0 + (lane >> 3);
+        const bool on = hh < h_end;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (on) raw = *reinterpret_cast<const uint4*>(row + (size_t)hh * 64 + chunk * 8);
+        const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
+        float v[8];
+        {
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(p2[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
         }
-        const float p0 = __shfl_xor_sync(0xffffffffu, n0, 16), p1 = __shfl_xor_sync(0xffffffffu, n1, 16);
-        const __nv_bfloat162 o = __floats2bfloat162_rn(n0 * cs[0] + sign * p0 * sn[0], n1 * cs[1] + sign * p1 * sn[1]);
-        if (is_q) *reinterpret_cast<__nv_bfloat162*>(q_out + (size_t)t * nh * 64 + (size_t)hh * 64 + 2 * lane) = o;
-        else if (page_base >= 0) *reinterpret_cast<__nv_bfloat162*>(k_pool + page_base + (long long)(hh - nh) * page_size * 64 + 2 * lane) = o;
+        if (q_w) {                          // (all lanes shuffle; value heads drop the result)
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+            const float inv = 1.0f / sqrtf(ss / 64.f + eps);
+            if (is_q || is_k) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = v[j] * inv * (is_q ? wq[j] : wk[j]);
+            }
+        }
+        uint4 outw;
+        {
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&outw);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                const float p0 = __shfl_xor_sync(0xffffffffu, v[j], 4), p1 = __shfl_xor_sync(0xffffffffu, v[j + 1], 4);
+                const __nv_bfloat162 o = (is_q || is_k)
+                    ? __floats2bfloat162_rn(v[j] * cs[j] + sign * p0 * sn[j], v[j + 1] * cs[j + 1] + sign * p1 * sn[j + 1])
+                    : __floats2bfloat162_rn(v[j], v[j + 1]);
+                ow[j >> 1] = *reinterpret_cast<const uint32_t*>(&o);
+            }
+        }
+        if (!on) continue;
+        if (is_q) *reinterpret_cast<uint4*>(q_out + (size_t)t * nh * 64 + (size_t)hh * 64 + chunk * 8) = outw;
+        else if (page_base >= 0) {
+            __nv_bfloat16* pool = is_k ? k_pool : v_pool;
+            const int kvh = is_k ? hh - nh : hh - nh - nkv;
+            *reinterpret_cast<uint4*>(pool + page_base + (long long)kvh * page_size * 64 + chunk * 8) = is_k ? outw : raw;
+        }
     }
-    if (page_base >= 0 && blockIdx.y == gridDim.y - 1)
-        for (int hh = 0; hh < nkv; ++hh)
-            *reinterpret_cast<uint32_t*>(v_pool + page_base + (long long)hh * page_size * 64 + 2 * lane) =
-                *reinterpret_cast<const uint32_t*>(row + (size_t)(nh + nkv + hh) * 64 + 2 * lane);
 }
 
 // qkv: [T, row_stride] rows holding nh query heads, then nkv key heads, then nkv
@@ -179,9 +215,10 @@ CELLM_API int cellm_qk_norm_rope(void* q_out, const void* qkv, long long row_str
     if (T <= 0) return CELLM_OK;
     if (rot < 0 || rot > hd || (rot & 1)) return CELLM_ERR_SIZE;
     if ((q_w == nullptr) != (k_w == nullptr)) return CELLM_ERR_ARG;
-    if (act_dtype == CELLM_BF16 && hd == 64 && rot == 64 && !interleaved && T >= 256 && (row_stride & 1) == 0 &&
-        (((uintptr_t)q_out | (uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) & 3) == 0) {
-        const dim3 blocks((unsigned)((T + 3) / 4), (unsigned)((nh + nkv + 7) / 8));
+    if (act_dtype == CELLM_BF16 && hd == 64 && rot == 64 && !interleaved && T >= 256 && (row_stride & 7) == 0 &&
+        (((uintptr_t)q_out | (uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0) {
+        // heads in runs of sixteen: enough warps to keep loads in flight, few repeats of a token's cosines and sines
+        const dim3 blocks((unsigned)((T + 3) / 4), (unsigned)((nh + 2 * nkv + 15) / 16));
         if (w_dtype == CELLM_BF16 || q_w == nullptr)
             CELLM_RUN(qk_norm_rope_hd64_kernel<__nv_bfloat16>, blocks, 128, 0, stream, (__nv_bfloat16*)q_out,
                       (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, eps,

@@ -115,6 +115,101 @@ __global__ void short_conv_fwd_vec8_kernel(__nv_bfloat16* __restrict__ y, const 
     *reinterpret_cast<uint4*>(y + (size_t)t * H + c0) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// The same again for long portions (TAPS = 2, 3 or 4): a thread takes eight neighbouring channels
+// of a run of RUN tokens and keeps the last TAPS - 1 products B.x in registers as it walks the run, so
+// every row of bcx is read once. A run may cross from one request into the next: at a request's first
+// token the window is taken from that request's state.
+template <typename TW, int TAPS, int RUN>
+__global__ void short_conv_fwd_run_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ bcx,
+                                          const TW* __restrict__ w, const TW* __restrict__ bias,
+                                          const float* __restrict__ state, long long slot_stride,
+                                          const int* __restrict__ slot_ids, const int* __restrict__ seq_of_token,
+                                          const int* __restrict__ cu_seqlens, int T, int H, int n_slots,
+                                          int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    const int t0 = blockIdx.x * RUN;
+    const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c0 >= H || t0 >= T) return;
+    auto load8 = [](const __nv_bfloat16* p, float* out) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); out[2 * j] = f.x; out[2 * j + 1] = f.y; }
+    };
+    float wt[TAPS][8], bs[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int k = 0; k < TAPS; ++k) wt[k][j] = to_float(w[(size_t)(c0 + j) * TAPS + k]);
+        bs[j] = bias ? to_float(bias[c0 + j]) : 0.f;
+    }
+    float win[TAPS - 1][8];          // B.x of the TAPS - 1 tokens before the current one, oldest first
+    int b = -1, b_start = 0;
+    const float* st = nullptr;
+    bool bad = false;
+#pragma unroll 4
+    for (int t = t0; t < min(T, t0 + RUN); ++t) {
+        const int bt = seq_of_token[t];
+        if (bt != b) {                // the run's first token, or the first token of the next request
+            b = bt;
+            b_start = cu_seqlens[b];
+            const int slot = slot_ids[b];
+            bad = slot < 0 || slot >= n_slots;
+            if (bad) { if (threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_SLOT); }
+            else st = state + (long long)slot * slot_stride;
+            // the window: tokens of this request before t where there are any, else rows of the state
+#pragma unroll
+            for (int k = 0; k < TAPS - 1; ++k) {
+                const int jj = (t - b_start) - (TAPS - 1) + k;     // index within the request's portion
+                if (bad) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) win[k][j] = 0.f;
+                } else if (jj >= 0) {
+                    const __nv_bfloat16* row = bcx + (size_t)(b_start + jj) * 3 * H;
+                    float bb[8], xx[8];
+                    load8(row + c0, bb);
+                    load8(row + 2 * H + c0, xx);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) win[k][j] = bb[j] * xx[j];
+                } else {
+                    const float4 a = *reinterpret_cast<const float4*>(st + (size_t)(TAPS - 1 + jj) * H + c0);
+                    const float4 d = *reinterpret_cast<const float4*>(st + (size_t)(TAPS - 1 + jj) * H + c0 + 4);
+                    win[k][0] = a.x; win[k][1] = a.y; win[k][2] = a.z; win[k][3] = a.w;
+                    win[k][4] = d.x; win[k][5] = d.y; win[k][6] = d.z; win[k][7] = d.w;
+                }
+            }
+        }
+        const __nv_bfloat16* row = bcx + (size_t)t * 3 * H;
+        float bb[8], cc[8], xx[8], cur[8];
+        load8(row + c0, bb);
+        load8(row + H + c0, cc);
+        load8(row + 2 * H + c0, xx);
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            cur[j] = bb[j] * xx[j];
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < TAPS - 1; ++k) acc += win[k][j] * wt[k][j];      // oldest tap first, as the other kernels add
+            acc += cur[j] * wt[TAPS - 1][j];
+            cc[j] = cc[j] * (acc + bs[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 pk = __floats2bfloat162_rn(cc[2 * j], cc[2 * j + 1]);
+            o[j] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+        if (!bad) *reinterpret_cast<uint4*>(y + (size_t)t * H + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+        for (int k = 0; k + 1 < TAPS - 1; ++k)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) win[TAPS - 2][j] = cur[j];
+    }
+}
+
 template <typename TA>
 __global__ void short_conv_state_kernel(const TA* __restrict__ bcx, float* __restrict__ state,
                                         long long slot_stride, const int* __restrict__ slot_ids,
@@ -205,7 +300,13 @@ CELLM_API int cellm_short_conv(void* y, const void* bcx, const void* w, const vo
                       (const TW*)w, (const TW*)bias, state, slot_stride, slot_ids, cu_seqlens, H, taps, n_slots, err); \
             break;                                                                                  \
         }                                                                                           \
-        if (vec8) {                                                                                 \
+        if (vec8 && T >= 256 && taps >= 2 && taps <= 4) {                                          \
+            /* long portions: runs of eight tokens per thread, each row of bcx read once */        \
+            dim3 grid_r((unsigned)((T + 7) / 8), (unsigned)((H / 8 + threads - 1) / threads));      \
+            if (taps == 2) CELLM_RUN((short_conv_fwd_run_kernel<TW, 2, 8>), grid_r, threads, 0, stream, (__nv_bfloat16*)y, (const __nv_bfloat16*)bcx, (const TW*)w, (const TW*)bias, (const float*)state, slot_stride, slot_ids, seq_of_token, cu_seqlens, T, H, n_slots, err); \
+            else if (taps == 3) CELLM_RUN((short_conv_fwd_run_kernel<TW, 3, 8>), grid_r, threads, 0, stream, (__nv_bfloat16*)y, (const __nv_bfloat16*)bcx, (const TW*)w, (const TW*)bias, (const float*)state, slot_stride, slot_ids, seq_of_token, cu_seqlens, T, H, n_slots, err); \
+            else CELLM_RUN((short_conv_fwd_run_kernel<TW, 4, 8>), grid_r, threads, 0, stream, (__nv_bfloat16*)y, (const __nv_bfloat16*)bcx, (const TW*)w, (const TW*)bias, (const float*)state, slot_stride, slot_ids, seq_of_token, cu_seqlens, T, H, n_slots, err); \
+        } else if (vec8) {                                                                          \
             CELLM_RUN(short_conv_fwd_vec8_kernel<TW>, grid_v, threads, 0, stream, (__nv_bfloat16*)y,     \
                       (const __nv_bfloat16*)bcx, (const TW*)w, (const TW*)bias, (const float*)state, slot_stride, \
                       slot_ids, seq_of_token, cu_seqlens, H, taps, n_slots, err);                   \

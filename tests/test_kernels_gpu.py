@@ -117,6 +117,47 @@ def test_short_conv_portions_carry_the_state(dtype, taps, bias, walk):
         close(torch.cat(got[r]), whole(bcx[r]), dtype, f"request {r}")
 
 
+@pytest.mark.parametrize("taps,bias", [(2, False), (3, True), (4, False), (5, True)])
+def test_short_conv_long_portions_of_several_requests(taps, bias):
+    """Portions of hundreds of bfloat16 tokens (the kernel that walks runs of eight
+    tokens per thread): three requests whose portions start and end off the runs'
+    edges, one of them continuing from a state, and a second step that continues all."""
+    from cellm_b200 import ops
+    H, slots = 264, 5
+    lens = {0: 530, 1: 301, 2: 95}
+    g = torch.Generator(device=DEV).manual_seed(taps)
+    bcx = {r: torch.randn(n, 3 * H, device=DEV, generator=g).bfloat16() for r, n in lens.items()}
+    w = (torch.randn(H, taps, device=DEV, generator=g) * 0.5).bfloat16()
+    b = (torch.randn(H, device=DEV, generator=g) * 0.5).bfloat16() if bias else None
+
+    def whole(x):
+        x = x.double().cpu()
+        B, C, xt = x[:, :H], x[:, H:2 * H], x[:, 2 * H:]
+        hist = torch.cat([torch.zeros(taps - 1, H, dtype=torch.float64), B * xt])
+        conv = sum(hist[k:k + x.shape[0]] * w.double().cpu()[:, k] for k in range(taps))
+        return C * (conv + (b.double().cpu() if bias else 0))
+    state = torch.zeros(slots, taps - 1, H, device=DEV)
+    state[4] = 7.0
+    slot_of = {0: 3, 1: 0, 2: 2}
+    fed = {r: 0 for r in lens}
+    got = {r: [] for r in lens}
+    e = err_word()
+    for step in ([(0, 3)], [(0, 261), (1, 300), (2, 95)], [(1, 1), (0, 266)]):     # the first step leaves request 0 a state
+        rows = torch.cat([bcx[r][fed[r]:fed[r] + n] for r, n in step])
+        cu = torch.tensor(np.cumsum([0] + [n for _, n in step]), dtype=torch.int32, device=DEV)
+        seq = torch.cat([torch.full((n,), i) for i, (_, n) in enumerate(step)]).int().to(DEV)
+        sl = torch.tensor([slot_of[r] for r, _ in step], dtype=torch.int32, device=DEV)
+        y = ops.short_conv(rows, w, b, state, sl, seq, cu, e, max(n for _, n in step))
+        o = 0
+        for r, n in step:
+            got[r].append(y[o:o + n])
+            fed[r] += n
+            o += n
+    assert e.item() == 0 and fed == lens and bool((state[4] == 7).all())
+    for r in lens:
+        close(torch.cat(got[r]), whole(bcx[r]), torch.bfloat16, f"request {r}")
+
+
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("hd,rot,inter", [(16, 16, False), (48, 32, False), (64, 64, True), (32, 0, False)])
 def test_qk_norm_rope_and_page_write(dtype, hd, rot, inter):
