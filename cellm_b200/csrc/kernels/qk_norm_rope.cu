@@ -34,7 +34,8 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
     const int heads_per_block = (n_heads_all + gridDim.y - 1) / gridDim.y;
     const int h_begin = blockIdx.y * heads_per_block, h_end = min(n_heads_all, h_begin + heads_per_block);
     pdl_trigger();
-    pdl_wait();
+    // Positions, block table and frequencies are the step's inputs, not the work of the kernel before this one:
+    // the cosines, sines and the page look-up are done before the wait on it; only the rows of qkv come after.
     const int t = blockIdx.x;
     const int pos = positions[t];
     for (int p = threadIdx.x; p < rot / 2; p += blockDim.x) {
@@ -58,6 +59,7 @@ __global__ void qk_norm_rope_kernel(TA* __restrict__ q_out, const TA* __restrict
         }
     }
     __syncthreads();
+    pdl_wait();
     const TA* row = qkv + (size_t)t * row_stride;
     for (int hh = h_begin + warp; hh < h_end; hh += nwarps) {
         const TA* src = row + (size_t)hh * hd;

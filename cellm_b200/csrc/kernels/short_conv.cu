@@ -248,7 +248,9 @@ __global__ void short_conv_walk_kernel(TA* __restrict__ y, const TA* __restrict_
                                        const int* __restrict__ slot_ids, const int* __restrict__ cu_seqlens, int H,
                                        int taps, int n_slots, int* __restrict__ err) {
     pdl_trigger();
-    pdl_wait();
+    // The step's index arrays, the weights and the state (last written by this kernel in the step before) are the
+    // work of no kernel of this step: they are fetched before the wait on the kernel before this one; only the
+    // rows of bcx come after it.
     const int b = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= H) return;
@@ -264,6 +266,7 @@ __global__ void short_conv_walk_kernel(TA* __restrict__ y, const TA* __restrict_
     for (int r = 0; r < rows; ++r) hist[r] = st[(size_t)r * H + c];
     for (int k = 0; k < taps; ++k) wt[k] = to_float(w[(size_t)c * taps + k]);
     const float bs = bias ? to_float(bias[c]) : 0.f;
+    pdl_wait();
     for (int i = 0; i < n; ++i) {
         const TA* row = bcx + (size_t)(start + i) * 3 * H;
         const float bx = to_float(row[c]) * to_float(row[2 * H + c]);
