@@ -42,7 +42,8 @@ struct DecodeSmem {
     static constexpr size_t o_off = kv_off;                               // [NW][16][HD] float, over the ring once the keys are done
     static constexpr size_t ml_off = kv_off + (size_t)ST * 2 * KV_BYTES;  // [NW][16][2] float
     static constexpr size_t flag_off = ml_off + (size_t)NW * 16 * 2 * 4;
-    static constexpr size_t total = flag_off + 16;
+    static constexpr size_t pages_off = flag_off + 16;                    // [bt_stride] int: this CTA's slice of the block table
+    static constexpr size_t fixed = pages_off;
     static_assert((size_t)NW * 16 * HD * 4 <= (size_t)ST * 2 * KV_BYTES, "the warps' outputs must fit the ring");
 };
 
@@ -61,6 +62,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     float* o_s = reinterpret_cast<float*>(dec_smem + L::o_off);
     float* ml_s = reinterpret_cast<float*>(dec_smem + L::ml_off);
     int* flag_s = reinterpret_cast<int*>(dec_smem + L::flag_off);
+    int* page_s = reinterpret_cast<int*>(dec_smem + L::pages_off);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint8_t* kv_s = dec_smem + L::kv_off;
     constexpr int WK = FA_BN / NW;          // keys of a block that one warp takes (16 or 32)
@@ -82,24 +84,21 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     auto page_of = [&](int j) { return page_shift >= 0 ? (j >> page_shift) : (j / page_size); };
     auto slot_of = [&](int j) { return page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size); };
 
-    // By all threads. The pages of a thread's keys are looked up first, all at once,
-    // so that the copies that follow do not each wait for a load of the block table.
+    // The block-table entries of this CTA's keys come into shared memory in one round trip, so that the copies of
+    // a block do not each wait for a load of the table.
+    const int p_lo = page_of(my_begin * BN), p_hi = my_begin < my_end ? page_of(min(key_end, my_end * BN) - 1) + 1 : p_lo;
+    for (int i = threadIdx.x; i < p_hi - p_lo; i += THREADS) page_s[i] = bt[p_lo + i];
+    __syncthreads();
     constexpr int KV_ITERS = (BN * CH + THREADS - 1) / THREADS;
     auto load_kv = [&](int kb, int stage) {
         uint8_t* ks = kv_s + (size_t)stage * 2 * L::KV_BYTES;
         uint8_t* vs = ks + L::KV_BYTES;
-        int pages[KV_ITERS];
-#pragma unroll
-        for (int it = 0; it < KV_ITERS; ++it) {
-            const int i = threadIdx.x + it * THREADS, j = kb * BN + i / CH;
-            pages[it] = (i < BN * CH && j >= key_begin && j < key_end) ? bt[page_of(j)] : -1;
-        }
 #pragma unroll
         for (int it = 0; it < KV_ITERS; ++it) {
             const int i = threadIdx.x + it * THREADS;
             if (i >= BN * CH) break;
             const int row = i / CH, chunk = i % CH, j = kb * BN + row;
-            int page = pages[it];
+            int page = (j >= key_begin && j < key_end) ? page_s[page_of(j) - p_lo] : -1;
             if (j >= key_begin && j < key_end && (page < 0 || page >= num_pages)) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
             const size_t off = page >= 0 ? (size_t)page * page_elems + ((size_t)kvh * page_size + slot_of(j)) * HD + chunk * 8 : 0;
             cp_async16(ks + tile_offset<HD>(row, chunk), k_pool + off, page >= 0 ? 16 : 0);
@@ -296,12 +295,14 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, int* counte
                   const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool, const int* cu, const int* ctx, const int* bt,
                   int bt_stride, int B, int T, int num_pages, int page_size, int nh, int nkv, float scale, int window,
                   int nsplit, int* err, cudaStream_t stream) {
-    const size_t smem = DecodeSmem<HD, NW>::total;
-    static bool configured = false;
-    if (!configured) {
+    // the CTA's slice of a block-table row is at most the row
+    const size_t smem = DecodeSmem<HD, NW>::fixed + (size_t)(bt_stride > 0 ? bt_stride : 1) * sizeof(int);
+    if (smem > 200 * 1024) return CELLM_ERR_SIZE;
+    static size_t configured = 0;
+    if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured = smem;
     }
     dim3 grid((unsigned)B, (unsigned)nkv, (unsigned)nsplit);
     CELLM_RUN((attention_decode_kernel<HD, NW>), grid, NW * 32, smem, stream, out, part_o, part_ml, counters, q, k_pool,
