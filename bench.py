@@ -139,14 +139,18 @@ def time_decode(eng, ids, steps, warmup, rng, sampler=None):
     # device-timed: the step function and the arg-max on given tokens, no read back
     V = eng.plan.vocab_size
     toks = rng.integers(0, V, (warmup + steps, B))
+    def device_step(i):
+        # the step function and the arg-max of its logits (inside the step's graph where there is one)
+        logits = eng.runner.run([StepEntry(r, [int(toks[i, b])], [0]) for b, r in enumerate(ids)])
+        return eng.runner.last_argmax if eng.runner.last_argmax is not None else ops.argmax(logits)
     for i in range(warmup):
-        ops.argmax(eng.runner.run([StepEntry(r, [int(toks[i, b])], [0]) for b, r in enumerate(ids)]))
+        device_step(i)
     torch.cuda.synchronize()
     l0 = LAUNCHES[0]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(warmup, warmup + steps):
-        ops.argmax(eng.runner.run([StepEntry(r, [int(toks[i, b])], [0]) for b, r in enumerate(ids)]))
+        device_step(i)
     e1.record()
     torch.cuda.synchronize()
     if sampler:

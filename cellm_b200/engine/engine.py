@@ -110,7 +110,7 @@ class Engine:
         produced = []
         if rows:
             samplers = [self._samplers[r] for r in rows]
-            tokens = sample_rows(logits, samplers)
+            tokens = sample_rows(logits, samplers, self.runner.last_argmax)
             self.runner.check_rarely()
             eos = self.plan.eos_token_id
             stops = [s.params.stop_eos and eos is not None and tok == eos for s, tok in zip(samplers, tokens)]

@@ -17,6 +17,7 @@ from typing import Optional, Sequence
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager, OutOfPages
 from ..models.decoder import DecoderModel
 from ..parts.base import StepContext
@@ -52,6 +53,9 @@ class StepRunner:
         self.use_graphs = use_graphs and model.graph_safe
         self.graph_width_step = 32        # block-table widths are rounded up to this many pages per graph
         self._graphs: dict = {}
+        # arg-max of the last step's logits where the step's graph has computed it (greedy requests then
+        # need no launch of their own); None after a step that ran without a graph
+        self.last_argmax: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------
     def _staging(self, n: int) -> torch.Tensor:
@@ -189,6 +193,7 @@ class StepRunner:
             self.cache.commit(e.request_id, total)
         self.steps += 1
         self.tokens += B
+        self.last_argmax = g["argmax"]
         return g["logits"]
 
     def _layout(self, B: int, T: int, R: int, width: int):
@@ -244,7 +249,9 @@ class StepRunner:
             from ..ops._lib import LAUNCHES
             g["graph"].replay()
             LAUNCHES[0] += g["launches"]
+            self.last_argmax = g["argmax"]
             return g["logits"]
+        self.last_argmax = None
         dev = stage[:n_meta].to(self.device, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
@@ -270,6 +277,7 @@ class StepRunner:
         before = LAUNCHES[0]
         with torch.cuda.graph(graph):
             g["logits"] = self.model.forward(ctx, bindings, logit_rows)
+            g["argmax"] = ops.argmax(g["logits"])          # greedy requests read their tokens here
         g["graph"] = graph
         g["launches"] = LAUNCHES[0] - before     # kernels one replay runs
         LAUNCHES[0] = before
@@ -280,6 +288,7 @@ class StepRunner:
         The tensor may be overwritten by the next step."""
         if self.use_graphs and max_layers is None and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return self._run_decode_graph(entries)
+        self.last_argmax = None
         ctx, tables, logit_rows, totals = self.build_context(entries)
         logits = self.model.forward(ctx, self.cache.bindings(tables), logit_rows, max_layers)
         for e, total in zip(entries, totals):

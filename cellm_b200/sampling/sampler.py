@@ -22,13 +22,15 @@ class RequestSampler:
         self.history = list(history)
 
 
-def sample_rows(logits: torch.Tensor, samplers: Sequence[RequestSampler]) -> list[int]:
+def sample_rows(logits: torch.Tensor, samplers: Sequence[RequestSampler],
+                argmax: torch.Tensor | None = None) -> list[int]:
     """One token for each row of float32 logits [R, V]; advances the random
-    stream of every request that samples with temperature."""
+    stream of every request that samples with temperature. `argmax`: the rows'
+    arg-max if the step has computed it already (int32 [R])."""
     R = logits.shape[0]
     assert R == len(samplers)
     if all(s.params.temperature <= 0.0 for s in samplers):
-        return ops.argmax(logits).tolist()
+        return (argmax if argmax is not None and argmax.shape[0] == R else ops.argmax(logits)).tolist()
     W = max((s.params.repeat_window for s in samplers if s.params.repeat_penalty > 1.0), default=0)
     f = np.zeros((3, R), dtype=np.float32)
     k = np.zeros((R,), dtype=np.int32)
