@@ -18,6 +18,14 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_float(row[i]) : 0.f;
 }
 
+// The step's index arrays go up in one asynchronous copy from pinned host memory (a plain call of the runtime,
+// here so that the step function pays one short foreign call for it instead of a tensor operation).
+CELLM_API int cellm_upload(void* dst, const void* pinned_src, long long bytes, cudaStream_t stream) {
+    if (bytes <= 0) return CELLM_OK;
+    const cudaError_t e = cudaMemcpyAsync(dst, pinned_src, (size_t)bytes, cudaMemcpyHostToDevice, stream);
+    return e == cudaSuccess ? CELLM_OK : (int)e;
+}
+
 CELLM_API int cellm_embed(float* out, const void* table, int table_dtype, const int* ids, int T, int H,
                           int V, int* err, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;

@@ -46,8 +46,10 @@ class StepRunner:
         from ..ops.gemm_bf16 import error_word
         self.err = error_word(self.device)      # one error word for every kernel on this device
         self._pinned = [None, None]
-        self._events = [None, None]
+        self._events = [None, None]        # one reusable event per staging buffer: recorded after its upload
+        self._recorded = [False, False]
         self._flip = 0
+        self._layouts: dict = {}
         self.steps = 0
         self.tokens = 0
         self.use_graphs = use_graphs and model.graph_safe
@@ -62,11 +64,19 @@ class StepRunner:
         """A pinned int32 buffer of at least n values whose last upload has finished."""
         self._flip ^= 1
         i = self._flip
-        if self._events[i] is not None:
+        if self._recorded[i]:
             self._events[i].synchronize()
         if self._pinned[i] is None or self._pinned[i].numel() < n:
             self._pinned[i] = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=True)
         return self._pinned[i]
+
+    def _uploaded(self) -> None:
+        """Marks the point in the stream after which the current staging buffer may be written again."""
+        i = self._flip
+        if self._events[i] is None:
+            self._events[i] = torch.cuda.Event()
+        self._events[i].record()
+        self._recorded[i] = True
 
     def _prepare(self, entries: Sequence[StepEntry]):
         """Checks the entries and reserves their pages. Returns the host-side
@@ -156,9 +166,7 @@ class StepRunner:
         stage = self._staging(n_meta)
         spans, tables, n = self._fill(stage.numpy(), entries, q_lens, ctx_lens, slots, ids, cu, rows, width)
         dev = stage[:n_meta].to(self.device, non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self._events[self._flip] = ev
+        self._uploaded()
         ctx, tabs, logit_rows = self._context(dev, spans, tables, q_lens, ctx_lens, max(totals))
         return ctx, tabs, logit_rows, totals
 
@@ -180,10 +188,8 @@ class StepRunner:
         if g is None:
             g = {"meta": torch.empty(n_meta, dtype=torch.int32, device=self.device)}
             self._graphs[key] = g
-        g["meta"].copy_(stage[:n_meta], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self._events[self._flip] = ev
+        ops.upload(g["meta"], stage, n_meta)
+        self._uploaded()
         if "graph" not in g:
             self._capture(g, spans, tables, q_lens, ctx_lens, width * ps, slots)
         from ..ops._lib import LAUNCHES
@@ -222,13 +228,16 @@ class StepRunner:
         need = (max_total + ps - 1) // ps
         graph = self.use_graphs and all_decode and max_layers is None
         width = -(-need // self.graph_width_step) * self.graph_width_step if graph else need
-        spans, tables, n_meta = self._layout(B, T, R, width)
+        lay = self._layouts.get((B, T, R, width))
+        if lay is None:
+            lay = self._layouts[(B, T, R, width)] = self._layout(B, T, R, width)
+        spans, tables, n_meta = lay
         stage = self._staging(n_meta)
         scheduler.plan_fill(stage.data_ptr(), n_meta, width, len(self.cache.paged_keys))
-        buf = stage.numpy()
         if all_decode:
             q_lens, ctx_lens = [1] * B, None
         else:
+            buf = stage.numpy()
             cu = buf[spans["cu"][0]:spans["cu"][0] + B + 1]
             q_lens = np.diff(cu).tolist()
         self.steps += 1
@@ -239,12 +248,10 @@ class StepRunner:
             if g is None:
                 g = {"meta": torch.empty(n_meta, dtype=torch.int32, device=self.device)}
                 self._graphs[key] = g
-            g["meta"].copy_(stage[:n_meta], non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record()
-            self._events[self._flip] = ev
+            ops.upload(g["meta"], stage, n_meta)
+            self._uploaded()
             if "graph" not in g:
-                slots = buf[spans["slot"][0]:spans["slot"][0] + B].tolist()
+                slots = stage.numpy()[spans["slot"][0]:spans["slot"][0] + B].tolist()
                 self._capture(g, spans, tables, q_lens, [0] * B, width * ps, slots)
             from ..ops._lib import LAUNCHES
             g["graph"].replay()
@@ -253,10 +260,8 @@ class StepRunner:
             return g["logits"]
         self.last_argmax = None
         dev = stage[:n_meta].to(self.device, non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self._events[self._flip] = ev
-        ctx_lens = buf[spans["ctx"][0]:spans["ctx"][0] + B].tolist()
+        self._uploaded()
+        ctx_lens = stage.numpy()[spans["ctx"][0]:spans["ctx"][0] + B].tolist()
         ctx, tabs, logit_rows = self._context(dev, spans, tables, q_lens, ctx_lens, max_total)
         return self.model.forward(ctx, self.cache.bindings(tabs), logit_rows, max_layers)
 

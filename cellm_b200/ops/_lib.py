@@ -19,6 +19,7 @@ _ERRORS = {-1: "unsupported element type", -2: "a size this kernel does not take
 _SIGNATURES = {
     "kernels_common": {
         "cellm_embed": [P, P, I, P, I, I, I, P, P],
+        "cellm_upload": [P, P, L, P],
         "cellm_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P],
         "cellm_residual_add": [P, P, L, I, P],
         "cellm_swiglu": [P, P, I, I, I, P],

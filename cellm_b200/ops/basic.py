@@ -36,6 +36,16 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor,
     return y
 
 
+def upload(dst: torch.Tensor, pinned: torch.Tensor, n: int) -> None:
+    """The first n elements of a pinned host tensor into a device tensor of the same
+    element type, asynchronously on the current stream."""
+    if not dst.is_cuda or not pinned.is_pinned() or dst.dtype != pinned.dtype or n > dst.numel() or n > pinned.numel():
+        raise ValueError("upload: a pinned host tensor into a device tensor of the same element type")
+    code = fn(_LIB, "cellm_upload")(dst.data_ptr(), pinned.data_ptr(), n * dst.element_size(), stream_of(dst))
+    if code != 0:
+        raise RuntimeError(f"upload: CUDA error {code}")
+
+
 def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
     require_cuda(x, delta)
     if x.dtype != torch.float32 or x.shape != delta.shape:
