@@ -4,6 +4,30 @@
 // (crates/cellm-model/src/lfm.rs:806-815).
 #include "common.cuh"
 
+// Order-preserving 32-bit key of a logit (larger logit, larger key); non-finite logits count as -inf and -0 as +0,
+// so that equal logits have equal keys.
+__device__ __forceinline__ uint32_t float_key(float v) {
+    if (!isfinite(v)) v = -INFINITY;
+    v += 0.0f;
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+// (key of the logit, ~id): the larger of two is the larger logit, or among equal logits the lower id
+__device__ __forceinline__ unsigned long long pick_key(float v, int i) {
+    return ((unsigned long long)float_key(v) << 32) | (0xffffffffu - (uint32_t)i);
+}
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long k) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long t = __shfl_xor_sync(0xffffffffu, k, o);
+        k = t > k ? t : k;
+    }
+    return k;
+}
+
 // ---------------------------------------------------------------- arg-max
 // Largest logit of each row; among equal logits the lowest id wins (the
 // reference's stable descending sort puts it first). Non-finite logits count
@@ -42,8 +66,56 @@ __global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ l
     }
 }
 
-CELLM_API int cellm_argmax(int* out, const float* logits, int R, int V, cudaStream_t stream) {
+// The same in two steps for long rows, so that a few rows still use many SMs: ARGMAX_PARTS blocks a row each
+// leave the best (logit, id) of their run of the row, and one warp a row picks among those.
+#define ARGMAX_PARTS 32
+__global__ void __launch_bounds__(256)
+argmax_parts_kernel(unsigned long long* __restrict__ parts, const float* __restrict__ logits, int V) {
+    __shared__ unsigned long long best_w[8];
+    pdl_trigger();
+    pdl_wait();
+    const float* row = logits + (size_t)blockIdx.y * V;
+    const int per = ((V + ARGMAX_PARTS - 1) / ARGMAX_PARTS + 3) & ~3;
+    const int begin = blockIdx.x * per, end = min(V, begin + per);
+    unsigned long long best = 0ull;
+    if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        for (int i = begin + threadIdx.x * 4; i < end; i += 256 * 4) {        // per is a multiple of 4, so i + 3 < V
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            unsigned long long k = pick_key(v.x, i);
+            unsigned long long t = pick_key(v.y, i + 1); k = t > k ? t : k;
+            t = pick_key(v.z, i + 2); k = t > k ? t : k;
+            t = pick_key(v.w, i + 3); k = t > k ? t : k;
+            best = k > best ? k : best;
+        }
+    } else {
+        for (int i = begin + threadIdx.x; i < end; i += 256) {
+            const unsigned long long k = pick_key(row[i], i);
+            best = k > best ? k : best;
+        }
+    }
+    best = warp_max_u64(best);
+    if ((threadIdx.x & 31) == 0) best_w[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = warp_max_u64(threadIdx.x < 8 ? best_w[threadIdx.x] : 0ull);
+        if (threadIdx.x == 0) parts[(size_t)blockIdx.y * ARGMAX_PARTS + blockIdx.x] = best;
+    }
+}
+__global__ void argmax_pick_kernel(int* __restrict__ out, const unsigned long long* __restrict__ parts) {
+    pdl_trigger();
+    pdl_wait();
+    const unsigned long long k = warp_max_u64(threadIdx.x < ARGMAX_PARTS ? parts[(size_t)blockIdx.x * ARGMAX_PARTS + threadIdx.x] : 0ull);
+    if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xffffffffu - (uint32_t)(k & 0xffffffffu));
+}
+
+// parts: R * 32 64-bit words of scratch for rows of 8,192 logits or more (null: one block a row).
+CELLM_API int cellm_argmax(int* out, const float* logits, int R, int V, unsigned long long* parts, cudaStream_t stream) {
     if (R <= 0) return CELLM_OK;
+    if (parts != nullptr && V >= 8192) {
+        CELLM_RUN(argmax_parts_kernel, dim3(ARGMAX_PARTS, (unsigned)R), 256, 0, stream, parts, logits, V);
+        CELLM_RUN(argmax_pick_kernel, R, 32, 0, stream, out, (const unsigned long long*)parts);
+        return CELLM_OK;
+    }
     CELLM_RUN(argmax_kernel, R, 512, 0, stream, out, logits, V);
     return CELLM_OK;
 }
@@ -61,14 +133,6 @@ CELLM_API int cellm_argmax(int* out, const float* logits, int R, int V, cudaStre
 #define SAMPLE_THREADS 1024
 #define SAMPLE_MAX_K 1024
 
-__device__ __forceinline__ uint32_t float_key(float v) {
-    if (!isfinite(v)) v = -INFINITY;
-    const uint32_t b = __float_as_uint(v);
-    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-}
-__device__ __forceinline__ float key_float(uint32_t k) {
-    return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
-}
 
 // Inclusive scan of one value per thread over the block; returns this thread's
 // prefix and, through `total`, the block's sum. Fixed order.

@@ -6,7 +6,7 @@ import os
 
 import torch
 
-from ._lib import check, fn, ptr, stream_of, tag
+from ._lib import check, count_launch, fn, ptr, stream_of, tag
 from .gemm import gemm_plain
 
 _SM_COUNT: dict[int, int] = {}
@@ -126,6 +126,8 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bn: i
         ptr(c), ptr(a), ptr(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), tag(out_dtype), int(bn),
         int(split_k), int(epilogue), _STATIC_FLAG if w_is_static else 0, ptr(ws), ptr(counters), ptr(err), stream_of(a)),
         "gemm_tcgen05")
+    if bn > 0 and split > 1:
+        count_launch()          # the kernel that sums the K-split pieces
     return c
 
 
