@@ -186,11 +186,36 @@ __device__ __forceinline__ int block_scan_inclusive_int(int v, int* warp_tot, in
     return v + base;
 }
 
+// Largest key of every group of 128 logits of a row, a warp a group. The k-th largest of a row's group maxima is a
+// lower bound of its k-th largest logit (k different logits reach it), so sample_kernel looks only at the few logits
+// that reach that bound instead of selecting among all of them.
+#define SAMPLE_GROUP 128
+#define SAMPLE_MAX_GROUPS 8192
+__global__ void __launch_bounds__(256)
+group_max_kernel(uint32_t* __restrict__ gmax, const float* __restrict__ logits, int V, int G) {
+    pdl_trigger();
+    pdl_wait();
+    const int g = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (g >= G) return;
+    const float* row = logits + (size_t)blockIdx.y * V;
+    uint32_t key = 0u;
+#pragma unroll
+    for (int e = 0; e < SAMPLE_GROUP / 32; ++e) {
+        const int i = g * SAMPLE_GROUP + e * 32 + lane;
+        if (i < V) key = max(key, float_key(row[i]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) key = max(key, __shfl_xor_sync(0xffffffffu, key, o));
+    if (lane == 0) gmax[(size_t)blockIdx.y * G + g] = key;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ u, const float* __restrict__ penalty,
-              const int* __restrict__ recent, int W) {
+              const int* __restrict__ recent, int W, int bitmap_words, const uint32_t* __restrict__ gmax, int G,
+              int g_sort) {
+    extern __shared__ uint32_t dyn_words[];      // the groups' maxima (top-k rows) or a bit per id (whole rows)
     __shared__ unsigned long long cand[SAMPLE_MAX_K];
     __shared__ int hist[256];
     __shared__ float fscratch[32];
@@ -208,7 +233,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
     for (int i = tid; i < nrec; i += blockDim.x) s_recent[i] = recent[(size_t)r * W + i];
     __syncthreads();
 
-    if (temp <= 0.0f) {  // arg-max, lowest id among equals
+    if (temp <= 0.0f && gmax == nullptr) {  // arg-max, lowest id among equals
         float best = -INFINITY;
         int idx = 0x7fffffff;
         for (int i = tid; i < V; i += blockDim.x) {
@@ -234,9 +259,38 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
         return;
     }
 
-    int k = top_k[r];
+    int k = temp <= 0.0f ? 1 : top_k[r];          // with the groups' maxima the arg-max is the first of one candidate
     if (k >= V) k = 0;
     if (k > 0) {
+        int n = -1;                               // candidates in cand[], or -1 while there are none
+        if (gmax != nullptr && k <= G) {
+            // ---- the k-th largest group maximum bounds the k-th largest logit from below
+            for (int i = tid; i < g_sort; i += blockDim.x) dyn_words[i] = i < G ? gmax[(size_t)r * G + i] : 0u;
+            if (tid == 0) s_cnt = 0;
+            __syncthreads();
+            for (int size = 2; size <= g_sort; size <<= 1) {
+                for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                    for (int t = tid; t < g_sort / 2; t += blockDim.x) {
+                        const int lo = 2 * t - (t & (stride - 1)), hi = lo + stride;
+                        const uint32_t a = dyn_words[lo], b = dyn_words[hi];
+                        if ((a < b) == ((lo & size) == 0)) { dyn_words[lo] = b; dyn_words[hi] = a; }
+                    }
+                    __syncthreads();
+                }
+            }
+            const uint32_t bound = dyn_words[k - 1];
+            for (int i = tid; i < V; i += blockDim.x) {
+                const uint32_t key = float_key(row[i]);
+                if (key >= bound) {
+                    const int p = atomicAdd(&s_cnt, 1);
+                    if (p < SAMPLE_MAX_K) cand[p] = ((unsigned long long)key << 32) | (0xffffffffu - (uint32_t)i);
+                }
+            }
+            __syncthreads();
+            if (s_cnt <= SAMPLE_MAX_K) n = s_cnt;  // else (many equal logits at the bound): select among the whole row
+            __syncthreads();
+        }
+        if (n < 0) {
         // ---- radix select of the k-th largest key
         if (tid == 0) { s_prefix = 0; s_mask = 0; s_krem = k; s_cnt = 0; }
         __syncthreads();
@@ -284,13 +338,17 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
             base += total;
             __syncthreads();
         }
-        for (int i = k + tid; i < SAMPLE_MAX_K; i += blockDim.x) cand[i] = 0ull;
+        n = k;
+        }
+        int n_sort = 2;
+        while (n_sort < n) n_sort <<= 1;
+        for (int i = n + tid; i < n_sort; i += blockDim.x) cand[i] = 0ull;   // sorts below every real key
         __syncthreads();
-        // ---- bitonic sort, descending
-        for (int size = 2; size <= SAMPLE_MAX_K; size <<= 1) {
+        // ---- bitonic sort, descending: larger logit first, lower id first among equal logits
+        for (int size = 2; size <= n_sort; size <<= 1) {
             for (int stride = size >> 1; stride > 0; stride >>= 1) {
                 const int j = tid ^ stride;
-                if (j > tid) {
+                if (j > tid && j < n_sort) {
                     const unsigned long long a = cand[tid], b = cand[j];
                     const bool desc = (tid & size) == 0;
                     if ((a < b) == desc) { cand[tid] = b; cand[j] = a; }
@@ -298,26 +356,32 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
                 __syncthreads();
             }
         }
+        if (temp <= 0.0f) {
+            if (tid == 0) out[r] = (int)(0xffffffffu - (uint32_t)(cand[0] & 0xffffffffu));
+            return;
+        }
+        // penalised scores and their weights by a thread each; one thread adds them in the candidates' order
+        float sc = -INFINITY;
+        int id = 0;
+        if (tid < k) {
+            id = (int)(0xffffffffu - (uint32_t)(cand[tid] & 0xffffffffu));
+            sc = key_float((uint32_t)(cand[tid] >> 32));
+            for (int j = 0; j < nrec; ++j)
+                if (s_recent[j] == id) { sc = sc / pen; break; }
+        }
+        const float mx = block_max(sc, fscratch);
+        if (tid < k) cand[tid] = ((unsigned long long)__float_as_uint(expf((sc - mx) / temp)) << 32) | (uint32_t)id;
+        __syncthreads();
         if (tid == 0) {
-            float mx = -INFINITY;
-            for (int i = 0; i < k; ++i) {
-                const int id = (int)(0xffffffffu - (uint32_t)(cand[i] & 0xffffffffu));
-                float s = key_float((uint32_t)(cand[i] >> 32));
-                for (int j = 0; j < nrec; ++j)
-                    if (s_recent[j] == id) { s = s / pen; break; }
-                // keep the penalised score in the upper half for the second walk
-                cand[i] = ((unsigned long long)__float_as_uint(s) << 32) | (uint32_t)id;
-                mx = fmaxf(mx, s);
-            }
             float sum = 0.f;
-            for (int i = 0; i < k; ++i) sum += expf((__uint_as_float((uint32_t)(cand[i] >> 32)) - mx) / temp);
+            for (int i = 0; i < k; ++i) sum += __uint_as_float((uint32_t)(cand[i] >> 32));
             int pick = (int)(cand[0] & 0xffffffffu);
             if (sum != 0.f) {
                 const float rr = u[r] * sum;
                 float acc = 0.f;
                 pick = (int)(cand[k - 1] & 0xffffffffu);
                 for (int i = 0; i < k; ++i) {
-                    acc += expf((__uint_as_float((uint32_t)(cand[i] >> 32)) - mx) / temp);
+                    acc += __uint_as_float((uint32_t)(cand[i] >> 32));
                     if (rr <= acc) { pick = (int)(cand[i] & 0xffffffffu); break; }
                 }
             }
@@ -327,11 +391,28 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
     }
 
     // ---- whole row, in the order of the ids
+    // which ids are recent: a bit each in shared memory where the row fits, else the list is searched
+    uint32_t* recent_bits = dyn_words;
+    if (bitmap_words > 0 && nrec > 0) {
+        for (int i = tid; i < bitmap_words; i += blockDim.x) recent_bits[i] = 0u;
+        __syncthreads();
+        for (int j = tid; j < nrec; j += blockDim.x) {
+            const int id = s_recent[j];
+            if (id >= 0 && id < V) atomicOr(&recent_bits[id >> 5], 1u << (id & 31));
+        }
+        __syncthreads();
+    }
     auto score = [&](int i) -> float {
         float s = row[i];
         if (!isfinite(s)) s = -INFINITY;
-        for (int j = 0; j < nrec; ++j)
-            if (s_recent[j] == i) { s = s / pen; break; }
+        if (nrec > 0) {
+            if (bitmap_words > 0) {
+                if ((recent_bits[i >> 5] >> (i & 31)) & 1u) s = s / pen;
+            } else {
+                for (int j = 0; j < nrec; ++j)
+                    if (s_recent[j] == i) { s = s / pen; break; }
+            }
+        }
         return s;
     };
     float mx = -INFINITY;
@@ -371,11 +452,28 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
 
 // logits [R, V] float32; temperature, u, penalty [R] float32; top_k [R] int32
 // (0 = whole row, at most 1024); recent [R, W] int32 padded with -1 (W <= 256) or null.
+// max_top_k: the largest top_k of the rows. group_max: scratch of R * ceil(V / 128) 32-bit words, or null; with it
+// (and a row of 2,048 to a million logits) the rows that take the top k, or the arg-max, look only at the logits that
+// reach the k-th largest of the maxima of groups of 128.
 CELLM_API int cellm_sample(int* out, const float* logits, int R, int V, const float* temperature,
                            const int* top_k, const float* u, const float* penalty, const int* recent,
-                           int W, int max_top_k, cudaStream_t stream) {
+                           int W, int max_top_k, uint32_t* group_max, cudaStream_t stream) {
     if (R <= 0) return CELLM_OK;
     if (max_top_k > SAMPLE_MAX_K || W > 256 || W < 0) return CELLM_ERR_SIZE;
-    CELLM_RUN(sample_kernel, R, SAMPLE_THREADS, 0, stream, out, logits, V, temperature, top_k, u, penalty, recent, W);
+    int G = (V + SAMPLE_GROUP - 1) / SAMPLE_GROUP, g_sort = 0;
+    if (group_max != nullptr && V >= 2048 && G <= SAMPLE_MAX_GROUPS) {
+        g_sort = 2;
+        while (g_sort < G) g_sort <<= 1;
+        CELLM_RUN(group_max_kernel, dim3((unsigned)((G + 7) / 8), (unsigned)R), 256, 0, stream, group_max, logits, V, G);
+    } else {
+        group_max = nullptr;
+        G = 0;
+    }
+    // a bit per id for the recent tokens of rows that draw from the whole row, where that fits beside the static arrays
+    const int words = (V + 31) / 32;
+    const int bitmap_words = (recent != nullptr && W > 0 && words <= 8192) ? words : 0;
+    const int dyn = bitmap_words > g_sort ? bitmap_words : g_sort;
+    CELLM_RUN(sample_kernel, R, SAMPLE_THREADS, (size_t)dyn * sizeof(uint32_t), stream, out, logits, V, temperature, top_k, u,
+              penalty, recent, W, bitmap_words, (const uint32_t*)group_max, G, g_sort);
     return CELLM_OK;
 }

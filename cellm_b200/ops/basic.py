@@ -150,17 +150,25 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, u: torch.Tensor,
            penalty: Optional[torch.Tensor] = None, recent: Optional[torch.Tensor] = None,
-           max_top_k: int = 0) -> torch.Tensor:
+           max_top_k: int = 0, prefilter: bool = True) -> torch.Tensor:
     """One token per row of float32 logits [R, V]: arg-max where temperature <= 0,
     else a draw from softmax(logits / temperature) over the top_k logits (0: all),
     decided by the uniform number u[r]. recent [R, W] int32 (-1 padded) and
-    penalty [R] apply the repetition penalty. Returns int32 [R]."""
+    penalty [R] apply the repetition penalty. max_top_k is the host's bound of top_k.
+    `prefilter`: a first kernel finds the maxima of groups of 128 logits, which lets the
+    rows that take a top k skip most of the row (off: one block searches the whole row;
+    the choice is the same). Returns int32 [R]."""
     require_cuda(logits, temperature, top_k, u, penalty, recent)
     if logits.dtype != torch.float32 or logits.dim() != 2:
         raise ValueError("sample: logits must be float32 [R, V]")
     R, V = logits.shape
     W = recent.shape[1] if recent is not None else 0
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    group_max = None
+    if prefilter and 2048 <= V <= 128 * 8192:
+        group_max = torch.empty((R, (V + 127) // 128), dtype=torch.int32, device=logits.device)
+        count_launch()
     check(fn(_LIB, "cellm_sample")(ptr(out), ptr(logits), R, V, ptr(temperature), ptr(top_k), ptr(u),
-                                   ptr(penalty), ptr(recent), W, int(max_top_k), stream_of(logits)), "sample")
+                                   ptr(penalty), ptr(recent), W, int(max_top_k), ptr(group_max),
+                                   stream_of(logits)), "sample")
     return out

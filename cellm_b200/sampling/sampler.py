@@ -32,9 +32,12 @@ def sample_rows(logits: torch.Tensor, samplers: Sequence[RequestSampler],
     if all(s.params.temperature <= 0.0 for s in samplers):
         return (argmax if argmax is not None and argmax.shape[0] == R else ops.argmax(logits)).tolist()
     W = max((s.params.repeat_window for s in samplers if s.params.repeat_penalty > 1.0), default=0)
-    f = np.zeros((3, R), dtype=np.float32)
-    k = np.zeros((R,), dtype=np.int32)
-    recent = np.full((R, max(W, 1)), -1, dtype=np.int32)
+    # one upload: temperature, uniform number, penalty (float32 bits), top_k, then the recent tokens
+    buf = np.empty((4 * R + R * W,), dtype=np.int32)
+    f = buf[:3 * R].view(np.float32).reshape(3, R)
+    k = buf[3 * R:4 * R]
+    recent = buf[4 * R:].reshape(R, W)
+    recent.fill(-1)
     for r, s in enumerate(samplers):
         p = s.params
         f[0, r] = p.temperature
@@ -44,8 +47,8 @@ def sample_rows(logits: torch.Tensor, samplers: Sequence[RequestSampler],
         if p.repeat_penalty > 1.0 and p.repeat_window > 0 and s.history:
             tail = s.history[-p.repeat_window:]
             recent[r, :len(tail)] = tail
-    dev = logits.device
-    fd = torch.from_numpy(f).to(dev)
-    out = ops.sample(logits, fd[0], torch.from_numpy(k).to(dev), fd[1], fd[2],
-                     torch.from_numpy(recent).to(dev) if W > 0 else None, int(k.max()))
+    d = torch.from_numpy(buf).to(logits.device)
+    fd = d[:3 * R].view(torch.float32).view(3, R)
+    out = ops.sample(logits, fd[0], d[3 * R:4 * R], fd[1], fd[2], d[4 * R:].view(R, W) if W > 0 else None,
+                     int(k.max()))
     return out.tolist()

@@ -522,3 +522,51 @@ def test_argmax_and_sampling_follow_the_plain_sampler():
             else:
                 checked += 1
     assert checked > 200
+
+
+@pytest.mark.parametrize("V", [3001, 70001])
+def test_sampling_with_and_without_the_group_maxima(V):
+    """The first kernel's maxima of groups of 128 logits let the second look at few logits; the choice is the
+    same as one block's search of the whole row. Equal logits at the k-th place and at the top, in one group
+    and across groups; a row of equal leaders in every group (more candidates than fit: the whole row is
+    searched after all); a row that takes the arg-max."""
+    from cellm_b200 import ops
+    torch.manual_seed(V)
+    R = 6
+    logits = torch.randn(R, V, device=DEV) * 3
+    logits[0, 7] = logits[0, V - 2] = 50.0                      # equal maxima: the lower id wins
+    logits[1, 5] = float("nan")
+    logits[2, ::97] = 9.0                                       # many equal leaders in every run: the lowest ids
+    logits[3, 127] = logits[3, 128] = logits[3, 2048] = 40.0    # equal logits on both sides of a group's edge
+    logits[4, 1000:1200] = 30.0                                 # most of the top 300 in two groups
+    rng = plain.XorShift64(7)
+    checked = 0
+    for trial in range(30):
+        temps = [0.0, 0.7, 1.3, 0.9, 0.8, 1.0]
+        ks = [0, 40, 5, 3, 300, 1]
+        pens = [1.0, 1.05, 1.0, 1.3, 1.0, 2.0]
+        us = [rng.next_f32() for _ in range(R)]
+        recent = [[int(x) for x in torch.randint(0, V, (9,))] for _ in range(R)]
+        for r in range(R):
+            recent[r][:3] = logits[r].nan_to_num(-1e30).topk(3).indices.tolist()
+        out = ops.sample(logits, torch.tensor(temps, device=DEV), torch.tensor(ks, dtype=torch.int32, device=DEV),
+                         torch.tensor(us, device=DEV), torch.tensor(pens, device=DEV),
+                         torch.tensor(recent, dtype=torch.int32, device=DEV), max_top_k=300).tolist()
+        one_block = ops.sample(logits, torch.tensor(temps, device=DEV), torch.tensor(ks, dtype=torch.int32, device=DEV),
+                               torch.tensor(us, device=DEV), torch.tensor(pens, device=DEV),
+                               torch.tensor(recent, dtype=torch.int32, device=DEV), max_top_k=300, prefilter=False).tolist()
+        assert out == one_block, (trial, out, one_block)         # the same candidates in the same order
+        for r in range(R):
+            class U:
+                def next_f32(self_inner):
+                    return us[r]
+            cands = plain.top_k_candidates(logits[r].cpu(), ks[r])
+            ref = plain.select_next(cands, temps[r], pens[r], 64, recent[r], U())
+            if out[r] != ref:
+                sc = np.array([s / pens[r] if (pens[r] > 1 and i in recent[r]) else s for i, s in cands], dtype=np.float64)
+                w = np.exp((sc - sc.max()) / temps[r])
+                cdf = np.cumsum(w) / w.sum()
+                assert np.abs(cdf - us[r]).min() < 1e-5, (trial, r, out[r], ref)
+            else:
+                checked += 1
+    assert checked > 150
