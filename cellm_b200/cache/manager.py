@@ -71,10 +71,9 @@ class CacheManager:
         for g, need in enumerate(self.state_keys):
             self.states.append(torch.zeros((members[("state", g)], self.num_slots) + tuple(need.shape),
                                            dtype=need.dtype, device=self.device))
-        # The native manager wants at least one group; a model without paged items gets a dummy of one page.
-        pages = self.group_pages or [1]
-        windows = [k.window for k in self.paged_keys] or [0]
-        self._h = lib().cellm_cache_create(self.page_size, len(pages), int_array(pages), int_array(windows),
+        # A model without paged items (no attention at all) has no page group: its requests hold a slot only.
+        windows = [k.window for k in self.paged_keys]
+        self._h = lib().cellm_cache_create(self.page_size, n_paged, int_array(self.group_pages), int_array(windows),
                                            self.num_slots)
         if not self._h:
             raise CacheError(last_error())
@@ -140,7 +139,7 @@ class CacheManager:
         return lib().cellm_cache_live(self._h)
 
     def max_blocks(self, group: int) -> int:
-        return self.group_pages[group] if self.group_pages else 1
+        return self.group_pages[group]
 
     def pages_for(self, group: int, tokens: int, portion: int) -> int:
         return checked(lib().cellm_cache_pages_for(self._h, group, tokens, portion))

@@ -14,13 +14,20 @@ from .models import load_model
 
 
 class Replayer:
-    def __init__(self, model_dir: str, dtype: str, max_tokens: int, tokens_per_block: int = 16,
+    def __init__(self, model_dir, dtype: str, max_tokens: int, tokens_per_block: int = 16,
                  max_requests: int = 4, device: str = "cuda:0"):
-        """`max_tokens`: the most tokens live requests hold at any time, each
+        """`model_dir`: a model folder, or the (config, plan, model) triple that
+        `load_model` returned (several replays may share one loaded model).
+        `max_tokens`: the most tokens live requests hold at any time, each
         request's count rounded up to a multiple of 64; the pools are made for
         exactly this many, so pages are used again."""
         import torch
-        self.cfg, self.plan, self.model = load_model(model_dir, dtype, device)
+        if isinstance(model_dir, (str, bytes)) or hasattr(model_dir, "__fspath__"):
+            model_dir = load_model(model_dir, dtype, device)
+        self.cfg, self.plan, self.model = model_dir
+        from .config import parse_dtype
+        if self.model.dtype != parse_dtype(dtype):
+            raise ValueError(f"the loaded model computes in {self.model.dtype}, the replay was asked for {dtype}")
         pages = max(1, (int(max_tokens) + tokens_per_block - 1) // tokens_per_block)
         needs = self.model.cache_needs()
         self.cache = CacheManager(needs, [e.cache_of for e in self.plan.order], tokens_per_block, pages,

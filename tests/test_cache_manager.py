@@ -164,3 +164,19 @@ def test_bindings_follow_the_order_and_borrowed_caches():
     assert b[3].k.data_ptr() == b[1].k.data_ptr() and b[3].writes is False and b[1].writes is True
     assert b[4].block_table is t1 and b[4].num_pages == 3
     assert cm.bytes_per_token() == 2 * 4 * (2 * 2 * 8 + 1 * 1 * 16)
+
+
+def test_requests_of_a_model_without_paged_items_hold_a_slot_only():
+    """Layers with fixed-size state alone (no attention anywhere): no page group exists,
+    a request of any length fits, and what limits the live requests is the slots."""
+    cm = CacheManager([FixedState((2, 8)), FixedState((2, 8))], [None, None], 4, 8, 2, torch.float32, "cpu")
+    assert cm.paged_keys == [] and cm.group_pages == [] and cm.k_pools == []
+    a, b = cm.add(1), cm.add(2)
+    assert {a, b} == {0, 1}
+    with pytest.raises(OutOfPages):
+        cm.add(3)
+    assert cm.reserve(1, 10_000)
+    cm.commit(1, 10_000)
+    assert cm.tokens(1) == 10_000
+    cm.release(1)
+    assert cm.free_slots == 1 and cm.add(3) == a

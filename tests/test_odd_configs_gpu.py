@@ -1,6 +1,7 @@
 """Configurations off the beaten path: head sizes in steps of 16 (16, 48, 80,
 128), widths and vocabularies that are no multiple of 8 or 64, one and many
-key/value heads, two to five convolution taps, several page sizes. Each is
+key/value heads, one to five convolution taps, a model without attention,
+several page sizes. Each is
 replayed whole, in portions and mixed, in both modes, against the plain
 implementation."""
 import numpy as np
@@ -39,6 +40,12 @@ ODD = {
     # sixteen query heads on one key/value head (the decode tile is full), heads of 64, width 128
     "g16": (cfg(vocab_size=512, hidden_size=128, num_hidden_layers=2, layer_types=["full_attention", "conv"],
                 num_attention_heads=16, num_key_value_heads=1, head_dim=64, intermediate_size=192), 16),
+    # no attention at all: requests hold a state slot and no page; a single tap (no state to carry) is the other edge
+    "convonly": (cfg(vocab_size=300, hidden_size=72, num_hidden_layers=2, layer_types=["conv", "conv"],
+                     num_attention_heads=3, num_key_value_heads=3, head_dim=16, intermediate_size=128, conv_L_cache=4,
+                     conv_bias=True), 16),
+    "onetap": (cfg(vocab_size=400, hidden_size=64, num_hidden_layers=3, layer_types=["conv", "full_attention", "conv"],
+                   num_attention_heads=2, num_key_value_heads=1, head_dim=32, intermediate_size=128, conv_L_cache=1), 8),
 }
 
 

@@ -147,3 +147,19 @@ def test_append_rules():
     with pytest.raises(SchedulerError, match="not decoding"):
         s.append_token(0, 1)
     assert s.tokens(0) == list(range(12)) and s.tokens(0, 10) == [10, 11]
+
+
+def test_a_model_without_paged_items_is_scheduled_by_slots_and_budget_alone():
+    cm = CacheManager([FixedState((2, 4))], [None], 4, 1, 2, torch.float32, "cpu")
+    s = Scheduler(cm, 16, 8, 256)
+    for rid in range(3):
+        s.add_request(rid, list(range(10)), 3)
+    plan, _ = run_step(s)
+    assert [(e.request_id, e.start, e.count) for e in plan.entries] == [(0, 0, 8), (1, 0, 8)]     # two slots
+    done = []
+    for _ in range(20):
+        plan, fin = run_step(s)
+        done += fin
+        if len(done) == 3:
+            break
+    assert sorted(done) == [0, 1, 2] and cm.free_slots == 2 and s.stats()["preemptions"] == 0
