@@ -24,16 +24,10 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: LFM2-1.2B shape.
-LFM2_1P2B = {
-    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
-    "vocab_size": 65536, "hidden_size": 2048, "num_hidden_layers": 16,
-    "full_attn_idxs": [2, 5, 8, 10, 12, 14],
-    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
-    "intermediate_size": 12288, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
-    "block_ffn_dim_multiplier": 1.0, "rope_theta": 1000000.0, "conv_L_cache": 3, "conv_bias": False,
-    "norm_eps": 1e-5, "tie_embedding": True, "max_position_embeddings": 128000,
-}
+from cellm_b200.config.presets import LFM2_SHAPES  # noqa: E402
+
+# The benchmark's model: layers of LFM2-1.2B's sizes.
+LFM2_1P2B = LFM2_SHAPES["lfm2-1.2b"]
 CONTEXT_LEN = 8192
 PROMPT_LEN = 2048
 PAGE = 16
