@@ -9,7 +9,8 @@ lm_head, and the feed-forward size adjustment.
 
 It shares no code with the package: it reads tensors with the `safetensors`
 library, works on whole sequences with torch on the CPU (float64 by default),
-and keeps no cache of any kind.
+and keeps no cache of any kind. A second restatement, token by token in C++
+(tests/plain_cpp/plain_lfm2.cc), is compared with this one in test_plain.py.
 """
 from __future__ import annotations
 

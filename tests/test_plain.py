@@ -102,3 +102,65 @@ def test_sampler_follows_select_next():
     for _ in range(3000):
         pen[plain.select_next(c, 1.0, 2.0, 4, [9, 9, 1], rng)] += 1             # token 1 was seen: its score halves
     assert pen[1] < counts[1] * 0.7
+
+
+def _cpp_forward(lib, cfg, w, ids):
+    """Logits of the C++ restatement (tests/plain_cpp/plain_lfm2.cc) for tensors `w` (float64)."""
+    import ctypes
+
+    class Config(ctypes.Structure):
+        _fields_ = [(n, ctypes.c_int) for n in ("vocab", "hidden", "layers", "heads", "kv_heads", "head_dim", "ff", "taps")] + \
+                   [("eps", ctypes.c_double), ("theta", ctypes.c_double)]
+    types = plain.layer_types(cfg)
+    L = cfg["num_hidden_layers"]
+    c = Config(cfg["vocab_size"], cfg["hidden_size"], L, cfg["num_attention_heads"], cfg["num_key_value_heads"],
+               plain.head_dim(cfg), plain.feed_forward_size(cfg), int(cfg.get("conv_L_cache", 3)),
+               plain.norm_eps(cfg), float(cfg.get("rope_theta", 1e6)))
+    keep = []
+
+    def p(name):
+        t = w.get(name)
+        if t is None:
+            return None
+        t = t.to(torch.float64).contiguous()
+        keep.append(t)
+        return t.data_ptr()
+    tied = cfg.get("tie_embedding", cfg.get("tie_word_embeddings", True))
+    ptrs = [p("model.embed_tokens.weight"), p("model.embedding_norm.weight"), None if tied else p("lm_head.weight")]
+    for l in range(L):
+        q = f"model.layers.{l}."
+        ptrs += [p(q + n) for n in ("operator_norm.weight", "ffn_norm.weight", "feed_forward.w1.weight", "feed_forward.w2.weight",
+                                    "feed_forward.w3.weight", "conv.in_proj.weight", "conv.conv.weight", "conv.conv.bias",
+                                    "conv.out_proj.weight", "self_attn.q_proj.weight", "self_attn.k_proj.weight",
+                                    "self_attn.v_proj.weight", "self_attn.out_proj.weight", "self_attn.q_layernorm.weight",
+                                    "self_attn.k_layernorm.weight")]
+    arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+    kinds = (ctypes.c_int * L)(*[0 if t == "conv" else 1 for t in types])
+    ids_c = (ctypes.c_int * len(ids))(*ids)
+    out = np.empty((len(ids), cfg["vocab_size"]), dtype=np.float64)
+    lib.plain_lfm2_forward.restype = ctypes.c_int
+    rc = lib.plain_lfm2_forward(ctypes.byref(c), arr, kinds, ids_c, len(ids), out.ctypes.data_as(ctypes.c_void_p))
+    assert rc == 0
+    return out
+
+
+def test_cpp_restatement_agrees_with_the_python_one(tmp_path):
+    """Two restatements of the reference's formulas, written apart (whole sequences in
+    torch; token by token with a growing cache in C++), give the same logits on both
+    tiny configurations: a slip in reading the reference would have to be made twice."""
+    import ctypes
+    import os
+    import shutil
+    import subprocess
+    cxx = shutil.which("g++") or shutil.which("c++")
+    assert cxx, "a host C++ compiler is needed"
+    so = str(tmp_path / "libplain_cpp.so")
+    src = os.path.join(os.path.dirname(os.path.abspath(__file__)), "plain_cpp", "plain_lfm2.cc")
+    subprocess.run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-o", so, src], check=True)
+    lib = ctypes.CDLL(so)
+    for name in ("tiny_a", "tiny_b"):
+        cfg, w = plain.load_folder(make_model(tmp_path, name))
+        ids = np.random.default_rng(3).integers(0, cfg["vocab_size"], 41).tolist()
+        a = plain.forward(cfg, w, ids).numpy()
+        b = _cpp_forward(lib, cfg, w, ids)
+        assert np.abs(a - b).max() < 1e-10 * (1 + np.abs(a).max()), name
