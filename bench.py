@@ -253,7 +253,7 @@ def main() -> int:
     pk, pk_src = peaks()
     t_setup = time.time()
     with tempfile.TemporaryDirectory(prefix="cellm_bench_") as d:
-        # BASELINE.json: N(0, 0.02) weights, norm weights 1
+        # the benchmark's weights: N(0, 0.02), norm weights 1
         write_random_model(d, LFM2_1P2B, seed=0, dtype="bfloat16", init=InitSpec(norm_jitter=0.0))
         loaded = load_model(d, "bfloat16", "cuda:0")
     cfg, plan, model = loaded

@@ -183,6 +183,7 @@ struct alignas(1024) GemmSmem {
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
+    int conv_slots[64];         // EPI = 2: the state slots of the tile's tokens
 };
 
 template <typename TO> __device__ __forceinline__ void store_row(TO* dst, const uint32_t* r, int valid, bool aligned);
@@ -245,12 +246,31 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 // memory; after a cluster barrier every CTA sums, in the order of the ranks, the
 // pieces of its share of the tile's tokens, reading the peers' memory directly, and
 // writes those outputs. No workspace, no counter, no fence to global memory.
+//
+// EPI = 2 (swapped tiles in a cluster; every token of the step belongs to a request of its own):
+// the gated short convolution in the epilogue of its in_proj. W is in_proj cut into tiles of 128
+// rows that hold, for 42 channels each, the 42 rows of B, of C and of x (two rows of padding), so
+// that the thread of a channel finds all three sums in its tile. It rounds them to bfloat16 as
+// the plain product would have stored them, forms B*x, takes the request's last taps-1 values
+// of B*x from its state slot, writes y = C * (taps . history) and moves the state on by one.
+struct ConvEpi {
+    const __nv_bfloat16* taps;   // [H, ntaps]
+    const __nv_bfloat16* bias;   // [H] or null
+    float* state;                // [slots][ntaps - 1][H]
+    const int* slot_ids;         // [M]: the state slot of each token's request
+    long long slot_stride;       // floats between slots
+    int H, ntaps, n_slots;
+};
+constexpr int CONV_CH = 42;          // channels per tile of 128 rows
+constexpr int CONV_MAX_TAPS = 4;
+
 template <int BN, int STAGES, bool SWAP, int EPI, bool CLUSTER, typename TO>
 __global__ void __launch_bounds__(192, SWAP ? 2 : 1)      // swapped tiles: two CTAs an SM, so the next product's can move in early
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                     TO* __restrict__ C, float* __restrict__ ws, int* __restrict__ counters, int M, int N, int K,
-                    long long ldc, int kblocks_per_split, int w_is_static, int* __restrict__ err) {
+                    long long ldc, int kblocks_per_split, int w_is_static, int* __restrict__ err, const ConvEpi conv) {
     static_assert(!CLUSTER || SWAP, "the cluster reduction serves swapped tiles");
+    static_assert(EPI != 2 || CLUSTER, "the convolution epilogue is written for the cluster's reduction");
     extern __shared__ uint8_t smem_raw[];
     using Smem = GemmSmem<BN, STAGES, CLUSTER ? BN * BM : 0>;
     auto& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -281,6 +301,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     pdl_trigger();
     const uint32_t tmem = sm.tmem_base;
     volatile int* abort_flag = &sm.abort_flag;
+    // EPI = 2: what an epilogue thread fetches ahead of the accumulator (see there)
+    float cv_wt[CONV_MAX_TAPS - 1] = {}, cv_hist[CONV_MAX_TAPS - 1] = {}, cv_wlast = 0.f, cv_bias = 0.f;
+    bool cv_active = false;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -331,6 +354,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             if (ok) umma_commit(&sm.acc_full);
         }
     } else {
+        if constexpr (EPI == 2) {
+            // While the products run: the slots of the tile's tokens, this thread's taps and the history of its
+            // first token. None of it is the work of a kernel of this step (the state was last written by this
+            // kernel one step ago), so it does not wait for the kernel before this one.
+            const int pl = (warp & 3) * 32 + lane;
+            if (pl < BN) sm.conv_slots[pl] = q0 + pl < Q ? conv.slot_ids[q0 + pl] : -1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int sub = pl / CONV_CH, ch = (p0 / BM) * CONV_CH + pl % CONV_CH;
+            cv_active = sub < 3 && ch < conv.H;
+            if (cv_active) {
+                const int rows = conv.ntaps - 1;
+#pragma unroll
+                for (int k = 0; k < CONV_MAX_TAPS - 1; ++k)
+                    cv_wt[k] = k < rows ? __bfloat162float(conv.taps[(size_t)ch * conv.ntaps + k]) : 0.f;
+                cv_wlast = __bfloat162float(conv.taps[(size_t)ch * conv.ntaps + rows]);
+                cv_bias = conv.bias ? __bfloat162float(conv.bias[ch]) : 0.f;
+                const int ql = (int)cluster_rank() + sub * splits;       // this thread's first token of the tile
+                const int slot = ql < BN ? sm.conv_slots[ql] : -1;
+#pragma unroll
+                for (int k = 0; k < CONV_MAX_TAPS - 1; ++k)
+                    cv_hist[k] = (k < rows && slot >= 0 && slot < conv.n_slots)
+                                     ? conv.state[(long long)slot * conv.slot_stride + (size_t)k * conv.H + ch] : 0.f;
+            }
+        }
         const bool ok = mbar_wait(&sm.acc_full, 0, abort_flag);
         if (!ok && lane == 0) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); }
         tc_fence_after();
@@ -522,8 +569,60 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             const int pl = (warp & 3) * 32 + lane, p = p0 + pl;
             const uint32_t rank = cluster_rank();
             const int q_end = min(Q, q0 + BN);
+            if constexpr (EPI == 2) {
+                // Tokens rank, rank + splits, ... of the tile are this CTA's; three of them are worked on side by
+                // side (threads 0..41, 42..83, 84..125: one channel each). The history of the token after this
+                // one is asked for before this one's sums are, so that the two round trips overlap.
+                const int sub = pl / CONV_CH, cl = pl % CONV_CH, ch = (p0 / BM) * CONV_CH + cl;
+                const int rows = conv.ntaps - 1;
+                if (cv_active) {
+                    for (int ql = (int)rank + sub * splits; q0 + ql < q_end; ql += 3 * splits) {
+                        const int q = q0 + ql, slot = sm.conv_slots[ql];
+                        float hist[CONV_MAX_TAPS - 1];
+#pragma unroll
+                        for (int k = 0; k < CONV_MAX_TAPS - 1; ++k) hist[k] = cv_hist[k];
+                        const int qn = ql + 3 * splits;
+                        if (q0 + qn < q_end) {
+                            const int sn = sm.conv_slots[qn];
+#pragma unroll
+                            for (int k = 0; k < CONV_MAX_TAPS - 1; ++k)
+                                cv_hist[k] = (k < rows && sn >= 0 && sn < conv.n_slots)
+                                                 ? conv.state[(long long)sn * conv.slot_stride + (size_t)k * conv.H + ch] : 0.f;
+                        }
+                        if (slot < 0 || slot >= conv.n_slots) { atomicOr(err, CELLM_DEV_BAD_SLOT); continue; }
+                        const float* mine = &sm.red[ql * BM + cl];
+                        float vb[8], vc[8], vx[8];
+#pragma unroll
+                        for (int r = 0; r < 8; ++r) {
+                            vb[r] = r < splits ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
+                            vc[r] = r < splits ? ld_peer_shared(mine + CONV_CH, (uint32_t)r) : 0.f;
+                            vx[r] = r < splits ? ld_peer_shared(mine + 2 * CONV_CH, (uint32_t)r) : 0.f;
+                        }
+                        float b = 0.f, c = 0.f, x = 0.f;
+#pragma unroll
+                        for (int r = 0; r < 8; ++r) { b += vb[r]; c += vc[r]; x += vx[r]; }
+                        // the plain product stores B, C and x as bfloat16 before the convolution reads them
+                        b = __bfloat162float(__float2bfloat16_rn(b));
+                        c = __bfloat162float(__float2bfloat16_rn(c));
+                        x = __bfloat162float(__float2bfloat16_rn(x));
+                        const float bx = b * x;
+                        float acc = 0.f;
+#pragma unroll
+                        for (int k = 0; k < CONV_MAX_TAPS - 1; ++k)
+                            if (k < rows) acc += hist[k] * cv_wt[k];
+                        acc += bx * cv_wlast;
+                        if (conv.bias) acc += cv_bias;
+                        C[(size_t)q * ldc + ch] = from_float<TO>(c * acc);
+                        float* st = conv.state + (long long)slot * conv.slot_stride;
+#pragma unroll
+                        for (int k = 0; k < CONV_MAX_TAPS - 2; ++k)
+                            if (k + 1 < rows) st[(size_t)k * conv.H + ch] = hist[k + 1];
+                        if (rows > 0) st[(size_t)(rows - 1) * conv.H + ch] = bx;
+                    }
+                }
+            }
             // tokens rank, rank + splits, ... of the tile are summed and written by this CTA
-            for (int q = q0 + (int)rank; q < q_end; q += splits) {
+            for (int q = q0 + (int)rank; EPI != 2 && q < q_end; q += splits) {
                 const float* mine = &sm.red[(q - q0) * BM + pl];
                 // all the peers' pieces of a token are asked for at once (a cluster has at most 8 CTAs), then
                 // added in the order of the ranks
@@ -798,7 +897,8 @@ bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
 
 template <int BN, int STAGES, bool SWAP, int EPI, bool CLUSTER, typename TO>
 int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* ws, int* counters, int M, int N, int K,
-           long long ldc, int split_k, int kblocks_per_split, int w_is_static, int* err, cudaStream_t stream) {
+           long long ldc, int split_k, int kblocks_per_split, int w_is_static, int* err, cudaStream_t stream,
+           const ConvEpi& conv) {
     const size_t smem = sizeof(GemmSmem<BN, STAGES, CLUSTER ? BN * BM : 0>) + 1024;
     static bool configured = false;
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, EPI, CLUSTER, TO>;
@@ -827,7 +927,7 @@ int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* w
         cfg.numAttrs = 2;
     }
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, m_rows, m_cols, C, ws, counters, M, N, K, ldc, kblocks_per_split,
-                                       w_is_static, err);
+                                       w_is_static, err, conv);
     return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
@@ -881,14 +981,15 @@ CELLM_API int cellm_gemm_tcgen05_plan(int M, int N, int K, int bn, int split_k, 
 // further K blocks of the CTA's weights into L2 while it waits).
 // workspace: as many floats as cellm_gemm_tcgen05_plan says; counters: GEMM_MAX_COUNTERS
 // zeroed ints that products on one stream may share (each product leaves them zero).
-CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
-                                 long long ldw, long long ldc, int out_dtype, int bn, int split_k, int epilogue,
-                                 int w_is_static, float* workspace, int* counters, int* err, cudaStream_t stream) {
+static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
+                     long long ldw, long long ldc, int out_dtype, int bn, int split_k, int epilogue,
+                     int w_is_static, float* workspace, int* counters, int* err, cudaStream_t stream,
+                     const ConvEpi& conv) {
     if (M <= 0 || N <= 0) return CELLM_OK;
     if (K <= 0 || (K & 7)) return CELLM_ERR_SIZE;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((lda * 2) & 15) || ((ldw * 2) & 15)) return CELLM_ERR_ALIGN;
     if (out_dtype != CELLM_F32 && out_dtype != CELLM_BF16) return CELLM_ERR_DTYPE;
-    if (epilogue != 0 && epilogue != 1) return CELLM_ERR_ARG;
+    if (epilogue < 0 || epilogue > 2) return CELLM_ERR_ARG;
     const bool swap = bn < 0;
     const int narrow = swap ? -bn : bn;
     if (swap ? (narrow != 16 && narrow != 32 && narrow != 64) : (narrow != 64 && narrow != 128 && narrow != 256))
@@ -900,8 +1001,9 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
     static const bool use_cluster = [] { const char* e = std::getenv("CELLM_B200_CLUSTER_REDUCE"); return !(e && e[0] == '0'); }();
     // swapped tiles whose K split fits a cluster (2..8 CTAs) sum their pieces through shared memory
     // (an unsplit SwiGLU tile takes the same road as a cluster of one: gate and up meet in shared memory)
-    const bool in_cluster = swap && use_cluster && ((split >= 2 && split <= 8) || (split == 1 && epilogue == 1));
+    const bool in_cluster = swap && use_cluster && ((split >= 2 && split <= 8) || (split == 1 && epilogue >= 1));
     if (in_cluster) ws_floats = 0;
+    if (epilogue == 2 && !in_cluster) return CELLM_ERR_ARG;      // the convolution epilogue exists for clustered swapped tiles only
     const int kblocks = (K + BK - 1) / BK;
     const int per = (kblocks + split - 1) / split;
     if (ws_floats > 0 && workspace == nullptr) return CELLM_ERR_ARG;
@@ -934,14 +1036,14 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
     }
 #define GO3(BN_, ST_, SW_, EP_, CL_)                                                                                  \
     do {                                                                                                              \
-        if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, EP_, CL_, float>(m_rows, m_cols, (float*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
-        else rc = launch<BN_, ST_, SW_, EP_, CL_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream); \
+        if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, EP_, CL_, float>(m_rows, m_cols, (float*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream, conv); \
+        else rc = launch<BN_, ST_, SW_, EP_, CL_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream, conv); \
     } while (0)
 #define GO2(BN_, ST_, SW_, EP_) GO3(BN_, ST_, SW_, EP_, false)
     // swapped: ST_ stages without, CST_ stages with the cluster's reduction buffer (two CTAs must still fit an SM)
 #define GOS(BN_, ST_, CST_)                                                                                           \
     do {                                                                                                              \
-        if (in_cluster) { if (epilogue == 0) GO3(BN_, CST_, true, 0, true); else GO3(BN_, CST_, true, 1, true); }      \
+        if (in_cluster) { if (epilogue == 0) GO3(BN_, CST_, true, 0, true); else if (epilogue == 1) GO3(BN_, CST_, true, 1, true); else GO3(BN_, CST_, true, 2, true); } \
         else { if (epilogue == 0) GO3(BN_, ST_, true, 0, false); else GO3(BN_, ST_, true, 1, false); }                 \
     } while (0)
 #define GO(BN_, ST_, SW_)                           \
@@ -972,4 +1074,42 @@ CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, i
         else CELLM_RUN((splitk_sum_kernel<1, __nv_bfloat16>), blocks, 256, 0, stream, workspace, (__nv_bfloat16*)C, M, N, ldc, split);
     }
     return rc;
+}
+
+// The product described above gemm_impl.
+CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
+                                 long long ldw, long long ldc, int out_dtype, int bn, int split_k, int epilogue,
+                                 int w_is_static, float* workspace, int* counters, int* err, cudaStream_t stream) {
+    if (epilogue == 2) return CELLM_ERR_ARG;     // that epilogue has an entry point of its own
+    const ConvEpi none{};
+    return gemm_impl(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, bn, split_k, epilogue, w_is_static, workspace, counters,
+                     err, stream, none);
+}
+
+// in_proj and the gated short convolution of a decode step in one kernel (the kernel's EPI = 2).
+// A: [M, K] bf16, one token of M different requests. Wt: in_proj in tiles of 128 rows, [Nt, K] with
+// Nt = 128 * ceil(H / 42): rows 0..41 of tile j are the B rows of channels 42j..42j+41, rows 42..83
+// their C rows, rows 84..125 their x rows; rows of channels beyond H and the last two rows are zero.
+// Y: [M, H] bf16. taps: [H, ntaps] bf16 (1 to 4 taps), bias: [H] bf16 or null; state: [n_slots][ntaps-1][H]
+// floats, slot_stride floats apart, read and moved on by one token; slot_ids: [M]. bn: -16, -32 or -64;
+// the K split must leave the tile's CTAs in one cluster (at most 8), else the call is refused (-4).
+CELLM_API int cellm_gemm_conv_tcgen05(void* Y, const void* A, const void* Wt, int M, int Nt, int K, long long lda,
+                                      long long ldw, int H, int bn, int split_k, const void* taps, const void* bias,
+                                      int ntaps, float* state, long long slot_stride, const int* slot_ids, int n_slots,
+                                      int w_is_static, int* err, cudaStream_t stream) {
+    if (M <= 0) return CELLM_OK;
+    if (bn >= 0 || H <= 0 || (Nt & 127) || (long long)(Nt / 128) * CONV_CH < H) return CELLM_ERR_SIZE;
+    if (ntaps < 1 || ntaps > CONV_MAX_TAPS) return CELLM_ERR_SIZE;
+    if (!taps || !slot_ids || (ntaps > 1 && !state) || n_slots <= 0) return CELLM_ERR_ARG;
+    ConvEpi conv{};
+    conv.taps = (const __nv_bfloat16*)taps;
+    conv.bias = (const __nv_bfloat16*)bias;
+    conv.state = state;
+    conv.slot_ids = slot_ids;
+    conv.slot_stride = slot_stride;
+    conv.H = H;
+    conv.ntaps = ntaps;
+    conv.n_slots = n_slots;
+    return gemm_impl(Y, A, Wt, M, Nt, K, lda, ldw, (long long)H, CELLM_BF16, bn, split_k, 2, w_is_static, nullptr, nullptr,
+                     err, stream, conv);
 }

@@ -158,3 +158,57 @@ def gemm_swiglu_bf16(a: torch.Tensor, w_blocked: torch.Tensor, w_is_static: bool
     if bn == 64:
         bn = 128
     return gemm_tcgen05(a, w_blocked, a.dtype, bn, split, epilogue=1, w_is_static=w_is_static)
+
+
+CONV_TILE_CHANNELS = 42     # channels whose B, C and x rows share a tile of 128 rows
+CONV_MAX_TAPS = 4
+
+
+def tile_in_proj_for_conv(in_proj: torch.Tensor) -> torch.Tensor:
+    """in_proj [3H, K] (B rows, C rows, x rows) cut into tiles of 128 rows that hold, for 42
+    channels each, the 42 B rows, the 42 C rows and the 42 x rows (rows of channels beyond H and
+    the last two rows of a tile are zero): the layout `gemm_conv_bf16` reads."""
+    H3, K = in_proj.shape
+    H, ch = H3 // 3, CONV_TILE_CHANNELS
+    tiles = (H + ch - 1) // ch
+    parts = in_proj.reshape(3, H, K)
+    padded = torch.zeros((3, tiles * ch, K), dtype=in_proj.dtype, device=in_proj.device)
+    padded[:, :H] = parts
+    out = torch.zeros((tiles, 128, K), dtype=in_proj.dtype, device=in_proj.device)
+    out[:, :3 * ch] = padded.reshape(3, tiles, ch, K).permute(1, 0, 2, 3).reshape(tiles, 3 * ch, K)
+    return out.reshape(tiles * 128, K).contiguous()
+
+
+def gemm_conv_plan(M: int, H: int, K: int, device) -> tuple[int, int] | None:
+    """(bn, split_k) for the product with the convolution in its epilogue, or None if these
+    sizes do not run it (it needs swapped tiles whose K split is one cluster)."""
+    if not _CLUSTER_REDUCE:
+        return None
+    tiles = (H + CONV_TILE_CHANNELS - 1) // CONV_TILE_CHANNELS
+    bn, split = plan_tiles(M, tiles * 128, K, _sms(device))
+    if bn >= 0 or (M + -bn - 1) // -bn != 1 or _effective_split(K, split) > 8:
+        return None
+    return bn, split
+
+
+def gemm_conv_bf16(a: torch.Tensor, w_tiled: torch.Tensor, H: int, taps: torch.Tensor, bias: torch.Tensor | None,
+                   state: torch.Tensor, slot_ids: torch.Tensor, plan: tuple[int, int],
+                   err: torch.Tensor | None = None) -> torch.Tensor:
+    """One token of each of M requests: y [M, H] = C * conv(B * x) with B | C | x = a . in_proj^T, the
+    convolution's history read from and moved on in `state` [slots, taps-1, H] (float32) at each
+    request's slot. `w_tiled` is in_proj as `tile_in_proj_for_conv` lays it out; `plan` comes from
+    `gemm_conv_plan`. The arithmetic is that of the product followed by `short_conv`."""
+    M, K = a.shape
+    n_taps = taps.shape[1]
+    if a.dtype != torch.bfloat16 or w_tiled.dtype != torch.bfloat16 or taps.dtype != torch.bfloat16 \
+            or (bias is not None and bias.dtype != torch.bfloat16) or state.dtype != torch.float32:
+        raise ValueError("gemm_conv_bf16: bfloat16 activations, weights and taps, float32 state")
+    if tuple(state.shape[1:]) != (n_taps - 1, H) or taps.shape[0] != H or slot_ids.numel() != M:
+        raise ValueError(f"gemm_conv_bf16: shapes do not fit (state {tuple(state.shape)}, taps {tuple(taps.shape)}, {M} tokens)")
+    y = torch.empty((M, H), dtype=torch.bfloat16, device=a.device)
+    err = err if err is not None else error_word(a.device)
+    check(fn("gemm_tcgen05", "cellm_gemm_conv_tcgen05")(
+        ptr(y), ptr(a), ptr(w_tiled), M, w_tiled.shape[0], K, a.stride(0), w_tiled.stride(0), H, int(plan[0]), int(plan[1]),
+        ptr(taps), ptr(bias), n_taps, ptr(state), state.stride(0), ptr(slot_ids), state.shape[0], _STATIC_FLAG,
+        ptr(err), stream_of(a)), "gemm_conv_tcgen05")
+    return y

@@ -4,6 +4,8 @@ values of B*x, times C, out_proj. Its per-request state is the last taps-1
 values of B*x, in a slot of fixed size."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
@@ -42,8 +44,24 @@ class ShortConvMixer(Mixer):
         self.conv_b = None
         if params.get("bias"):
             self.conv_b = weights["conv_bias"].to(self.conv_w.dtype).contiguous()
+        # Decode steps (one token per request) run in_proj and the convolution as one kernel, which reads
+        # in_proj in tiles that keep a channel's B, C and x rows together: a second copy of that matrix.
+        from ..ops import gemm_bf16 as tc
+        self.in_proj_tiled = None
+        w = self.in_proj.weight
+        if (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and self.conv_w.dtype == torch.bfloat16
+                and self.taps <= tc.CONV_MAX_TAPS and self.H % 8 == 0 and w.is_cuda
+                and os.environ.get("CELLM_B200_FUSED_CONV", "1") != "0"):
+            self.in_proj_tiled = tc.tile_in_proj_for_conv(w)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        if self.in_proj_tiled is not None and ctx.max_q_len == 1 and x.dtype == torch.bfloat16:
+            from ..ops import gemm_bf16 as tc
+            plan = tc.gemm_conv_plan(ctx.T, self.H, x.shape[1], x.device) if tc.tensor_core_ok(x, self.in_proj_tiled) else None
+            if plan is not None:
+                y = tc.gemm_conv_bf16(x, self.in_proj_tiled, self.H, self.conv_w, self.conv_b, cache.state, ctx.slot_ids,
+                                      plan, ctx.err)
+                return self.out_proj(y)
         bcx = self.in_proj(x)
         y = ops.short_conv(bcx, self.conv_w, self.conv_b, cache.state, ctx.slot_ids, ctx.seq_of_token,
                            ctx.cu_seqlens, ctx.err, ctx.max_q_len)

@@ -35,7 +35,7 @@ def _margin_ok(cfg, w, prompt, out, k=2e-3):
 
 
 def test_greedy_generation_tiny_a(folders):
-    """BASELINE workload of Tiny A: prompts of 1, 7, 33 and 64 tokens, 16 greedy tokens each, page 8."""
+    """The workload of the first tiny configuration: prompts of 1, 7, 33 and 64 tokens, 16 greedy tokens each, page 8."""
     from cellm_b200 import Engine, SamplingParams
     cfg, w = plain.load_folder(folders["tiny_a"])
     prompts = _prompts(cfg["vocab_size"], [1, 7, 33, 64])
@@ -53,7 +53,7 @@ def test_greedy_generation_tiny_a(folders):
 
 
 def test_temperature_generation_tiny_b(folders):
-    """BASELINE workload of Tiny B: prompts 5/50/200 in portions of 13 mixed with
+    """The workload of the second tiny configuration: prompts 5/50/200 in portions of 13 mixed with
     decode steps, 24 tokens at temperature 0.8 with a fixed seed, page 16."""
     from cellm_b200 import Engine, SamplingParams
     from cellm_b200.sampling import session_seed

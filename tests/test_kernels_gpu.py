@@ -158,6 +158,43 @@ def test_short_conv_long_portions_of_several_requests(taps, bias):
         close(torch.cat(got[r]), whole(bcx[r]), torch.bfloat16, f"request {r}")
 
 
+@pytest.mark.parametrize("H,K,taps,bias,M", [(2048, 2048, 3, False, 8), (96, 96, 4, True, 3), (100 * 8, 64, 2, True, 33),
+                                             (42, 200, 1, False, 1), (520, 1032, 3, True, 64), (2048, 2048, 3, False, 1)])
+def test_in_proj_with_the_convolution_in_its_epilogue(H, K, taps, bias, M):
+    """Decode steps: in_proj and the gated convolution as one kernel against the product
+    followed by short_conv, four steps in a row (the state is carried in slots that change
+    place from step to step), widths that do and do not fill the tiles of 42 channels."""
+    from cellm_b200 import ops
+    from cellm_b200.ops import gemm_bf16 as tc
+    g = torch.Generator(device=DEV).manual_seed(H + taps)
+    w_in = (torch.randn(3 * H, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    w = (torch.randn(H, taps, device=DEV, generator=g) * 0.5).bfloat16()
+    b = (torch.randn(H, device=DEV, generator=g) * 0.5).bfloat16() if bias else None
+    tiled = tc.tile_in_proj_for_conv(w_in)
+    slots = M + 2
+    state_a = torch.randn(slots, taps - 1, H, device=DEV, generator=g)
+    state_b = state_a.clone()
+    e = err_word()
+    plan = tc.gemm_conv_plan(M, H, K, DEV)
+    assert plan is not None
+    cu = torch.arange(M + 1, dtype=torch.int32, device=DEV)
+    seq = torch.arange(M, dtype=torch.int32, device=DEV)
+    for step in range(4):
+        x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+        sl = ((torch.arange(M, device=DEV) + step) % slots).int()
+        ref = ops.short_conv(ops.gemm(x, w_in, torch.bfloat16), w, b, state_a, sl, seq, cu, e, 1)
+        got = tc.gemm_conv_bf16(x, tiled, H, w, b, state_b, sl, plan, e)
+        assert e.item() == 0
+        # the same sums rounded at the same places (the K split may differ, hence a unit of bfloat16 rounding here and there)
+        close(got, ref.double().cpu(), torch.bfloat16, f"step {step}")
+        assert torch.allclose(state_a, state_b, rtol=2e-2, atol=1e-3)
+    # a slot outside the pool is reported, and nothing is written for it
+    bad = torch.full((M,), slots, dtype=torch.int32, device=DEV)
+    tc.gemm_conv_bf16(torch.randn(M, K, device=DEV).bfloat16(), tiled, H, w, b, state_b, bad, plan, e)
+    assert e.item() == 4
+    e.zero_()
+
+
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("hd,rot,inter", [(16, 16, False), (48, 32, False), (64, 64, True), (32, 0, False)])
 def test_qk_norm_rope_and_page_write(dtype, hd, rot, inter):
