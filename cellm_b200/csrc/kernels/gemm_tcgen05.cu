@@ -37,6 +37,13 @@
 
 namespace {
 
+#ifndef CELLM_CLUSTER_TOKENS_IN_FLIGHT
+// Tokens whose pieces a CTA asks its cluster peers for at once. Measured at 1 and 4 (LFM2-1.2B sizes, 1, 8 and
+// 64 requests): four in flight cost 3 to 5 % of the decode step (30 more registers a thread, predicated loads)
+// and gained nothing, so one it is.
+#define CELLM_CLUSTER_TOKENS_IN_FLIGHT 1
+#endif
+
 constexpr int BM = 128;
 constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
@@ -621,31 +628,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     }
                 }
             }
-            // tokens rank, rank + splits, ... of the tile are summed and written by this CTA
-            for (int q = q0 + (int)rank; EPI != 2 && q < q_end; q += splits) {
-                const float* mine = &sm.red[(q - q0) * BM + pl];
-                // all the peers' pieces of a token are asked for at once (a cluster has at most 8 CTAs), then
-                // added in the order of the ranks
+            // Tokens rank, rank + splits, ... of the tile are summed and written by this CTA.
+            // TU of this CTA's tokens at a time: all the peers' pieces of a token are asked for at once (a cluster
+            // has at most 8 CTAs), then added in the order of the ranks.
+            constexpr int TU = CELLM_CLUSTER_TOKENS_IN_FLIGHT;
+            for (int q = q0 + (int)rank; EPI != 2 && q < q_end; q += TU * splits) {
                 if constexpr (EPI == 0) {
-                    float v[8];
+                    float v[TU][8];
 #pragma unroll
-                    for (int r = 0; r < 8; ++r) v[r] = r < splits ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
-                    float acc = 0.f;
+                    for (int t = 0; t < TU; ++t) {
+                        const int qt = q + t * splits;
+                        const float* mine = &sm.red[(qt - q0) * BM + pl];
 #pragma unroll
-                    for (int r = 0; r < 8; ++r) acc += v[r];
-                    if (p < P) C[(size_t)q * ldc + p] = from_float<TO>(acc);
+                        for (int r = 0; r < 8; ++r) v[t][r] = (qt < q_end && r < splits) ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
+                    }
+#pragma unroll
+                    for (int t = 0; t < TU; ++t) {
+                        const int qt = q + t * splits;
+                        float acc = 0.f;
+#pragma unroll
+                        for (int r = 0; r < 8; ++r) acc += v[t][r];
+                        if (qt < q_end && p < P) C[(size_t)qt * ldc + p] = from_float<TO>(acc);
+                    }
                 } else {
                     if (pl < 64) {
-                        float vg[8], vu[8];
+                        float vg[TU][8], vu[TU][8];
 #pragma unroll
-                        for (int r = 0; r < 8; ++r) {
-                            vg[r] = r < splits ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
-                            vu[r] = r < splits ? ld_peer_shared(mine + 64, (uint32_t)r) : 0.f;
+                        for (int t = 0; t < TU; ++t) {
+                            const int qt = q + t * splits;
+                            const float* mine = &sm.red[(qt - q0) * BM + pl];
+#pragma unroll
+                            for (int r = 0; r < 8; ++r) {
+                                vg[t][r] = (qt < q_end && r < splits) ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
+                                vu[t][r] = (qt < q_end && r < splits) ? ld_peer_shared(mine + 64, (uint32_t)r) : 0.f;
+                            }
                         }
-                        float g = 0.f, u = 0.f;
 #pragma unroll
-                        for (int r = 0; r < 8; ++r) { g += vg[r]; u += vu[r]; }
-                        if (p + 64 < P) C[(size_t)q * ldc + (p0 / 2 + pl)] = from_float<TO>(silu_mul(g, u));
+                        for (int t = 0; t < TU; ++t) {
+                            const int qt = q + t * splits;
+                            float g = 0.f, u = 0.f;
+#pragma unroll
+                            for (int r = 0; r < 8; ++r) { g += vg[t][r]; u += vu[t][r]; }
+                            if (qt < q_end && p + 64 < P) C[(size_t)qt * ldc + (p0 / 2 + pl)] = from_float<TO>(silu_mul(g, u));
+                        }
                     }
                 }
             }
