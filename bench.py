@@ -124,12 +124,16 @@ def time_decode(eng, ids, steps, warmup, rng, sampler=None):
     torch.cuda.synchronize()
     if sampler:
         sampler.active.set()
+    import gc
+    gc.collect()
+    gc.disable()            # a collection inside the timed steps would be charged to one of them
     t0 = time.perf_counter()
     for _ in range(steps):
         out = eng.step()
         assert len(out) == B
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+    gc.enable()
     # device-timed: the step function and the arg-max on given tokens, no read back
     V = eng.plan.vocab_size
     toks = rng.integers(0, V, (warmup + steps, B))
