@@ -163,3 +163,89 @@ def test_a_model_without_paged_items_is_scheduled_by_slots_and_budget_alone():
         if len(done) == 3:
             break
     assert sorted(done) == [0, 1, 2] and cm.free_slots == 2 and s.stats()["preemptions"] == 0
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_arrivals_keep_the_invariants(seed):
+    """Requests of random length arrive at random steps into pools of random size (often too
+    small for all at once), some stop early, some are cancelled. In every step: the budget and the
+    portion limit hold, every portion starts where the request's cache ends, nobody appears twice,
+    pages and slots add up; in the end everybody has finished with the tokens it was given and
+    everything is free."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    page = int(rng.choice([2, 4, 8]))
+    n_req = int(rng.integers(3, 12))
+    growing = seed % 2 == 1          # short prompts that grow long in a tight pool: running requests get preempted
+    lens = rng.integers(1, 12 if growing else 60, n_req).tolist()
+    news = rng.integers(20 if growing else 1, 60 if growing else 30, n_req).tolist()
+    need = [-(-(l + n) // page) for l, n in zip(lens, news)]
+    pages = int(max(max(need), sum(need) * rng.uniform(0.2, 0.6 if growing else 1.1)))
+    slots = n_req if growing else int(rng.integers(1, n_req + 1))
+    budget, chunk = int(rng.integers(1, 48)), int(rng.integers(1, 32))
+    cm = CacheManager([FixedState((2, 4)), PagedKV(1, 8, 0)], [None, None], page, pages, slots, torch.float32, "cpu")
+    s = Scheduler(cm, budget, chunk, 4096)
+    arrive = sorted(rng.integers(0, 3 if growing else 40, n_req).tolist())
+    stop_after = {r: int(rng.integers(1, news[r] + 1)) for r in range(n_req) if rng.random() < 0.3}
+    cancel_at = {r: int(rng.integers(1, 80)) for r in range(n_req) if rng.random() < 0.15}
+    given = {r: [] for r in range(n_req)}         # the tokens handed to each request, in order
+    added, cancelled, finished = set(), set(), set()
+    cached = {}                                   # request -> tokens in its cache, as the plans imply
+    step = 0
+    while len(finished | cancelled) < n_req:
+        for r in range(n_req):
+            if r not in added and arrive[r] <= step:
+                s.add_request(r, list(range(r, r + lens[r])), news[r])
+                added.add(r)
+        for r, at in cancel_at.items():
+            if at == step and r in added and r not in finished and r not in cancelled:
+                s.cancel(r)
+                cancelled.add(r)
+                cached.pop(r, None)
+        plan = s.schedule()
+        for r in plan.preempted:
+            cached.pop(r, None)                   # recomputed from the start
+        seen = set()
+        assert sum(e.count for e in plan.entries) <= budget
+        for e in plan.entries:
+            assert e.request_id not in seen and e.request_id not in finished | cancelled
+            seen.add(e.request_id)
+            assert 1 <= e.count <= max(chunk, 1)
+            assert e.start == cached.get(e.request_id, 0), (e, cached)
+            total = lens[e.request_id] + len(given[e.request_id])
+            assert e.start + e.count <= total
+            assert e.wants_logits == (e.start + e.count == total)
+            cached[e.request_id] = e.start + e.count
+        s.step_done()
+        held = 0
+        for r in added - finished - cancelled:
+            if cm.has(r):
+                n_blocks = len(cm.block_table(r, 0))
+                assert n_blocks * page >= cached.get(r, 0)
+                held += n_blocks
+        assert held + cm.free_pages(0) == pages
+        for e in plan.entries:
+            if e.wants_logits:
+                r = e.request_id
+                tok = 1000 + len(given[r])
+                given[r].append(tok)
+                if s.append_token(r, tok, stop=stop_after.get(r) == len(given[r])):
+                    finished.add(r)
+                    cached.pop(r, None)
+        step += 1
+        assert step < 5000, "the scheduler stopped making progress"
+    for r in finished:
+        info = s.info(r)
+        assert info["generated"] == len(given[r]) == stop_after.get(r, news[r])
+        assert info["finish_reason"] == ("stop" if r in stop_after else "length")
+        assert s.tokens(r) == list(range(r, r + lens[r])) + given[r]
+    assert s.stats()["idle"] and cm.free_pages(0) == pages and cm.free_slots == slots
+    PREEMPTIONS_SEEN[seed] = s.stats()["preemptions"]
+
+
+PREEMPTIONS_SEEN: dict = {}
+
+
+def test_random_arrivals_did_meet_preemption():
+    """The random runs above are only worth their name if pages did run out in a good share of them."""
+    assert len(PREEMPTIONS_SEEN) < 24 or sum(1 for v in PREEMPTIONS_SEEN.values() if v > 0) >= 6
