@@ -2,6 +2,7 @@
 tile shape and K split for the sizes at hand."""
 from __future__ import annotations
 
+import functools
 import os
 
 import torch
@@ -56,6 +57,7 @@ def error_word(device) -> torch.Tensor:
     return e
 
 
+@functools.lru_cache(maxsize=4096)
 def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
     """(bn, split_k) for a product of these sizes: bn > 0 plain tiles of 128 x bn,
     bn < 0 swapped tiles of 128 weight rows x -bn tokens."""
@@ -97,6 +99,7 @@ def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
     return bn, 1
 
 
+@functools.lru_cache(maxsize=4096)
 def _effective_split(K: int, split_k: int) -> int:
     kblocks = (K + 63) // 64
     split_k = max(1, min(split_k, kblocks))
