@@ -11,6 +11,7 @@ portions of a step run as one batch.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -54,7 +55,10 @@ class StepRunner:
         self.tokens = 0
         self.use_graphs = use_graphs and model.graph_safe
         self.graph_width_step = 32        # block-table widths are rounded up to this many pages per graph
-        self._graphs: dict = {}
+        # Captured decode steps by (entries, width bucket), least recently used first. Each holds its own logits
+        # and activations (tens of MB at large batches), so a long-running engine keeps only the most recent ones.
+        self._graphs: OrderedDict = OrderedDict()
+        self.max_graphs = 128
         # arg-max of the last step's logits where the step's graph has computed it (greedy requests then
         # need no launch of their own); None after a step that ran without a graph
         self.last_argmax: Optional[torch.Tensor] = None
@@ -183,11 +187,7 @@ class StepRunner:
         n_meta = self._meta_size(B, B, B, width)
         stage = self._staging(n_meta)
         spans, tables, _ = self._fill(stage.numpy(), entries, q_lens, ctx_lens, slots, ids, cu, rows, width)
-        key = (B, width)
-        g = self._graphs.get(key)
-        if g is None:
-            g = {"meta": torch.empty(n_meta, dtype=torch.int32, device=self.device)}
-            self._graphs[key] = g
+        g = self._graph_slot((B, width), n_meta)
         ops.upload(g["meta"], stage, n_meta)
         self._uploaded()
         if "graph" not in g:
@@ -201,6 +201,19 @@ class StepRunner:
         self.tokens += B
         self.last_argmax = g["argmax"]
         return g["logits"]
+
+    def _graph_slot(self, key, n_meta: int) -> dict:
+        """The record of the captured step for `key`, made (and the least recently used one dropped) if need be."""
+        g = self._graphs.get(key)
+        if g is not None:
+            self._graphs.move_to_end(key)
+            return g
+        if len(self._graphs) >= self.max_graphs:
+            torch.cuda.synchronize(self.device)      # its last replay may still be running
+            self._graphs.popitem(last=False)
+        g = {"meta": torch.empty(n_meta, dtype=torch.int32, device=self.device)}
+        self._graphs[key] = g
+        return g
 
     def _layout(self, B: int, T: int, R: int, width: int):
         """Offsets of the index arrays for a step of this shape (the order `_fill` and
@@ -243,11 +256,7 @@ class StepRunner:
         self.steps += 1
         self.tokens += T
         if graph:
-            key = (B, width)
-            g = self._graphs.get(key)
-            if g is None:
-                g = {"meta": torch.empty(n_meta, dtype=torch.int32, device=self.device)}
-                self._graphs[key] = g
+            g = self._graph_slot((B, width), n_meta)
             ops.upload(g["meta"], stage, n_meta)
             self._uploaded()
             if "graph" not in g:

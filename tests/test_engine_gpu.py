@@ -143,3 +143,29 @@ def test_stop_at_eos_and_request_too_large(folders):
         if eos in out:
             assert out.index(eos) == len(out) - 1
             break
+
+
+def test_captured_steps_are_dropped_least_recently_used_first(folders):
+    """Decode steps are captured per (requests in the step, block-table width). With room for two
+    captures only, requests that finish one after the other (4, 3, 2, 1 in a step) force captures
+    out and, for the widths that come back, in again: the tokens are those of the uncaptured run."""
+    from cellm_b200 import Engine, SamplingParams
+    cfg, _ = plain.load_folder(folders["tiny_a"])
+    prompts = _prompts(cfg["vocab_size"], [5, 9, 3, 12], seed=8)
+    kw = dict(dtype="float32", tokens_per_block=8, total_blocks=64, max_num_seqs=4)
+    ref_eng = Engine(folders["tiny_a"], use_cuda_graphs=False, **kw)
+    eng = Engine(folders["tiny_a"], use_cuda_graphs=True, **kw)
+    eng.runner.max_graphs = 2
+    ids_ref, ids = [], []
+    for i, p in enumerate(prompts):
+        params = SamplingParams.greedy(6 + 7 * i, stop_eos=False)
+        ids_ref.append(ref_eng.add_request(p, params))
+        ids.append(eng.add_request(p, params))
+    while ref_eng.has_unfinished():
+        ref_eng.step()
+    seen = 0
+    while eng.has_unfinished():
+        eng.step()
+        seen = max(seen, len(eng.runner._graphs))
+    assert seen == 2
+    assert [eng.output(i).tokens for i in ids] == [ref_eng.output(i).tokens for i in ids_ref]
