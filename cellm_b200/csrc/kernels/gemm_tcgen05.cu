@@ -191,6 +191,10 @@ struct alignas(1024) GemmSmem {
     int abort_flag;
     int is_last;
     int conv_slots[64];         // EPI = 2: the state slots of the tile's tokens
+    int rope_pos[64];           // EPI = 3: position and page of the tile's tokens
+    int rope_page[64];
+    float ex_ss[4];             // EPI = 3: the epilogue warps' sums of squares and normed values of one token
+    float ex_y[128];
 };
 
 template <typename TO> __device__ __forceinline__ void store_row(TO* dst, const uint32_t* r, int valid, bool aligned);
@@ -268,6 +272,23 @@ struct ConvEpi {
     long long slot_stride;       // floats between slots
     int H, ntaps, n_slots;
 };
+//
+// EPI = 3 (swapped tiles in a cluster; every token of the step belongs to a request of its own; heads
+// of 64): W is q_proj | k_proj | v_proj, so a tile of 128 rows is two whole heads. After the cluster's
+// reduction the two warps of a head hold one token's 64 sums: they round them to bfloat16 as the plain
+// product would have stored them, take the head's RMSNorm (q and k heads), turn the pairs (i, i + 32)
+// by the token's position and write queries to C [M, nh * 64], keys and values to the request's page.
+struct RopeEpi {
+    const __nv_bfloat16* q_w;    // [64] norm weights
+    const __nv_bfloat16* k_w;
+    const int* positions;        // [M]
+    const int* block_table;      // [M][bt_stride]
+    __nv_bfloat16* k_pool;       // [pages][nkv][page_size][64]
+    __nv_bfloat16* v_pool;
+    const float* inv_freq;       // [32][2]: frequency as a float and its remainder
+    float eps;
+    int bt_stride, num_pages, page_size, nh, nkv;
+};
 constexpr int CONV_CH = 42;          // channels per tile of 128 rows
 constexpr int CONV_MAX_TAPS = 4;
 
@@ -275,9 +296,9 @@ template <int BN, int STAGES, bool SWAP, int EPI, bool CLUSTER, typename TO>
 __global__ void __launch_bounds__(192, SWAP ? 2 : 1)      // swapped tiles: two CTAs an SM, so the next product's can move in early
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                     TO* __restrict__ C, float* __restrict__ ws, int* __restrict__ counters, int M, int N, int K,
-                    long long ldc, int kblocks_per_split, int w_is_static, int* __restrict__ err, const ConvEpi conv) {
+                    long long ldc, int kblocks_per_split, int w_is_static, int* __restrict__ err, const ConvEpi conv, const RopeEpi rope) {
     static_assert(!CLUSTER || SWAP, "the cluster reduction serves swapped tiles");
-    static_assert(EPI != 2 || CLUSTER, "the convolution epilogue is written for the cluster's reduction");
+    static_assert(EPI < 2 || CLUSTER, "the convolution and rotation epilogues are written for the cluster's reduction");
     extern __shared__ uint8_t smem_raw[];
     using Smem = GemmSmem<BN, STAGES, CLUSTER ? BN * BM : 0>;
     auto& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -311,6 +332,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     // EPI = 2: what an epilogue thread fetches ahead of the accumulator (see there)
     float cv_wt[CONV_MAX_TAPS - 1] = {}, cv_hist[CONV_MAX_TAPS - 1] = {}, cv_wlast = 0.f, cv_bias = 0.f;
     bool cv_active = false;
+    // EPI = 3: this thread's norm weight and its frequency
+    float rp_w = 0.f, rp_hi = 0.f, rp_lo = 0.f;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -384,6 +407,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                     cv_hist[k] = (k < rows && slot >= 0 && slot < conv.n_slots)
                                      ? conv.state[(long long)slot * conv.slot_stride + (size_t)k * conv.H + ch] : 0.f;
             }
+        }
+        if constexpr (EPI == 3) {
+            // While the products run: positions and pages of the tile's tokens (the step's inputs, the work of no
+            // kernel of this step), this thread's norm weight and frequency.
+            const int pl = (warp & 3) * 32 + lane;
+            if (pl < BN) {
+                int pos = 0, page = -1;
+                if (q0 + pl < Q) {
+                    pos = rope.positions[q0 + pl];
+                    page = rope.block_table[(size_t)(q0 + pl) * rope.bt_stride + pos / rope.page_size];
+                }
+                sm.rope_pos[pl] = pos;
+                sm.rope_page[pl] = page;
+            }
+            const int hh = p0 / 64 + (pl >> 6), i = pl & 63;
+            if (hh < rope.nh) rp_w = __bfloat162float(rope.q_w[i]);
+            else if (hh < rope.nh + rope.nkv) rp_w = __bfloat162float(rope.k_w[i]);
+            rp_hi = rope.inv_freq[2 * lane];
+            rp_lo = rope.inv_freq[2 * lane + 1];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
         }
         const bool ok = mbar_wait(&sm.acc_full, 0, abort_flag);
         if (!ok && lane == 0) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); }
@@ -576,6 +619,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             const int pl = (warp & 3) * 32 + lane, p = p0 + pl;
             const uint32_t rank = cluster_rank();
             const int q_end = min(Q, q0 + BN);
+            if constexpr (EPI == 3) {
+                // Tokens rank, rank + splits, ... of the tile are this CTA's, one at a time; warps 0 and 1 of the
+                // epilogue hold the tile's first head (values 0..31 and 32..63), warps 2 and 3 its second.
+                const int wl = warp & 3, i = pl & 63, half = wl & 1;
+                const int hh = p0 / 64 + (pl >> 6);
+                const int kind = hh < rope.nh ? 0 : (hh < rope.nh + rope.nkv ? 1 : (hh < rope.nh + 2 * rope.nkv ? 2 : 3));
+                for (int ql = (int)rank; q0 + ql < q_end; ql += splits) {
+                    const int q = q0 + ql;
+                    const float* mine = &sm.red[ql * BM + pl];
+                    float v[8];
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) v[r] = r < splits ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
+                    float x = 0.f;
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) x += v[r];
+                    x = __bfloat162float(__float2bfloat16_rn(x));     // as the plain product stores it
+                    // the rotation of this thread's pair, meanwhile: angle = pos * (hi + lo) in split arithmetic
+                    const int pos = sm.rope_pos[ql];
+                    const float fp = (float)pos, a = fp * rp_hi, e = fmaf(fp, rp_hi, -a) + fp * rp_lo;
+                    float sa, ca, se, ce;
+                    sincosf(a, &sa, &ca);
+                    sincosf(e, &se, &ce);
+                    const float cs = ca * ce - sa * se, sn = sa * ce + ca * se;
+                    const float part = warp_sum(x * x);
+                    if (lane == 0) sm.ex_ss[wl] = part;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const float ss = sm.ex_ss[wl & 2] + sm.ex_ss[(wl & 2) + 1];
+                    const float inv = 1.0f / sqrtf(ss / 64.0f + rope.eps);
+                    const float y = x * inv * rp_w;
+                    sm.ex_y[pl] = y;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const float other = sm.ex_y[pl ^ 32];
+                    // values i < 32 are the first of their pair, values i >= 32 the second
+                    const float turned = half == 0 ? y * cs - other * sn : y * cs + other * sn;
+                    if (kind == 0) {
+                        C[(size_t)q * ldc + (size_t)hh * 64 + i] = from_float<TO>(turned);
+                    } else if (kind < 3) {
+                        const int page = sm.rope_page[ql];
+                        if (page < 0 || page >= rope.num_pages) {
+                            if (i == 0) atomicOr(err, CELLM_DEV_BAD_PAGE);
+                        } else {
+                            const int kvh = kind == 1 ? hh - rope.nh : hh - rope.nh - rope.nkv;
+                            const size_t at = ((size_t)page * rope.nkv + kvh) * rope.page_size * 64 +
+                                              (size_t)(pos % rope.page_size) * 64 + i;
+                            if (kind == 1) rope.k_pool[at] = __float2bfloat16_rn(turned);
+                            else rope.v_pool[at] = __float2bfloat16_rn(x);
+                        }
+                    }
+                }
+            }
             if constexpr (EPI == 2) {
                 // Tokens rank, rank + splits, ... of the tile are this CTA's; three of them are worked on side by
                 // side (threads 0..41, 42..83, 84..125: one channel each). The history of the token after this
@@ -632,7 +725,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             // TU of this CTA's tokens at a time: all the peers' pieces of a token are asked for at once (a cluster
             // has at most 8 CTAs), then added in the order of the ranks.
             constexpr int TU = CELLM_CLUSTER_TOKENS_IN_FLIGHT;
-            for (int q = q0 + (int)rank; EPI != 2 && q < q_end; q += TU * splits) {
+            for (int q = q0 + (int)rank; EPI < 2 && q < q_end; q += TU * splits) {
                 if constexpr (EPI == 0) {
                     float v[TU][8];
 #pragma unroll
@@ -923,7 +1016,7 @@ bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
 template <int BN, int STAGES, bool SWAP, int EPI, bool CLUSTER, typename TO>
 int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* ws, int* counters, int M, int N, int K,
            long long ldc, int split_k, int kblocks_per_split, int w_is_static, int* err, cudaStream_t stream,
-           const ConvEpi& conv) {
+           const ConvEpi& conv, const RopeEpi& rope) {
     const size_t smem = sizeof(GemmSmem<BN, STAGES, CLUSTER ? BN * BM : 0>) + 1024;
     static bool configured = false;
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, EPI, CLUSTER, TO>;
@@ -952,7 +1045,7 @@ int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* w
         cfg.numAttrs = 2;
     }
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, m_rows, m_cols, C, ws, counters, M, N, K, ldc, kblocks_per_split,
-                                       w_is_static, err, conv);
+                                       w_is_static, err, conv, rope);
     return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
@@ -1009,12 +1102,12 @@ CELLM_API int cellm_gemm_tcgen05_plan(int M, int N, int K, int bn, int split_k, 
 static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
                      long long ldw, long long ldc, int out_dtype, int bn, int split_k, int epilogue,
                      int w_is_static, float* workspace, int* counters, int* err, cudaStream_t stream,
-                     const ConvEpi& conv) {
+                     const ConvEpi& conv, const RopeEpi& rope) {
     if (M <= 0 || N <= 0) return CELLM_OK;
     if (K <= 0 || (K & 7)) return CELLM_ERR_SIZE;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((lda * 2) & 15) || ((ldw * 2) & 15)) return CELLM_ERR_ALIGN;
     if (out_dtype != CELLM_F32 && out_dtype != CELLM_BF16) return CELLM_ERR_DTYPE;
-    if (epilogue < 0 || epilogue > 2) return CELLM_ERR_ARG;
+    if (epilogue < 0 || epilogue > 3) return CELLM_ERR_ARG;
     const bool swap = bn < 0;
     const int narrow = swap ? -bn : bn;
     if (swap ? (narrow != 16 && narrow != 32 && narrow != 64) : (narrow != 64 && narrow != 128 && narrow != 256))
@@ -1028,7 +1121,7 @@ static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K,
     // (an unsplit SwiGLU tile takes the same road as a cluster of one: gate and up meet in shared memory)
     const bool in_cluster = swap && use_cluster && ((split >= 2 && split <= 8) || (split == 1 && epilogue >= 1));
     if (in_cluster) ws_floats = 0;
-    if (epilogue == 2 && !in_cluster) return CELLM_ERR_ARG;      // the convolution epilogue exists for clustered swapped tiles only
+    if (epilogue >= 2 && !in_cluster) return CELLM_ERR_ARG;      // the convolution and rotation epilogues exist for clustered swapped tiles only
     const int kblocks = (K + BK - 1) / BK;
     const int per = (kblocks + split - 1) / split;
     if (ws_floats > 0 && workspace == nullptr) return CELLM_ERR_ARG;
@@ -1061,14 +1154,14 @@ static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K,
     }
 #define GO3(BN_, ST_, SW_, EP_, CL_)                                                                                  \
     do {                                                                                                              \
-        if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, EP_, CL_, float>(m_rows, m_cols, (float*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream, conv); \
-        else rc = launch<BN_, ST_, SW_, EP_, CL_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream, conv); \
+        if (out_dtype == CELLM_F32) rc = launch<BN_, ST_, SW_, EP_, CL_, float>(m_rows, m_cols, (float*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream, conv, rope); \
+        else rc = launch<BN_, ST_, SW_, EP_, CL_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream, conv, rope); \
     } while (0)
 #define GO2(BN_, ST_, SW_, EP_) GO3(BN_, ST_, SW_, EP_, false)
     // swapped: ST_ stages without, CST_ stages with the cluster's reduction buffer (two CTAs must still fit an SM)
 #define GOS(BN_, ST_, CST_)                                                                                           \
     do {                                                                                                              \
-        if (in_cluster) { if (epilogue == 0) GO3(BN_, CST_, true, 0, true); else if (epilogue == 1) GO3(BN_, CST_, true, 1, true); else GO3(BN_, CST_, true, 2, true); } \
+        if (in_cluster) { if (epilogue == 0) GO3(BN_, CST_, true, 0, true); else if (epilogue == 1) GO3(BN_, CST_, true, 1, true); else if (epilogue == 2) GO3(BN_, CST_, true, 2, true); else GO3(BN_, CST_, true, 3, true); } \
         else { if (epilogue == 0) GO3(BN_, ST_, true, 0, false); else GO3(BN_, ST_, true, 1, false); }                 \
     } while (0)
 #define GO(BN_, ST_, SW_)                           \
@@ -1105,10 +1198,11 @@ static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K,
 CELLM_API int cellm_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
                                  long long ldw, long long ldc, int out_dtype, int bn, int split_k, int epilogue,
                                  int w_is_static, float* workspace, int* counters, int* err, cudaStream_t stream) {
-    if (epilogue == 2) return CELLM_ERR_ARG;     // that epilogue has an entry point of its own
+    if (epilogue >= 2) return CELLM_ERR_ARG;     // those epilogues have entry points of their own
     const ConvEpi none{};
+    const RopeEpi none3{};
     return gemm_impl(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, bn, split_k, epilogue, w_is_static, workspace, counters,
-                     err, stream, none);
+                     err, stream, none, none3);
 }
 
 // in_proj and the gated short convolution of a decode step in one kernel (the kernel's EPI = 2).
@@ -1135,6 +1229,39 @@ CELLM_API int cellm_gemm_conv_tcgen05(void* Y, const void* A, const void* Wt, in
     conv.H = H;
     conv.ntaps = ntaps;
     conv.n_slots = n_slots;
+    const RopeEpi none3{};
     return gemm_impl(Y, A, Wt, M, Nt, K, lda, ldw, (long long)H, CELLM_BF16, bn, split_k, 2, w_is_static, nullptr, nullptr,
-                     err, stream, conv);
+                     err, stream, conv, none3);
+}
+
+// The q/k/v product of a decode step with the heads' RMSNorm, the rotation and the write into the paged cache in
+// its epilogue (the kernel's EPI = 3). A: [M, K] bf16, one token of M different requests. W: q_proj | k_proj | v_proj,
+// [(nh + 2 nkv) * 64, K] bf16 (heads of 64, turned whole in pairs (i, i + 32)). Q: [M, nh * 64] bf16. q_w, k_w: [64]
+// bf16; positions: [M]; block_table: [M][bt_stride]; pools: [pages][nkv][page_size][64] bf16; inv_freq: [32][2]
+// floats (frequency and remainder). bn: -16, -32 or -64; the K split must leave the tile's CTAs in one cluster.
+CELLM_API int cellm_gemm_rope_tcgen05(void* Q, const void* A, const void* W, int M, int K, long long lda, long long ldw,
+                                      int bn, int split_k, const void* q_w, const void* k_w, float eps,
+                                      const int* positions, const int* block_table, int bt_stride, void* k_pool,
+                                      void* v_pool, int num_pages, int page_size, int nh, int nkv,
+                                      const float* inv_freq, int w_is_static, int* err, cudaStream_t stream) {
+    if (M <= 0) return CELLM_OK;
+    if (bn >= 0 || nh <= 0 || nkv <= 0 || page_size <= 0 || num_pages <= 0 || bt_stride <= 0) return CELLM_ERR_SIZE;
+    if (!q_w || !k_w || !positions || !block_table || !k_pool || !v_pool || !inv_freq) return CELLM_ERR_ARG;
+    RopeEpi rope{};
+    rope.q_w = (const __nv_bfloat16*)q_w;
+    rope.k_w = (const __nv_bfloat16*)k_w;
+    rope.positions = positions;
+    rope.block_table = block_table;
+    rope.k_pool = (__nv_bfloat16*)k_pool;
+    rope.v_pool = (__nv_bfloat16*)v_pool;
+    rope.inv_freq = inv_freq;
+    rope.eps = eps;
+    rope.bt_stride = bt_stride;
+    rope.num_pages = num_pages;
+    rope.page_size = page_size;
+    rope.nh = nh;
+    rope.nkv = nkv;
+    const ConvEpi none{};
+    return gemm_impl(Q, A, W, M, (nh + 2 * nkv) * 64, K, lda, ldw, (long long)nh * 64, CELLM_BF16, bn, split_k, 3,
+                     w_is_static, nullptr, nullptr, err, stream, none, rope);
 }

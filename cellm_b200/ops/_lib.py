@@ -46,6 +46,7 @@ _SIGNATURES = {
     "gemm_tcgen05": {
         "cellm_gemm_tcgen05": [P, P, P, I, I, I, L, L, L, I, I, I, I, I, P, P, P, P],
         "cellm_gemm_conv_tcgen05": [P, P, P, I, I, I, L, L, I, I, I, P, P, I, P, L, P, I, I, P, P],
+        "cellm_gemm_rope_tcgen05": [P, P, P, I, I, L, L, I, I, P, P, F, P, P, I, P, P, I, I, I, I, P, I, P, P],
     },
 }
 

@@ -215,3 +215,40 @@ def gemm_conv_bf16(a: torch.Tensor, w_tiled: torch.Tensor, H: int, taps: torch.T
         ptr(taps), ptr(bias), n_taps, ptr(state), state.stride(0), ptr(slot_ids), state.shape[0], _STATIC_FLAG,
         ptr(err), stream_of(a)), "gemm_conv_tcgen05")
     return y
+
+
+def gemm_rope_plan(M: int, nh: int, nkv: int, hd: int, K: int, device) -> tuple[int, int] | None:
+    """(bn, split_k) for the q/k/v product with norm, rotation and cache write in its epilogue, or
+    None if these sizes do not run it (heads of 64; swapped tiles whose K split is one cluster)."""
+    if not _CLUSTER_REDUCE or hd != 64:
+        return None
+    bn, split = plan_tiles(M, (nh + 2 * nkv) * hd, K, _sms(device))
+    if bn >= 0 or (M + -bn - 1) // -bn != 1 or _effective_split(K, split) > 8:
+        return None
+    return bn, split
+
+
+def gemm_rope_bf16(a: torch.Tensor, w_qkv: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, eps: float,
+                   positions: torch.Tensor, block_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                   nh: int, nkv: int, inv_freq: torch.Tensor, plan: tuple[int, int],
+                   err: torch.Tensor | None = None) -> torch.Tensor:
+    """One token of each of M requests: q [M, nh * 64], normed and turned, from a . w_qkv^T; the keys (normed,
+    turned) and values go to the requests' pages [pages, kv heads, page_size, 64]. Heads of 64 turned whole in
+    pairs (i, i + 32); `plan` comes from `gemm_rope_plan`. The arithmetic is that of the product followed by
+    `qk_norm_rope`."""
+    M, K = a.shape
+    pages, pool_kv, page_size, hd = k_pool.shape
+    bf = torch.bfloat16
+    if a.dtype != bf or w_qkv.dtype != bf or q_w.dtype != bf or k_w.dtype != bf or k_pool.dtype != bf or v_pool.dtype != bf:
+        raise ValueError("gemm_rope_bf16: bfloat16 activations, weights, norm weights and pools")
+    if hd != 64 or pool_kv != nkv or v_pool.shape != k_pool.shape or w_qkv.shape[0] != (nh + 2 * nkv) * 64 \
+            or q_w.numel() != 64 or k_w.numel() != 64 or tuple(inv_freq.shape) != (32, 2) or inv_freq.dtype != torch.float32 \
+            or positions.numel() != M or block_table.shape[0] != M:
+        raise ValueError("gemm_rope_bf16: shapes do not fit (heads of 64, one block-table row and one position per token)")
+    q = torch.empty((M, nh * 64), dtype=bf, device=a.device)
+    err = err if err is not None else error_word(a.device)
+    check(fn("gemm_tcgen05", "cellm_gemm_rope_tcgen05")(
+        ptr(q), ptr(a), ptr(w_qkv), M, K, a.stride(0), w_qkv.stride(0), int(plan[0]), int(plan[1]), ptr(q_w), ptr(k_w),
+        float(eps), ptr(positions), ptr(block_table), block_table.stride(0), ptr(k_pool), ptr(v_pool), pages, page_size,
+        nh, nkv, ptr(inv_freq), _STATIC_FLAG, ptr(err), stream_of(a)), "gemm_rope_tcgen05")
+    return q

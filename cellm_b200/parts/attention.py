@@ -4,6 +4,8 @@ q and k head, position encoding, keys and values written to the request's
 pages, softmax(q.k * scale) over all earlier keys (or a window), out_proj."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
@@ -61,11 +63,29 @@ class AttentionMixer(Mixer):
         pos: PartSpec | None = params.get("position")
         self.position = part_class("position", pos.kind)(pos.params, dev) if pos is not None else None
 
+    def _fused_rope_ok(self, x, ctx, cache, rot) -> bool:
+        """One token per request, bfloat16 throughout, heads of 64 turned whole in the "half" layout, own cache.
+        Asked for with CELLM_B200_FUSED_ROPE=1: the kernel is tested, its effect on a step's time is not measured yet."""
+        bf = torch.bfloat16
+        return (ctx.max_q_len == 1 and cache.writes and self.hd == 64 and x.dtype == bf and self.qkv.weight.dtype == bf
+                and self.q_norm_w is not None and self.q_norm_w.dtype == bf and rot is not None
+                and rot[0] == 64 and not rot[1] and cache.k.dtype == bf
+                and os.environ.get("CELLM_B200_FUSED_ROPE", "0") == "1" and ops.tensor_core_ok(x, self.qkv.weight))
+
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         nh, nkv, hd = self.nh, (self.nkv if cache.writes else 0), self.hd
-        qkv = self.qkv(x) if cache.writes else self.q_only(x)
         rot = self.position.rotation() if self.position is not None else (0, False, None)
         bt, kp, vp = (cache.block_table, cache.k, cache.v) if nkv else (None, None, None)
+        if self._fused_rope_ok(x, ctx, cache, rot):
+            # decode steps: the product, the heads' norm, the rotation and the cache write as one kernel
+            from ..ops import gemm_bf16 as tc
+            plan = tc.gemm_rope_plan(ctx.T, nh, nkv, hd, x.shape[1], x.device)
+            if plan is not None:
+                q = tc.gemm_rope_bf16(x, self.qkv.weight, self.q_norm_w, self.k_norm_w, self.norm_eps, ctx.positions,
+                                      bt, kp, vp, nh, nkv, rot[2], plan, ctx.err)
+                o = ops.attention(q, cache.k, cache.v, ctx, cache.block_table, nh, self.scale, self.window)
+                return self.out_proj(o)
+        qkv = self.qkv(x) if cache.writes else self.q_only(x)
         if rot is not None:
             rotary_dim, interleaved, inv_freq = rot
             q = ops.qk_norm_rope(qkv, self.q_norm_w, self.k_norm_w, self.norm_eps, ctx.positions,

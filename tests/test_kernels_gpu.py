@@ -244,6 +244,49 @@ def test_qk_norm_rope_and_page_write(dtype, hd, rot, inter):
     assert e.item() == 2
 
 
+@pytest.mark.parametrize("nh,nkv,K,M,ps,theta", [(32, 8, 2048, 8, 16, 1e6), (3, 1, 96, 5, 8, 1e4), (4, 4, 264, 33, 32, 5e4),
+                                                 (16, 2, 1024, 64, 16, 1e6), (32, 8, 2048, 1, 16, 1e6)])
+def test_qkv_product_with_norm_rotation_and_cache_write_in_its_epilogue(nh, nkv, K, M, ps, theta):
+    """Decode steps: the q/k/v product, the heads' norm, the rotation and the write into the pages as
+    one kernel against the product followed by qk_norm_rope: one token of M requests at positions
+    near and far, pages in scrambled order, an odd number of heads (a tile with a single head)."""
+    from cellm_b200 import ops
+    from cellm_b200.ops import gemm_bf16 as tc
+    from cellm_b200.parts.rope import split_inv_freq
+    hd = 64
+    g = torch.Generator(device=DEV).manual_seed(nh * 100 + M)
+    w = (torch.randn((nh + 2 * nkv) * hd, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    qw = (torch.rand(hd, device=DEV, generator=g) + 0.5).bfloat16()
+    kw = (torch.rand(hd, device=DEV, generator=g) + 0.5).bfloat16()
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    width = 40
+    pos = torch.randint(0, width * ps, (M,), device=DEV, generator=g).int()
+    pos[0] = 0
+    pos[-1] = width * ps - 1
+    pages = M * width
+    bt = torch.randperm(pages, device=DEV, generator=g).int().reshape(M, width).contiguous()
+    seq = torch.arange(M, dtype=torch.int32, device=DEV)
+    inv = split_inv_freq(theta, hd).to(DEV)
+    kp_a = torch.zeros(pages, nkv, ps, hd, device=DEV, dtype=torch.bfloat16)
+    vp_a, kp_b, vp_b = torch.zeros_like(kp_a), torch.zeros_like(kp_a), torch.zeros_like(kp_a)
+    e = err_word()
+    ref = ops.qk_norm_rope(ops.gemm(x, w, torch.bfloat16), qw, kw, 1e-5, pos, seq, bt, kp_a, vp_a, ps, nh, nkv, hd, hd, False, inv, e)
+    plan = tc.gemm_rope_plan(M, nh, nkv, hd, K, DEV)
+    assert plan is not None
+    got = tc.gemm_rope_bf16(x, w, qw, kw, 1e-5, pos, bt, kp_b, vp_b, nh, nkv, inv, plan, e)
+    assert e.item() == 0
+    # the same sums rounded at the same places (the K split may differ, hence a unit of bfloat16 rounding here and there)
+    close(got, ref, torch.bfloat16, "q")
+    close(kp_b, kp_a, torch.bfloat16, "keys")
+    close(vp_b, vp_a, torch.bfloat16, "values")
+    assert torch.equal(kp_b.float().abs().sum(-1) > 0, kp_a.float().abs().sum(-1) > 0)      # the same places were written
+    bad = bt.clone()
+    bad[M - 1, int(pos[M - 1]) // ps] = pages
+    tc.gemm_rope_bf16(x, w, qw, kw, 1e-5, pos, bad, kp_b, vp_b, nh, nkv, inv, plan, e)
+    assert e.item() == 2
+    e.zero_()
+
+
 @pytest.mark.parametrize("wdt", [torch.bfloat16, torch.float32])
 def test_qk_norm_rope_long_batches_of_64_wide_heads(wdt):
     """300 tokens of 64-wide heads take the one-warp-per-token form; it must agree

@@ -98,6 +98,33 @@ def test_prompt_attention_on_tcgen05_in_every_cutting(tmp_path, monkeypatch, nam
     assert calls
 
 
+def test_decode_with_the_rotation_in_the_qkv_product(tmp_path, monkeypatch):
+    """CELLM_B200_FUSED_ROPE=1 sends decode steps of 64-wide heads through the q/k/v product that norms,
+    turns and stores in its epilogue: the same traces, the same plain implementation."""
+    import importlib
+    from cellm_b200.replay import Replayer
+    from cellm_b200.weights import write_random_model
+    tc = importlib.import_module("cellm_b200.ops.gemm_bf16")
+    monkeypatch.setenv("CELLM_B200_FUSED_ROPE", "1")
+    calls = []
+    real = tc.gemm_rope_bf16
+    monkeypatch.setattr(tc, "gemm_rope_bf16", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    config = cfg(vocab_size=900, hidden_size=192, num_hidden_layers=3, layer_types=["full_attention", "conv", "full_attention"],
+                 num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=320)
+    folder = write_random_model(str(tmp_path / "m"), config, seed=32, dtype="bfloat16", init=TEST_INIT)
+    c, w = plain.load_folder(folder)
+    rng = np.random.default_rng(8)
+    reqs = {f"r{i}": rng.integers(0, config["vocab_size"], n).tolist() for i, n in enumerate((150, 9, 300, 67))}
+    ref = {r: plain.forward(c, w, t).numpy() for r, t in reqs.items()}
+    for make in (traces.tail_one_by_one, traces.mixed):
+        steps = make(reqs)
+        rp = Replayer(folder, "bfloat16", traces.max_live_tokens(steps), 32, 4)
+        got = traces.collect(steps, [rp.step(s["entries"], s["end"]) for s in steps])
+        for r, t in reqs.items():
+            check_close(traces.as_matrix(got[r], len(t)), ref[r], "bfloat16", f"fused rope {make.__name__} {r}")
+    assert calls
+
+
 def test_odd_configuration_generates(tmp_path):
     from cellm_b200 import Engine, SamplingParams
     from cellm_b200.weights import write_random_model
