@@ -105,6 +105,10 @@ def test_decode_with_the_rotation_in_the_qkv_product(tmp_path, monkeypatch):
     from cellm_b200.replay import Replayer
     from cellm_b200.weights import write_random_model
     tc = importlib.import_module("cellm_b200.ops.gemm_bf16")
+    att = importlib.import_module("cellm_b200.ops.attention")
+    # prompt portions on the tcgen05 kernel, as in the test above: the two differ in the decode steps only
+    monkeypatch.setitem(att.TC_POLICY, "min_ctas", 0)
+    monkeypatch.setitem(att.TC_POLICY, "min_fill", 0.0)
     monkeypatch.setenv("CELLM_B200_FUSED_ROPE", "1")
     calls = []
     real = tc.gemm_rope_bf16
