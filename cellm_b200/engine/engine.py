@@ -10,14 +10,12 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
-import torch
-
 from ..cache.manager import CacheManager
 from ..config.engine_config import EngineConfig
 from ..models import load_model
 from ..sampling import RequestSampler, SamplingParams, sample_rows, session_seed
 from .scheduler import Scheduler
-from .step import StepEntry, StepRunner
+from .step import StepRunner
 
 
 @dataclass

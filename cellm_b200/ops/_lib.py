@@ -3,7 +3,7 @@ raises at first use; there is no fallback to another implementation."""
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 

@@ -2,7 +2,7 @@ from __future__ import annotations
 
 import torch
 
-from ._lib import check, fn, ptr, require_cuda, stream_of, tag
+from ._lib import check, fn, ptr, stream_of, tag
 
 
 def gemm_plain(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:

@@ -8,7 +8,7 @@ import torch
 
 import plain_lfm2 as plain
 import traces
-from tiny_configs import CONFIGS, TINY_B, make_model
+from tiny_configs import CONFIGS, make_model
 from tolerances import check_close
 
 pytestmark = pytest.mark.gpu

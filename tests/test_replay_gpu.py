@@ -9,7 +9,6 @@ import sys
 
 import numpy as np
 import pytest
-import torch
 
 import plain_lfm2 as plain
 import traces

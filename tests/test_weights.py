@@ -8,8 +8,8 @@ import pytest
 import torch
 
 from cellm_b200.config import load_config
-from cellm_b200.weights import SafetensorsFile, WeightError, expected_tensors, load_weights, save_file, write_random_model
-from tiny_configs import TINY_A, TINY_B, make_model
+from cellm_b200.weights import SafetensorsFile, WeightError, expected_tensors, load_weights, save_file
+from tiny_configs import make_model
 
 
 def test_random_model_folder_is_readable_by_the_safetensors_library(tmp_path):
