@@ -25,6 +25,12 @@
 // each slice writes its partial tile as float into a workspace [split_k, M, N]
 // and the slice that finishes last sums them in a fixed order (see the kernel).
 //
+// Epilogues (template parameter EPI of gemm_tcgen05_kernel; each is described where it is defined):
+//   0  C = A.W^T                      1  SwiGLU over interleaved gate and up blocks
+//   2  in_proj + gated short convolution of a decode step (cellm_gemm_conv_tcgen05)
+//   3  q/k/v product + head norms + rotation + cache write of a decode step (cellm_gemm_rope_tcgen05)
+// 2 and 3 exist for swapped tiles whose K split is summed inside a cluster.
+//
 // The kernel takes part in programmatic dependent launch: barrier set-up, the
 // tensor-memory allocation and the loads of W for the first stages run before
 // the wait on the preceding kernel; only loads of A and all stores come after.
