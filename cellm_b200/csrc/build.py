@@ -30,7 +30,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-Wall"]
 # library name -> (compiler, sources relative to csrc/, extra flags)
 LIBRARIES: dict[str, tuple[str, list[str], list[str]]] = {
     "runtime": ("c++", ["runtime/block_allocator.cc", "runtime/cache_manager.cc",
-                        "runtime/scheduler.cc", "runtime/c_api.cc"], []),
+                        "runtime/scheduler.cc", "runtime/executor.cc", "runtime/c_api.cc"], []),
     "kernels_common": ("nvcc", ["kernels/embed.cu", "kernels/add_rmsnorm.cu", "kernels/short_conv.cu",
                                 "kernels/qk_norm_rope.cu", "kernels/swiglu.cu", "kernels/sample.cu",
                                 "kernels/attention_plain.cu"], []),

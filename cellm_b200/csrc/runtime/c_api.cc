@@ -266,3 +266,36 @@ API void cellm_sched_stats(void* s, long long* stats) {
     stats[0] = sc->num_waiting(); stats[1] = sc->num_running(); stats[2] = (long long)sc->steps();
     stats[3] = (long long)sc->tokens_scheduled(); stats[4] = (long long)sc->preemptions(); stats[5] = sc->idle() ? 1 : 0;
 }
+
+// ------------------------------------------------------------------ executor
+#include "executor.h"
+
+// Sizes of the executor's structs (0 ExecLinear, 1 ExecLayer, 2 ExecProgram, 3 ExecItem, 4 ExecStep), for the
+// caller to check its own layout against.
+API long long cellm_exec_sizeof(int which) {
+    switch (which) {
+        case 0: return sizeof(cellm::ExecLinear);
+        case 1: return sizeof(cellm::ExecLayer);
+        case 2: return sizeof(cellm::ExecProgram);
+        case 3: return sizeof(cellm::ExecItem);
+        case 4: return sizeof(cellm::ExecStep);
+        default: return -1;
+    }
+}
+// What a step needs (see exec_need): out[0] arena bytes, out[1] and out[2] workspace floats. Launches nothing.
+API int cellm_exec_need(const void* program, void* step, long long* out) {
+    return guarded([&] {
+        cellm::exec_need(*static_cast<const cellm::ExecProgram*>(program), *static_cast<cellm::ExecStep*>(step), out);
+        return 0;
+    });
+}
+// Runs one step's forward pass; 0, or -1 with the reason in cellm_last_error().
+API int cellm_exec_forward(const void* program, void* step) {
+    return guarded([&] {
+        return cellm::exec_forward(*static_cast<const cellm::ExecProgram*>(program), *static_cast<cellm::ExecStep*>(step));
+    });
+}
+API int cellm_exec_plan_tiles(long long M, long long N, long long K, long long sms, long long* out) {
+    cellm::plan_tiles(M, N, K, sms, &out[0], &out[1]);
+    return 0;
+}

@@ -11,6 +11,7 @@ portions of a step run as one batch.
 """
 from __future__ import annotations
 
+import os
 from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
@@ -41,9 +42,22 @@ _ERR_BITS = {1: "token id outside the vocabulary", 2: "page id outside the pool"
 
 
 class StepRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager, use_graphs: bool = False):
+    def __init__(self, model: DecoderModel, cache: CacheManager, use_graphs: bool = False,
+                 native_steps: Optional[bool] = None):
+        """`native_steps`: steps that are not replayed as CUDA graphs are launched by the runtime's executor
+        (engine/native_exec.py) where the model consists of parts it knows; others keep the Python parts.
+        None: as the environment says (CELLM_B200_NATIVE_STEPS=1), else off."""
+        if native_steps is None:
+            native_steps = os.environ.get("CELLM_B200_NATIVE_STEPS", "0") == "1"
         self.model, self.cache = model, cache
         self.device = model.device
+        self._forward = model.forward
+        self.native_reason = "not asked for"
+        if native_steps:
+            from .native_exec import NativeForward, unsupported
+            self.native_reason = unsupported(model)
+            if self.native_reason is None:
+                self._forward = NativeForward(model).forward
         from ..ops.gemm_bf16 import error_word
         self.err = error_word(self.device)      # one error word for every kernel on this device
         self._pinned = [None, None]
@@ -272,7 +286,7 @@ class StepRunner:
         self._uploaded()
         ctx_lens = stage.numpy()[spans["ctx"][0]:spans["ctx"][0] + B].tolist()
         ctx, tabs, logit_rows = self._context(dev, spans, tables, q_lens, ctx_lens, max_total)
-        return self.model.forward(ctx, self.cache.bindings(tabs), logit_rows, max_layers)
+        return self._forward(ctx, self.cache.bindings(tabs), logit_rows, max_layers)
 
     def _capture(self, g: dict, spans, tables, q_lens, ctx_lens, max_total_len: int, slots) -> None:
         """Captures the forward pass over g["meta"] as a CUDA graph (see _run_decode_graph)."""
@@ -304,7 +318,7 @@ class StepRunner:
             return self._run_decode_graph(entries)
         self.last_argmax = None
         ctx, tables, logit_rows, totals = self.build_context(entries)
-        logits = self.model.forward(ctx, self.cache.bindings(tables), logit_rows, max_layers)
+        logits = self._forward(ctx, self.cache.bindings(tables), logit_rows, max_layers)
         for e, total in zip(entries, totals):
             self.cache.commit(e.request_id, total)
         self.steps += 1
