@@ -153,3 +153,39 @@ def test_models_with_other_parts_are_left_to_python(monkeypatch):
     assert "norm" in unsupported(model)
     with pytest.raises(ValueError, match="does not run this model"):
         NativeForward(model, [0] * 13, sms=148)
+
+
+def test_random_models_and_steps(monkeypatch):
+    """Two hundred random models (head sizes, groups, widths that do and do not fit the tensor-core rules, one to
+    five taps, bias, tied or not, 32-bit now and then) and steps (single tokens, a few tokens each, prompt
+    portions, one long prompt; pages of 4 to 64), with and without the rotation in the product."""
+    for seed in range(200):
+        rng = np.random.default_rng(seed)
+        hd = int(rng.choice([16, 32, 48, 64, 64, 64, 128]))
+        nkv = int(rng.choice([1, 2, 4, 8]))
+        nh = nkv * int(rng.choice([1, 2, 4, 8] if hd <= 64 else [1, 2]))
+        layers = int(rng.integers(1, 4))
+        config = {"architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2", "vocab_size": int(rng.choice([500, 1000, 40000])),
+                  "hidden_size": int(rng.choice([64, 100, 256, 512, 1024, 2048])), "num_hidden_layers": layers,
+                  "layer_types": [str(rng.choice(["conv", "full_attention"])) for _ in range(layers)],
+                  "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd,
+                  "intermediate_size": int(rng.choice([128, 130, 512, 2048, 8192])), "block_auto_adjust_ff_dim": False,
+                  "rope_theta": 1e4, "conv_L_cache": int(rng.choice([1, 2, 3, 4, 5])), "conv_bias": bool(rng.random() < 0.3),
+                  "norm_eps": 1e-5, "tie_embedding": bool(rng.random() < 0.5), "max_position_embeddings": 100000}
+        B, kind = int(rng.integers(1, 70)), rng.random()
+        if kind < 0.35:
+            q_lens = [1] * B
+        elif kind < 0.6:
+            q_lens = [int(x) for x in rng.integers(1, 5, B)]
+        elif kind < 0.8:
+            q_lens = [int(x) for x in rng.integers(1, 400, min(B, 6))]
+        else:
+            q_lens = [int(rng.integers(64, 4000))]
+        ctx_lens = [int(x) for x in rng.integers(0, 3000, len(q_lens))]
+        dtype = torch.float32 if rng.random() < 0.15 else torch.bfloat16
+        with monkeypatch.context() as m:
+            m.setenv("CELLM_B200_FUSED_ROPE", "1" if rng.random() < 0.5 else "0")
+            try:
+                same(*both_ways(m, config, q_lens, ctx_lens, dtype=dtype, page=int(rng.choice([4, 8, 16, 32, 64]))))
+            except AssertionError as e:
+                raise AssertionError(f"seed {seed}: {config} {q_lens} {ctx_lens}: {e}") from None
