@@ -111,3 +111,36 @@ def test_widths_off_the_tensor_core_kernels_rules_take_the_plain_product(monkeyp
 
 def test_patches_are_put_back():
     assert torch.zeros(1).is_cuda is False
+
+
+def test_step_runner_builds_the_step_and_runs_it(monkeypatch):
+    """The step function itself on the CPU (pinned staging and events replaced by stand-ins): entries are
+    checked, pages reserved, the index arrays laid out, the model run on exactly the given tokens, lengths
+    committed."""
+    from cellm_b200.cache.manager import CacheManager
+    from cellm_b200.engine.step import StepEntry, StepRunner
+    rec = Recorder(monkeypatch)
+    small = dict(WIDE, vocab_size=1000, hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
+                 intermediate_size=512, block_auto_adjust_ff_dim=False)
+    cfg, plan, model = zero_model(small)
+    cache = CacheManager(model.cache_needs(), [e.cache_of for e in plan.order], 16, 8, 2, model.dtype, "cpu")
+    runner = StepRunner(model, cache, use_graphs=False, native_steps=False)
+    monkeypatch.setattr(runner, "_staging", lambda n: torch.empty(max(n, 4096), dtype=torch.int32))
+    monkeypatch.setattr(runner, "_uploaded", lambda: None)
+    cache.add(7)
+    cache.add(9)
+    logits = runner.run([StepEntry(7, [1, 2, 3], [0, 2]), StepEntry(9, [5], [])])
+    assert tuple(logits.shape) == (2, 1000) and cache.tokens(7) == 3 and cache.tokens(9) == 1
+    embed = rec.of("cellm_embed")[0]
+    assert embed[4] == 4                                            # four tokens in the step
+    rec.calls.clear()
+    assert runner.run([StepEntry(7, [4], [])]) is None and cache.tokens(7) == 4        # nothing wanted: no head product
+    assert rec.names()[-1] != "cellm_gemm_tcgen05" or rec.of("cellm_gemm_tcgen05")[-1][G_N] != 1000
+    with pytest.raises(ValueError, match="twice"):
+        runner.run([StepEntry(7, [1], [0]), StepEntry(7, [2], [0])])
+    with pytest.raises(ValueError, match="vocabulary"):
+        runner.run([StepEntry(9, [1000], [0])])
+    from cellm_b200.cache.manager import OutOfPages
+    with pytest.raises(OutOfPages):
+        runner.run([StepEntry(9, list(range(200)), [])])            # 8 pages of 16 tokens do not hold it
+    assert cache.tokens(9) == 1                                     # and nothing was committed
