@@ -1,0 +1,86 @@
+"""The engine's bookkeeping around the step function, on the CPU: kernels are recorders, and the arg-max
+"kernel" hands out tokens the test chooses. Requests are admitted, cut into portions, decoded, stopped at
+the end-of-sequence token, preempted when pages run out, and everything is given back."""
+import ctypes
+
+import pytest
+import torch
+
+from launch_recorder import Recorder, zero_model
+
+CONFIG = {"architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2", "vocab_size": 1000, "hidden_size": 64,
+          "num_hidden_layers": 2, "layer_types": ["conv", "full_attention"], "num_attention_heads": 4,
+          "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 128, "block_auto_adjust_ff_dim": False,
+          "rope_theta": 1e4, "conv_L_cache": 3, "norm_eps": 1e-5, "tie_embedding": True, "max_position_embeddings": 512,
+          "eos_token_id": 7}
+
+
+def engine(monkeypatch, next_token, **kw):
+    """An engine on the CPU whose arg-max gives next_token(row, call number)."""
+    from cellm_b200 import Engine
+    calls = [0]
+
+    def argmax(out, logits, R, V, parts, stream):
+        row = (ctypes.c_int * R).from_address(out)
+        for r in range(R):
+            row[r] = next_token(r, calls[0])
+        calls[0] += 1
+    rec = Recorder(monkeypatch, hooks={"cellm_argmax": argmax})
+    loaded = zero_model(CONFIG)
+    eng = Engine(loaded, dtype="bfloat16", device="cpu", use_cuda_graphs=False, native_steps=False, **kw)
+    monkeypatch.setattr(eng.runner, "_staging", lambda n: torch.empty(max(n, 4096), dtype=torch.int32))
+    monkeypatch.setattr(eng.runner, "_uploaded", lambda: None)
+    monkeypatch.setattr(eng.runner, "check", lambda: None)          # reads the device error word
+    return eng, rec
+
+
+def test_requests_run_to_their_length_and_everything_is_given_back(monkeypatch):
+    from cellm_b200 import SamplingParams
+    eng, rec = engine(monkeypatch, lambda r, n: 100 + n, tokens_per_block=8, total_blocks=32, max_num_seqs=3,
+                      max_batch_tokens=16, prefill_chunk=8)
+    prompts = [list(range(1, 20)), [5, 6, 7], list(range(30, 41)), [9]]
+    outs = eng.generate(prompts, SamplingParams.greedy(5, stop_eos=False))
+    assert [len(o) for o in outs] == [5, 5, 5, 5]
+    st = eng.stats()
+    assert st["idle"] and st["free_pages"] == st["total_pages"] and st["free_slots"] == 3
+    # every step stayed under the token budget, and portions under their limit
+    for args in rec.of("cellm_embed"):
+        assert args[4] <= 16
+
+
+def test_generation_stops_at_the_end_of_sequence_token(monkeypatch):
+    from cellm_b200 import SamplingParams
+    eng, _ = engine(monkeypatch, lambda r, n: 7 if n == 3 else 50, tokens_per_block=8, total_blocks=16, max_num_seqs=2)
+    out = eng.generate([[1, 2, 3]], SamplingParams.greedy(20, stop_eos=True))[0]
+    assert out == [50, 50, 50, 7]
+    eng2, _ = engine(monkeypatch, lambda r, n: 7 if n == 3 else 50, tokens_per_block=8, total_blocks=16, max_num_seqs=2)
+    assert len(eng2.generate([[1, 2, 3]], SamplingParams.greedy(20, stop_eos=False))[0]) == 20
+
+
+def test_preempted_requests_are_recomputed_and_finish(monkeypatch):
+    from cellm_b200 import SamplingParams
+    eng, _ = engine(monkeypatch, lambda r, n: 200 + (n % 50), tokens_per_block=4, total_blocks=14, max_num_seqs=4,
+                    max_batch_tokens=32, prefill_chunk=16)
+    prompts = [list(range(10, 18)) for _ in range(4)]
+    outs = eng.generate(prompts, SamplingParams.greedy(24, stop_eos=False))
+    assert [len(o) for o in outs] == [24] * 4
+    st = eng.stats()
+    assert st["preemptions"] > 0 and st["free_pages"] == st["total_pages"]
+
+
+def test_cancel_and_refusals(monkeypatch):
+    from cellm_b200 import SamplingParams
+    from cellm_b200.engine import SchedulerError
+    eng, _ = engine(monkeypatch, lambda r, n: 11, tokens_per_block=8, total_blocks=8, max_num_seqs=2)
+    a = eng.add_request([1, 2, 3], SamplingParams.greedy(30, stop_eos=False))
+    b = eng.add_request([4, 5], SamplingParams.greedy(3, stop_eos=False))
+    eng.step()
+    eng.cancel(a)
+    while eng.has_unfinished():
+        eng.step()
+    assert eng.output(a).finish_reason == "cancelled" and eng.output(b).tokens == [11, 11, 11]
+    with pytest.raises(SchedulerError):
+        eng.add_request(list(range(60)), SamplingParams.greedy(40))       # more than the pool holds
+    with pytest.raises(ValueError):
+        eng.add_request([5, 100000], SamplingParams.greedy(4))
+    assert eng.stats()["free_pages"] == eng.stats()["total_pages"]
