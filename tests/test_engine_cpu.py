@@ -84,3 +84,41 @@ def test_cancel_and_refusals(monkeypatch):
     with pytest.raises(ValueError):
         eng.add_request([5, 100000], SamplingParams.greedy(4))
     assert eng.stats()["free_pages"] == eng.stats()["total_pages"]
+
+
+def test_sampling_inputs_follow_the_requests_streams_and_histories(monkeypatch):
+    """With temperature, the sampling kernel gets one uniform number per request and step from the request's own
+    XorShift64 stream (seeded as the reference mixes session and seed), its top-k and penalty, and the last tokens
+    of prompt and output as the repetition window."""
+    import numpy as np
+    import plain_lfm2 as plain
+    from cellm_b200 import Engine, SamplingParams
+    from cellm_b200.sampling import session_seed
+    seen = []
+
+    def sample(out, logits, R, V, temperature, top_k, u, penalty, recent, W, max_top_k, group_max, stream):
+        f = lambda a: list((ctypes.c_float * R).from_address(a))
+        rec = np.ctypeslib.as_array((ctypes.c_int * (R * W)).from_address(recent)).reshape(R, W).copy() if W else None
+        seen.append((R, f(temperature), list((ctypes.c_int * R).from_address(top_k)), f(u), f(penalty), rec, W, max_top_k))
+        row = (ctypes.c_int * R).from_address(out)
+        for r in range(R):
+            row[r] = 300 + len(seen)
+    Recorder(monkeypatch, hooks={"cellm_sample": sample})
+    eng = Engine(zero_model(CONFIG), dtype="bfloat16", device="cpu", use_cuda_graphs=False, native_steps=False,
+                 tokens_per_block=8, total_blocks=16, max_num_seqs=2)
+    monkeypatch.setattr(eng.runner, "_staging", lambda n: torch.empty(max(n, 4096), dtype=torch.int32))
+    monkeypatch.setattr(eng.runner, "_uploaded", lambda: None)
+    monkeypatch.setattr(eng.runner, "check", lambda: None)
+    params = SamplingParams(temperature=0.7, top_k=12, seed=99, repeat_penalty=1.2, repeat_window=4, max_new_tokens=3, stop_eos=False)
+    outs = eng.generate([[1, 2, 3, 4, 5, 6], [9]], params)
+    assert outs == [[301, 302, 303], [301, 302, 303]] and len(seen) == 3
+    streams = [plain.XorShift64(session_seed(i, 99)) for i in range(2)]
+    history = [[1, 2, 3, 4, 5, 6], [9]]
+    for step, (R, temp, top_k, u, penalty, recent, W, max_top_k) in enumerate(seen):
+        assert R == 2 and W == 4 and max_top_k == 12 and top_k == [12, 12]
+        assert temp == pytest.approx([0.7, 0.7]) and penalty == pytest.approx([1.2, 1.2])
+        for r in range(2):
+            assert u[r] == pytest.approx(streams[r].next_f32(), abs=1e-7)
+            tail = history[r][-4:]
+            assert list(recent[r][:len(tail)]) == tail and all(v == -1 for v in recent[r][len(tail):])
+            history[r].append(301 + step)
