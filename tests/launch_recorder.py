@@ -12,7 +12,7 @@ class Recorder:
         """Patches (through `monkeypatch`, so that everything is put back) the look-up of the compiled
         entry points, the checks that operands lie on a GPU, the stream and SM queries. `hooks`: entry point
         name -> function of its arguments, run in the kernel's place (to leave something in an output)."""
-        hooks = hooks or {}
+        self.hooks = hooks = dict(hooks or {})
         from cellm_b200.ops import _lib, basic, gemm_bf16
         gemm = importlib.import_module("cellm_b200.ops.gemm")
         attention = importlib.import_module("cellm_b200.ops.attention")

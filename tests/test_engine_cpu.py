@@ -150,3 +150,59 @@ def test_engine_steps_through_the_native_executor(monkeypatch):
     assert native_names == python_names and set(rec2.names()) <= {"cellm_argmax"}
     st = eng2.stats()
     assert st["idle"] and st["free_pages"] == st["total_pages"]
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_requests_through_the_engine(monkeypatch, seed):
+    """Random prompts, lengths, sampling modes, pools and budgets; some requests meet the end-of-sequence token,
+    some are cancelled under way. Every request ends with a reason, no output is longer than asked for, nothing
+    of the engine's per-request state is left behind and all pages and slots come back."""
+    import numpy as np
+    from cellm_b200 import SamplingParams
+    rng = np.random.default_rng(seed)
+    page = int(rng.choice([4, 8, 16]))
+    n = int(rng.integers(2, 9))
+    lens = [int(x) for x in rng.integers(1, 50, n)]
+    news = [int(x) for x in rng.integers(1, 25, n)]
+    need = [-(-(l + g) // page) for l, g in zip(lens, news)]
+    pages = int(max(max(need), sum(need) * rng.uniform(0.3, 1.0)))
+    token = lambda r, k: 7 if rng.random() < 0.04 else int(rng.integers(8, 1000))
+
+    def sample(out, logits, R, V, *rest):
+        row = (ctypes.c_int * R).from_address(out)
+        for r in range(R):
+            row[r] = token(r, 0)
+    eng, rec = engine(monkeypatch, token, tokens_per_block=page, total_blocks=pages, max_num_seqs=int(rng.integers(1, n + 1)),
+                      max_batch_tokens=int(rng.integers(4, 64)), prefill_chunk=int(rng.integers(2, 32)))
+    monkeypatch.setitem(rec.hooks, "cellm_sample", sample)
+    ids, asked, stop = [], {}, {}
+    for l, g in zip(lens, news):
+        greedy = rng.random() < 0.5
+        stop_eos = bool(rng.random() < 0.5)
+        params = SamplingParams.greedy(g, stop_eos=stop_eos) if greedy else SamplingParams(
+            temperature=0.8, top_k=int(rng.choice([0, 40])), seed=int(rng.integers(1, 1000)),
+            repeat_penalty=float(rng.choice([1.0, 1.1])), max_new_tokens=g, stop_eos=stop_eos)
+        rid = eng.add_request([int(x) for x in rng.integers(8, 1000, l)], params)
+        ids.append(rid)
+        asked[rid], stop[rid] = g, stop_eos
+    cancel_at = {rid: int(rng.integers(1, 30)) for rid in ids if rng.random() < 0.2}
+    steps = 0
+    while eng.has_unfinished():
+        for rid, at in cancel_at.items():
+            if at == steps and not eng.output(rid).finished:
+                eng.cancel(rid)
+        eng.step()
+        steps += 1
+        assert steps < 3000
+    for rid in ids:
+        out = eng.output(rid)
+        assert out.finished and out.finish_reason in ("length", "stop", "cancelled")
+        assert len(out.tokens) <= asked[rid]
+        if out.finish_reason == "length":
+            assert len(out.tokens) == asked[rid]
+        if out.finish_reason == "stop":
+            assert stop[rid] and out.tokens[-1] == 7 and 7 not in out.tokens[:-1]
+        if not stop[rid]:
+            assert out.finish_reason != "stop"
+    st = eng.stats()
+    assert st["idle"] and st["free_pages"] == st["total_pages"] and not eng._samplers
