@@ -206,3 +206,41 @@ def test_random_requests_through_the_engine(monkeypatch, seed):
             assert out.finish_reason != "stop"
     st = eng.stats()
     assert st["idle"] and st["free_pages"] == st["total_pages"] and not eng._samplers
+
+
+def test_replayer_maps_requests_reuses_pages_and_refuses_more_than_its_pool(monkeypatch):
+    """Trace replay on the CPU: names become requests, `end` gives pages and slot back so that later requests get
+    them again, a request left out of a step goes on later, and a pool made for --max-tokens holds no more."""
+    from cellm_b200.cache.manager import OutOfPages
+    from cellm_b200.replay import Replayer
+    import traces
+    rec = Recorder(monkeypatch)
+    loaded = zero_model(CONFIG)
+    rp = Replayer(loaded, "bfloat16", max_tokens=128, tokens_per_block=16, max_requests=2, device="cpu")
+    monkeypatch.setattr(rp.runner, "_staging", lambda n: torch.empty(max(n, 4096), dtype=torch.int32))
+    monkeypatch.setattr(rp.runner, "_uploaded", lambda: None)
+    monkeypatch.setattr(rp.runner, "check", lambda: None)
+    assert rp.cache.group_pages == [8]
+    out = rp.step([{"id": "a", "tokens": list(range(1, 41)), "want": [0, 39]}, {"id": "b", "tokens": [5, 6], "want": []}])
+    assert out.shape == (2, 1000) and rp.cache.free_pages(0) == 8 - 3 - 1
+    assert rp.step([{"id": "b", "tokens": [7], "want": []}]) is None             # "a" sits this step out
+    rp.step([{"id": "a", "tokens": [41], "want": [0]}], end=["a"])
+    assert rp.cache.free_pages(0) == 7 and rp.cache.live == 1
+    first_pages = set(range(8)) - {int(rp.cache.block_table(rp._ids["b"], 0)[0])}
+    rp.step([{"id": "c", "tokens": list(range(60)), "want": [59]}])               # takes pages "a" gave back
+    assert set(int(p) for p in rp.cache.block_table(rp._ids["c"], 0)) <= first_pages
+    with pytest.raises(OutOfPages):
+        rp.step([{"id": "c", "tokens": list(range(60)), "want": []}])             # 120 + 3 tokens > the pool's 128
+    rp.step([], end=["b", "c"])
+    assert rp.cache.live == 0 and rp.cache.free_pages(0) == 8
+    # the traces the GPU tests replay need exactly the pool their own accounting asks for
+    reqs = {"x": list(range(70)), "y": list(range(9)), "z": list(range(130))}
+    for make in (traces.whole, traces.tail_one_by_one, traces.portions, traces.mixed):
+        steps = make(reqs)
+        rp2 = Replayer(loaded, "bfloat16", traces.max_live_tokens(steps), 16, 4, device="cpu")
+        monkeypatch.setattr(rp2.runner, "_staging", lambda n: torch.empty(max(n, 4096), dtype=torch.int32))
+        monkeypatch.setattr(rp2.runner, "_uploaded", lambda: None)
+        monkeypatch.setattr(rp2.runner, "check", lambda: None)
+        for s in steps:
+            rp2.step(s["entries"], s["end"])
+        assert rp2.cache.live == 0
