@@ -46,11 +46,11 @@ def lib():
             "cellm_sched_destroy": ([c_void_p], None),
             "cellm_sched_add": ([c_void_p, c_longlong, IP, c_int, c_int], c_int),
             "cellm_sched_schedule": ([c_void_p], c_int),
-            "cellm_sched_plan_entries": ([LP, IP, IP, IP, c_int], c_int),
-            "cellm_sched_plan_preempted": ([LP, c_int], c_int),
-            "cellm_sched_plan_admitted": ([LP, IP, c_int], c_int),
+            "cellm_sched_plan_entries": ([c_void_p, LP, IP, IP, IP, c_int], c_int),
+            "cellm_sched_plan_preempted": ([c_void_p, LP, c_int], c_int),
+            "cellm_sched_plan_admitted": ([c_void_p, LP, IP, c_int], c_int),
             "cellm_sched_step_done": ([c_void_p], c_int),
-            "cellm_sched_plan_shape": ([IP], c_int),
+            "cellm_sched_plan_shape": ([c_void_p, IP], c_int),
             "cellm_sched_plan_fill": ([c_void_p, c_void_p, c_int, c_int, c_int], c_int),
             "cellm_sched_append_rows": ([c_void_p, c_void_p, c_void_p, c_void_p, c_int], c_int),
             "cellm_sched_append": ([c_void_p, c_longlong, c_int, c_int], c_int),

@@ -1,8 +1,11 @@
 // Plain matrix product on the CUDA cores: C[M,N] = A[M,K] . W[N,K]^T with
 // 32-bit multiply-add and 32-bit sums, no tensor cores and no reduced-precision
-// mode. Every element of C is summed over k = 0..K-1 in that order whatever the
-// tile it falls in, so a row's result does not depend on the other rows of the
-// batch. It is the product of the 32-bit path and the reference for the tensor
+// mode. Every element of C is summed over k in runs of GP_RUN consecutive
+// products, each run in order, and the runs' sums are added in order: the
+// rounding of a sum of K terms then grows like sqrt(GP_RUN) + sqrt(K / GP_RUN)
+// units instead of sqrt(K), and the order depends on K alone, whatever the tile
+// an element falls in, so a row's result does not depend on the other rows of
+// the batch. It is the product of the 32-bit path and the reference for the tensor
 // core kernels (the reference's own linear is a scalar loop over k,
 // crates/cellm-model/src/lfm.rs:970-978).
 #include "common.cuh"
@@ -10,6 +13,7 @@
 #define GP_BM 64
 #define GP_BN 64
 #define GP_BK 16
+#define GP_RUN 256    // products summed in order before their sum joins the total; a multiple of GP_BK
 
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
@@ -22,12 +26,18 @@ gemm_plain_kernel(TO* __restrict__ C, const TI* __restrict__ A, const TI* __rest
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * GP_BM, n0 = blockIdx.x * GP_BN;
-    float acc[4][4];
+    float acc[4][4], total[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < 4; ++j) acc[i][j] = total[i][j] = 0.f;
     for (int k0 = 0; k0 < K; k0 += GP_BK) {
+        if (k0 && k0 % GP_RUN == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { total[i][j] += acc[i][j]; acc[i][j] = 0.f; }
+        }
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             const int idx = tid + r * 256;
@@ -58,7 +68,7 @@ gemm_plain_kernel(TO* __restrict__ C, const TI* __restrict__ A, const TI* __rest
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx * 4 + j;
-            if (gn < N) C[(size_t)gm * ldc + gn] = from_float<TO>(acc[i][j]);
+            if (gn < N) C[(size_t)gm * ldc + gn] = from_float<TO>(total[i][j] + acc[i][j]);
         }
     }
 }

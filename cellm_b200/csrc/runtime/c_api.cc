@@ -13,7 +13,9 @@
 
 namespace {
 thread_local std::string g_error;
-thread_local cellm::StepPlan g_plan;
+
+// the step a scheduler planned last
+const cellm::StepPlan& plan_of(void* s) { return static_cast<cellm::Scheduler*>(s)->last_plan(); }
 
 template <typename F>
 int guarded(F&& f) {
@@ -126,48 +128,45 @@ API void cellm_sched_destroy(void* s) { delete static_cast<cellm::Scheduler*>(s)
 API int cellm_sched_add(void* s, long long id, const int* tokens, int n, int max_new) {
     return guarded([&] { static_cast<cellm::Scheduler*>(s)->add_request(id, tokens, n, max_new); return 0; });
 }
-// Plans the next step and keeps the plan for the calling thread; returns the
-// number of entries. The plan's parts are then read with the *_plan_* calls.
+// Plans the next step; returns the number of entries. The scheduler keeps the plan, and its
+// parts are then read with the *_plan_* calls on the same scheduler.
 API int cellm_sched_schedule(void* s) {
-    return guarded([&] {
-        g_plan = static_cast<cellm::Scheduler*>(s)->schedule();
-        return (int)g_plan.entries.size();
-    });
+    return guarded([&] { return (int)static_cast<cellm::Scheduler*>(s)->schedule().entries.size(); });
 }
-API int cellm_sched_plan_entries(long long* ids, int* starts, int* counts, int* wants, int cap) {
-    const int n = (int)g_plan.entries.size();
+API int cellm_sched_plan_entries(void* s, long long* ids, int* starts, int* counts, int* wants, int cap) {
+    const int n = (int)plan_of(s).entries.size();
     if (n > cap) return -3;
     for (int i = 0; i < n; ++i) {
-        ids[i] = g_plan.entries[(size_t)i].id;
-        starts[i] = g_plan.entries[(size_t)i].start;
-        counts[i] = g_plan.entries[(size_t)i].count;
-        wants[i] = g_plan.entries[(size_t)i].wants_logits;
+        ids[i] = plan_of(s).entries[(size_t)i].id;
+        starts[i] = plan_of(s).entries[(size_t)i].start;
+        counts[i] = plan_of(s).entries[(size_t)i].count;
+        wants[i] = plan_of(s).entries[(size_t)i].wants_logits;
     }
     return n;
 }
-API int cellm_sched_plan_preempted(long long* ids, int cap) {
-    const int n = (int)g_plan.preempted.size();
+API int cellm_sched_plan_preempted(void* s, long long* ids, int cap) {
+    const int n = (int)plan_of(s).preempted.size();
     if (n > cap) return -3;
-    for (int i = 0; i < n; ++i) ids[i] = g_plan.preempted[(size_t)i];
+    for (int i = 0; i < n; ++i) ids[i] = plan_of(s).preempted[(size_t)i];
     return n;
 }
-API int cellm_sched_plan_admitted(long long* ids, int* slots, int cap) {
-    const int n = (int)g_plan.admitted.size();
+API int cellm_sched_plan_admitted(void* s, long long* ids, int* slots, int cap) {
+    const int n = (int)plan_of(s).admitted.size();
     if (n > cap) return -3;
-    for (int i = 0; i < n; ++i) { ids[i] = g_plan.admitted[(size_t)i].first; slots[i] = g_plan.admitted[(size_t)i].second; }
+    for (int i = 0; i < n; ++i) { ids[i] = plan_of(s).admitted[(size_t)i].first; slots[i] = plan_of(s).admitted[(size_t)i].second; }
     return n;
 }
 // Shape of the planned step: out[0..4] = entries, tokens, wanted rows, most tokens a
 // request will hold after the step, 1 if every entry is one token whose logits are wanted.
-API int cellm_sched_plan_shape(int* out) {
+API int cellm_sched_plan_shape(void* s, int* out) {
     int T = 0, R = 0, max_total = 0, all_decode = 1;
-    for (const auto& e : g_plan.entries) {
+    for (const auto& e : plan_of(s).entries) {
         T += e.count;
         R += e.wants_logits ? 1 : 0;
         max_total = std::max(max_total, e.start + e.count);
         if (e.count != 1 || !e.wants_logits) all_decode = 0;
     }
-    out[0] = (int)g_plan.entries.size(); out[1] = T; out[2] = R; out[3] = max_total; out[4] = all_decode;
+    out[0] = (int)plan_of(s).entries.size(); out[1] = T; out[2] = R; out[3] = max_total; out[4] = all_decode;
     return 0;
 }
 // Writes the planned step's index arrays into buf, in the order the step function
@@ -178,9 +177,9 @@ API int cellm_sched_plan_shape(int* out) {
 API int cellm_sched_plan_fill(void* s, int* buf, int cap, int width, int n_groups) {
     return guarded([&] {
         auto* sc = static_cast<cellm::Scheduler*>(s);
-        const int B = (int)g_plan.entries.size();
+        const int B = (int)plan_of(s).entries.size();
         int T = 0, R = 0;
-        for (const auto& e : g_plan.entries) { T += e.count; R += e.wants_logits ? 1 : 0; }
+        for (const auto& e : plan_of(s).entries) { T += e.count; R += e.wants_logits ? 1 : 0; }
         const long long need = 3LL * T + (B + 1) + 2LL * B + R + (long long)n_groups * B * width;
         if (need > cap) { g_error = "scheduler: index buffer too small"; return -3; }
         int* ids = buf; int* pos = ids + T; int* seq = pos + T; int* cu = seq + T; int* ctx = cu + B + 1;
@@ -188,7 +187,7 @@ API int cellm_sched_plan_fill(void* s, int* buf, int cap, int width, int n_group
         int t = 0, r = 0;
         cu[0] = 0;
         for (int b = 0; b < B; ++b) {
-            const auto& e = g_plan.entries[(size_t)b];
+            const auto& e = plan_of(s).entries[(size_t)b];
             const auto& rq = sc->request(e.id);
             const auto& rc = sc->cache().request(e.id);
             for (int i = 0; i < e.count; ++i, ++t) {
@@ -216,7 +215,7 @@ API int cellm_sched_append_rows(void* s, const int* tokens, const int* stops, in
     return guarded([&] {
         auto* sc = static_cast<cellm::Scheduler*>(s);
         int r = 0;
-        for (const auto& e : g_plan.entries) {
+        for (const auto& e : plan_of(s).entries) {
             if (!e.wants_logits) continue;
             if (r >= n) { g_error = "scheduler: fewer tokens than wanted rows"; return -3; }
             finished[r] = sc->append_token(e.id, tokens[r], stops[r] != 0) ? 1 : 0;
@@ -226,7 +225,7 @@ API int cellm_sched_append_rows(void* s, const int* tokens, const int* stops, in
     });
 }
 API int cellm_sched_step_done(void* s) {
-    return guarded([&] { static_cast<cellm::Scheduler*>(s)->step_done(g_plan); return 0; });
+    return guarded([&] { static_cast<cellm::Scheduler*>(s)->step_done(plan_of(s)); return 0; });
 }
 API int cellm_sched_append(void* s, long long id, int token, int stop) {
     return guarded([&] { return static_cast<cellm::Scheduler*>(s)->append_token(id, token, stop != 0) ? 1 : 0; });

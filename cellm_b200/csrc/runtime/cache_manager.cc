@@ -47,6 +47,16 @@ bool CacheManager::can_reserve(int64_t id, int new_total) const {
     return true;
 }
 
+bool CacheManager::can_hold(int64_t id, int tokens, int portion) const {
+    const RequestCache& rc = request(id);
+    for (size_t g = 0; g < groups_.size(); ++g) {
+        int held = 0;
+        for (int32_t p : rc.blocks[g]) held += p >= 0 ? 1 : 0;
+        if (pages_for((int)g, tokens, portion) - held > allocs_[g]->free_count()) return false;
+    }
+    return true;
+}
+
 bool CacheManager::reserve(int64_t id, int new_total) {
     if (!can_reserve(id, new_total)) return false;
     RequestCache& rc = requests_.at(id);

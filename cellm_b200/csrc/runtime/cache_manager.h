@@ -50,6 +50,10 @@ public:
     // New pages each group needs so that the request can hold `new_total` tokens.
     std::vector<int> pages_needed(int64_t id, int new_total) const;
     bool can_reserve(int64_t id, int new_total) const;
+    // Whether the free pages suffice for the most pages the request holds at any time while it grows to
+    // `tokens` tokens in portions of at most `portion`: all of them in a group that keeps every key,
+    // the window and one portion in a windowed group (pages_for), less what it holds already.
+    bool can_hold(int64_t id, int tokens, int portion) const;
     // Reserves pages in every group for tokens up to new_total; all or nothing.
     bool reserve(int64_t id, int new_total);
     // Marks tokens up to new_total as written and gives back the pages of

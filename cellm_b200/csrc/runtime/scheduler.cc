@@ -79,8 +79,9 @@ void Scheduler::finish(Request& r, const char* reason) {
     r.finish_reason = reason;
 }
 
-StepPlan Scheduler::schedule() {
-    StepPlan plan;
+const StepPlan& Scheduler::schedule() {
+    StepPlan& plan = plan_;
+    plan = StepPlan{};
     for (int attempt = 0; attempt < 1 + (int)requests_.size(); ++attempt) {
         int budget = cfg_.max_batch_tokens;
         // 1. one token for each decoding request, in rotation order. While prompts are
@@ -148,9 +149,11 @@ StepPlan Scheduler::schedule() {
             if (slot < 0) break;
             // Admit only if the pool could hold all the tokens the request has now;
             // otherwise it would start, starve a decoding request of pages and be
-            // preempted again at once.
+            // preempted again at once. A windowed group holds only its window plus one
+            // portion of them at a time (the measure add_request accepted the request by).
             int n = std::min({(int)r.tokens.size(), cfg_.prefill_chunk, budget});
-            if (!cache_->can_reserve(id, (int)r.tokens.size()) || !cache_->reserve(id, n)) { cache_->release(id); break; }
+            const int portion = std::min(cfg_.prefill_chunk, cfg_.max_batch_tokens);
+            if (!cache_->can_hold(id, (int)r.tokens.size(), portion) || !cache_->reserve(id, n)) { cache_->release(id); break; }
             waiting_.pop_front();
             running_.push_back(id);
             r.state = RequestState::Prefill;

@@ -69,7 +69,10 @@ public:
     Scheduler(SchedulerConfig cfg, CacheManager* cache);
 
     void add_request(int64_t id, const int32_t* tokens, int n, int max_new);
-    StepPlan schedule();
+    // Plans the next step. The plan is also kept as last_plan() until the next call, so that the
+    // calls that follow a step (index arrays, step_done, sampled tokens) refer to this scheduler's own plan.
+    const StepPlan& schedule();
+    const StepPlan& last_plan() const { return plan_; }
     // To be called after the step of `plan` has run: marks the tokens as cached.
     void step_done(const StepPlan& plan);
     // Appends a sampled token; returns true when the request is finished
@@ -95,6 +98,7 @@ private:
 
     SchedulerConfig cfg_;
     CacheManager* cache_;
+    StepPlan plan_;
     std::map<int64_t, Request> requests_;
     std::deque<int64_t> waiting_;
     std::deque<int64_t> running_;  // rotation order

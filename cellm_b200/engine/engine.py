@@ -51,7 +51,11 @@ class Engine:
         self._samplers: dict[int, RequestSampler] = {}
         self._outputs: dict[int, RequestOutput] = {}
         self._next_id = 0
+        self._check_due = False
         self.max_layers: Optional[int] = None     # run only the first layers (tools/infer --max-layers)
+        # Called after every step's forward pass with (ids of the requests whose logits were formed, in row
+        # order; the float32 logits [rows, vocab] on the device, valid until the next step): for inspection.
+        self.on_logits = None
 
     # -------------------------------------------------------------- requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -80,6 +84,7 @@ class Engine:
         self._finish(request_id)
 
     def _finish(self, rid: int) -> None:
+        self._check_due = True       # the device error word is read once per finished request, not per step
         out = self._outputs[rid]
         out.finished = True
         out.finish_reason = self.scheduler.info(rid)["finish_reason"]
@@ -107,6 +112,8 @@ class Engine:
         self.scheduler.step_done()
         produced = []
         if rows:
+            if self.on_logits is not None:
+                self.on_logits(list(rows), logits)
             samplers = [self._samplers[r] for r in rows]
             tokens = sample_rows(logits, samplers, self.runner.last_argmax)
             self.runner.check_rarely()
@@ -119,6 +126,9 @@ class Engine:
                 produced.append((rid, tok))
                 if fin:
                     self._finish(rid)
+        if self._check_due:
+            self._check_due = False
+            self.runner.check()
         return produced
 
     def output(self, request_id: int) -> RequestOutput:
@@ -137,7 +147,13 @@ class Engine:
             return [[] for _ in prompts]
         ids = [self.add_request(p, params, seed=session_seed(i, params.seed)) for i, p in enumerate(prompts)]
         while self.has_unfinished():
-            self.step()
+            before = self.scheduler.stats()
+            if not self.step() and self.has_unfinished():
+                after = self.scheduler.stats()
+                if after["running"] == 0 and after["waiting"] >= before["waiting"] > 0 and not after["preemptions"] > before["preemptions"]:
+                    raise RuntimeError(f"{after['waiting']} requests wait but none can be admitted "
+                                       f"(free pages {self.stats()['free_pages']}, free slots {self.cache.free_slots})")
+        self.runner.check()          # a fault a kernel flagged in any step of these requests
         outs = [self.release_output(i) for i in ids]
         for o in outs:
             if o.finish_reason == "out_of_pages":

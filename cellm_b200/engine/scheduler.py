@@ -59,11 +59,11 @@ class Scheduler:
     def schedule(self) -> StepPlan:
         l = lib()
         checked(l.cellm_sched_schedule(self._h), SchedulerError)
-        n = checked(l.cellm_sched_plan_entries(self._ids, self._a, self._b, self._c, self._cap), SchedulerError)
+        n = checked(l.cellm_sched_plan_entries(self._h, self._ids, self._a, self._b, self._c, self._cap), SchedulerError)
         entries = [PlannedEntry(self._ids[i], self._a[i], self._b[i], bool(self._c[i])) for i in range(n)]
-        n = checked(l.cellm_sched_plan_preempted(self._ids, self._cap), SchedulerError)
+        n = checked(l.cellm_sched_plan_preempted(self._h, self._ids, self._cap), SchedulerError)
         preempted = [self._ids[i] for i in range(n)]
-        n = checked(l.cellm_sched_plan_admitted(self._ids, self._a, self._cap), SchedulerError)
+        n = checked(l.cellm_sched_plan_admitted(self._h, self._ids, self._a, self._cap), SchedulerError)
         admitted = [(self._ids[i], self._a[i]) for i in range(n)]
         return StepPlan(entries, preempted, admitted)
 
@@ -71,7 +71,7 @@ class Scheduler:
         """(entries, tokens, wanted rows, most tokens of a request after the step, all
         entries are single decoded tokens) of the step planned last."""
         buf = (ctypes.c_int * 5)()
-        lib().cellm_sched_plan_shape(buf)
+        lib().cellm_sched_plan_shape(self._h, buf)
         return buf[0], buf[1], buf[2], buf[3], bool(buf[4])
 
     def plan_fill(self, buf_address: int, capacity: int, width: int, n_groups: int) -> int:
@@ -95,11 +95,11 @@ class Scheduler:
         preempted requests; newly admitted (request, slot) pairs; number of entries)."""
         l = lib()
         n_entries = checked(l.cellm_sched_schedule(self._h), SchedulerError)
-        n = checked(l.cellm_sched_plan_entries(self._ids, self._a, self._b, self._c, self._cap), SchedulerError)
+        n = checked(l.cellm_sched_plan_entries(self._h, self._ids, self._a, self._b, self._c, self._cap), SchedulerError)
         rows = [self._ids[i] for i in range(n) if self._c[i]]
-        n = checked(l.cellm_sched_plan_preempted(self._ids, self._cap), SchedulerError)
+        n = checked(l.cellm_sched_plan_preempted(self._h, self._ids, self._cap), SchedulerError)
         preempted = [self._ids[i] for i in range(n)] if n else []
-        n = checked(l.cellm_sched_plan_admitted(self._ids, self._a, self._cap), SchedulerError)
+        n = checked(l.cellm_sched_plan_admitted(self._h, self._ids, self._a, self._cap), SchedulerError)
         admitted = [(self._ids[i], self._a[i]) for i in range(n)] if n else []
         return rows, preempted, admitted, n_entries
 

@@ -67,7 +67,7 @@ class StepRunner:
         self._layouts: dict = {}
         self.steps = 0
         self.tokens = 0
-        self.use_graphs = use_graphs and model.graph_safe
+        self.use_graphs = use_graphs and model.graph_safe and self.device.type == "cuda"
         self.graph_width_step = 32        # block-table widths are rounded up to this many pages per graph
         # Captured decode steps by (entries, width bucket), least recently used first. Each holds its own logits
         # and activations (tens of MB at large batches), so a long-running engine keeps only the most recent ones.

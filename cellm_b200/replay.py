@@ -15,12 +15,14 @@ from .models import load_model
 
 class Replayer:
     def __init__(self, model_dir, dtype: str, max_tokens: int, tokens_per_block: int = 16,
-                 max_requests: int = 4, device: str = "cuda:0"):
+                 max_requests: int = 4, device: str = "cuda:0", use_graphs: bool = True):
         """`model_dir`: a model folder, or the (config, plan, model) triple that
         `load_model` returned (several replays may share one loaded model).
         `max_tokens`: the most tokens live requests hold at any time, each
         request's count rounded up to a multiple of 64; the pools are made for
-        exactly this many, so pages are used again."""
+        exactly this many, so pages are used again.
+        `use_graphs`: steps made of single tokens whose logits are wanted are replayed as CUDA
+        graphs, as the engine's decode steps are; False launches every step kernel by kernel."""
         import torch
         if isinstance(model_dir, (str, bytes)) or hasattr(model_dir, "__fspath__"):
             model_dir = load_model(model_dir, dtype, device)
@@ -32,7 +34,7 @@ class Replayer:
         needs = self.model.cache_needs()
         self.cache = CacheManager(needs, [e.cache_of for e in self.plan.order], tokens_per_block, pages,
                                   max_requests, self.model.dtype, device)
-        self.runner = StepRunner(self.model, self.cache)
+        self.runner = StepRunner(self.model, self.cache, use_graphs=use_graphs)
         self._ids: dict = {}
         self._next = 0
         self._torch = torch

@@ -182,7 +182,7 @@ def swiglu(m, w1, w3, w2):
 # whole model
 # --------------------------------------------------------------------------
 
-def forward(cfg: dict, w: dict, ids, order=None, window=0, hidden_out=None) -> torch.Tensor:
+def forward(cfg: dict, w: dict, ids, order=None, window=0, hidden_out=None, rows=None) -> torch.Tensor:
     """Logits [T, V] of one whole sequence (crates/cellm-model/src/lfm.rs:
     263-763: pre-norm block :333-347, residual :610-612, ffn_norm :615-629,
     residual :665-667, embedding_norm :670-687, tied output :689-757).
@@ -191,6 +191,7 @@ def forward(cfg: dict, w: dict, ids, order=None, window=0, hidden_out=None) -> t
     `(layer, cache_of)` where cache_of is the index in `order` of an earlier
     attention item whose keys and values this item reads instead of its own.
     (addition) an untied `lm_head.weight` is used when `tie_embedding` is false.
+    `rows`: form the logits of these positions only ([len(rows), V]).
     """
     dt = next(iter(w.values())).dtype
     ids = torch.as_tensor(ids)
@@ -226,6 +227,8 @@ def forward(cfg: dict, w: dict, ids, order=None, window=0, hidden_out=None) -> t
                        w[p + "feed_forward.w2.weight"])
     if hidden_out is not None:
         hidden_out.append(x)
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long)]
     xf = rms_norm(x, w["model.embedding_norm.weight"], eps)
     tied = cfg.get("tie_embedding", cfg.get("tie_word_embeddings", True))
     head = w["model.embed_tokens.weight"] if tied else w["lm_head.weight"]

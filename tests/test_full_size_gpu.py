@@ -8,33 +8,21 @@ import pytest
 
 import plain_lfm2 as plain
 import traces
+from tiny_configs import FULL_WIDTH, FULL_WIDTH_INIT
 from tolerances import K, K_SELF, check_close
 
 pytestmark = pytest.mark.gpu
 
-CONFIG = {
-    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
-    "vocab_size": 65536, "hidden_size": 2048, "num_hidden_layers": 4,
-    "layer_types": ["conv", "full_attention", "conv", "full_attention"],
-    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
-    "intermediate_size": 12288, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
-    "block_ffn_dim_multiplier": 1.0, "rope_theta": 1000000.0, "conv_L_cache": 3, "conv_bias": False,
-    "norm_eps": 1e-5, "tie_embedding": True, "max_position_embeddings": 128000,
-}
+CONFIG = FULL_WIDTH
 LENGTHS = (37, 300, 129, 8)
-# The bounds of tolerances.py are stated for sums of a few thousand products (the tiny
-# configurations). Here the longest sum has 8192 (the feed-forward's second product), four times
-# as many, and the rounding of a 32-bit sum grows with the square root of its length: twice the
-# bound against the plain implementation in 32-bit. bfloat16's bound is set by the rounding of the
-# activations, not by the sums, and stays. Cuttings are compared with each other at the usual bounds.
-K_PLAIN = {"float32": 2 * K["float32"], "bfloat16": K["bfloat16"]}
+K_PLAIN = K      # the bounds of tolerances.py, as for the tiny configurations
 
 
 @pytest.fixture(scope="module")
 def full(tmp_path_factory):
-    from cellm_b200.weights import InitSpec, write_random_model
+    from cellm_b200.weights import write_random_model
     folder = write_random_model(str(tmp_path_factory.mktemp("full") / "m"), CONFIG, seed=5, dtype="bfloat16",
-                                init=InitSpec(linear_std=0.03, embedding_std=0.03, conv_tap_std=0.3, norm_jitter=0.1))
+                                init=FULL_WIDTH_INIT)
     cfg, w = plain.load_folder(folder)
     rng = np.random.default_rng(9)
     reqs = {f"r{i}": rng.integers(0, CONFIG["vocab_size"], n).tolist() for i, n in enumerate(LENGTHS)}
@@ -61,3 +49,14 @@ def test_full_size_layers_in_every_cutting(full, dtype):
         for r, t in reqs.items():
             check_close(traces.as_matrix(results[fam][r], len(t)), traces.as_matrix(results["whole"][r], len(t)),
                         dtype, f"{dtype} {fam} vs whole {r}", k=K_SELF[dtype])
+    # the decode steps above ran as CUDA graphs, as in serving; kernel by kernel they give the same
+    for make in (traces.tail_one_by_one, traces.mixed):
+        steps = make(reqs)
+        rp = Replayer(loaded, dtype, traces.max_live_tokens(steps), 16, 4, use_graphs=False)
+        got = traces.collect(steps, [rp.step(s["entries"], s["end"]) for s in steps])
+        assert not rp.runner._graphs
+        for r, t in reqs.items():
+            check_close(traces.as_matrix(got[r], len(t)), ref[r], dtype, f"{dtype} {make.__name__} no graphs {r}",
+                        k=K_PLAIN[dtype])
+            check_close(traces.as_matrix(got[r], len(t)), traces.as_matrix(results[make.__name__][r], len(t)),
+                        dtype, f"{dtype} {make.__name__}: kernel by kernel vs graphs {r}", k=K_SELF[dtype])

@@ -10,6 +10,7 @@ import pytest
 import plain_lfm2 as plain
 import traces
 from tiny_configs import TEST_INIT
+from token_checks import check_greedy
 from tolerances import check_close
 
 pytestmark = pytest.mark.gpu
@@ -140,7 +141,5 @@ def test_odd_configuration_generates(tmp_path):
         eng = Engine(folder, dtype=dtype, tokens_per_block=page, total_blocks=64, max_num_seqs=3, max_batch_tokens=24, prefill_chunk=16)
         outs = eng.generate(prompts, SamplingParams.greedy(8, stop_eos=False))
         for p, o in zip(prompts, outs):
-            ref = plain.generate(c, w, p, 8)
-            assert o[0] == ref[0] and len(o) == 8
-            if dtype == "float32":
-                assert o == ref
+            assert len(o) == 8
+            check_greedy(c, w, p, o, dtype, f"{dtype} prompt of {len(p)}")

@@ -36,10 +36,12 @@ def models(tmp_path_factory):
     return out
 
 
-def run_trace(folder, dtype, steps, page, max_tokens=None):
+def run_trace(folder, dtype, steps, page, max_tokens=None, use_graphs=True):
     from cellm_b200.replay import Replayer
-    rp = Replayer(folder, dtype, max_tokens or traces.max_live_tokens(steps), page, 4)
+    rp = Replayer(folder, dtype, max_tokens or traces.max_live_tokens(steps), page, 4, use_graphs=use_graphs)
     outs = [rp.step(s["entries"], s["end"]) for s in steps]
+    decode_steps = sum(all(len(e["tokens"]) == 1 and e["want"] == [0] for e in s["entries"]) for s in steps)
+    assert (len(rp.runner._graphs) > 0) == (use_graphs and decode_steps > 0), "decode steps did not take the asked path"
     assert rp.cache.live == 0
     assert all(rp.cache.free_pages(g) == rp.cache.group_pages[g] for g in range(len(rp.cache.group_pages)))
     return traces.collect(steps, outs)
@@ -63,6 +65,14 @@ def test_every_cutting_matches_plain(models, name, dtype):
         for rid, toks in reqs.items():
             check_close(traces.as_matrix(results[fam][rid], len(toks)), traces.as_matrix(results["whole"][rid], len(toks)),
                         dtype, f"{name} {dtype} {fam} vs whole {rid}", k=K_SELF[dtype])
+    # Decode steps above were replayed as CUDA graphs (block tables padded to the graph's width, the number of key
+    # splits planned from that width), as serving replays them; launched kernel by kernel they must give the same.
+    for fam in ("tail", "mixed"):
+        got = run_trace(folder, dtype, FAMILIES[fam](reqs), PAGE[name], use_graphs=False)
+        for rid, toks in reqs.items():
+            check_close(traces.as_matrix(got[rid], len(toks)), ref[rid], dtype, f"{name} {dtype} {fam} no graphs {rid}")
+            check_close(traces.as_matrix(got[rid], len(toks)), traces.as_matrix(results[fam][rid], len(toks)),
+                        dtype, f"{name} {dtype} {fam}: kernel by kernel vs graphs {rid}", k=K_SELF[dtype])
 
 
 def test_mixed_trace_reuses_pages(models):

@@ -249,3 +249,40 @@ PREEMPTIONS_SEEN: dict = {}
 def test_random_arrivals_did_meet_preemption():
     """The random runs above are only worth their name if pages did run out in a good share of them."""
     assert len(PREEMPTIONS_SEEN) < 24 or sum(1 for v in PREEMPTIONS_SEEN.values() if v > 0) >= 6
+
+
+def test_a_prompt_longer_than_a_windowed_pool_is_admitted_and_runs_through():
+    """A windowed group holds a window and a portion of keys, not the prompt: a request accepted by
+    that measure must also be admitted by it, or it waits for ever."""
+    cm = CacheManager([PagedKV(1, 8, 0), PagedKV(1, 8, 8)], [None, None], 4, [16, 6], 2, torch.float32, "cpu")
+    s = Scheduler(cm, 8, 8, 256)
+    s.add_request(0, list(range(40)), 6)            # 46 tokens: 12 pages of the full group, at most 5 of the windowed one
+    assert cm.pages_for(1, 46, 8) <= 6 < (46 + 3) // 4
+    steps = 0
+    while not s.stats()["idle"]:
+        plan, _ = run_step(s)
+        assert plan.entries, "a step planned nothing although a request waits"
+        assert cm.free_pages(1) >= 0
+        steps += 1
+        assert steps < 100
+    assert s.info(0)["finish_reason"] == "length" and s.info(0)["generated"] == 6
+    assert cm.free_pages(0) == 16 and cm.free_pages(1) == 6 and cm.free_slots == 2
+    # and what the windowed pool can never hold is refused when added, not left waiting
+    with pytest.raises(SchedulerError, match="pages"):
+        Scheduler(CacheManager([PagedKV(1, 8, 32)], [None], 4, [6], 2, torch.float32, "cpu"), 8, 8, 256) \
+            .add_request(0, list(range(40)), 6)
+
+
+def test_two_schedulers_keep_their_own_plans():
+    """The planned step belongs to its scheduler: two engines stepped in turn on one thread do not mix them."""
+    cm1, s1 = make()
+    cm2, s2 = make()
+    s1.add_request(0, list(range(5)), 3)
+    s2.add_request(7, list(range(11)), 3)
+    p1 = s1.schedule()
+    p2 = s2.schedule()
+    assert s1.plan_shape()[:2] == (1, 5) and s2.plan_shape()[:2] == (1, 8)
+    assert [e.request_id for e in p1.entries] == [0] and [e.request_id for e in p2.entries] == [7]
+    s1.step_done()
+    s2.step_done()
+    assert s1.info(0)["computed"] == 5 and s2.info(7)["computed"] == 8
