@@ -3,7 +3,6 @@ crates/cellm-sdk/src/lib.rs:18-54, keeps tokens_per_block, total_blocks and
 the sampling defaults in one struct; sampling has a struct of its own here)."""
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass
 
 import torch
@@ -34,14 +33,9 @@ class EngineConfig:
     device: str = "cuda:0"
     seed: int = 1
     use_cuda_graphs: bool = True
-    # steps that carry prompt tokens launched by the native runtime instead of Python (engine/native_exec.py);
-    # None: as the environment says (CELLM_B200_NATIVE_STEPS=1), else off
-    native_steps: bool | None = None
 
     def __post_init__(self):
         self.dtype = parse_dtype(self.dtype)
-        if self.native_steps is None:
-            self.native_steps = os.environ.get("CELLM_B200_NATIVE_STEPS", "0") == "1"
         for n in ("tokens_per_block", "total_blocks", "max_num_seqs", "max_batch_tokens", "prefill_chunk"):
             if getattr(self, n) <= 0:
                 raise ValueError(f"EngineConfig.{n} must be positive")

@@ -42,16 +42,32 @@ class OrderEntry:
 
 @dataclass(frozen=True)
 class ModelPlan:
+    """`embedding` and `head` are parts like the others (families "embedding" and "head"). For the usual pair, a
+    table look-up and a plain output product, a file tensor's name may be given in their place: `embedding` the
+    table [vocab, hidden]; `head` the output matrix [vocab, hidden], or None for one tied to the embedding."""
     hidden_size: int
     vocab_size: int
     max_positions: int
-    embedding: str                      # file tensor [vocab, hidden]
+    embedding: Any                      # PartSpec, or the name of the table's file tensor
     final_norm: PartSpec
-    head: Optional[str]                 # file tensor [vocab, hidden]; None = tied to the embedding
+    head: Any                           # PartSpec, or the name of the matrix' file tensor, or None (tied)
     layers: tuple[LayerSpec, ...]
     order: tuple[OrderEntry, ...]
     eos_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
+
+    def __post_init__(self):
+        sizes = {"vocab_size": self.vocab_size, "dim": self.hidden_size}
+        if isinstance(self.embedding, str):
+            object.__setattr__(self, "embedding", PartSpec("lookup", dict(sizes), {"weight": self.embedding}))
+        if self.head is None or isinstance(self.head, str):
+            name = self.head if self.head is not None else self.embedding.weights.get("weight")
+            object.__setattr__(self, "head", PartSpec("linear", dict(sizes), {"weight": name}))
+
+    @property
+    def tied(self) -> bool:
+        """Whether the head reads the embedding's tensor."""
+        return self.head.weights.get("weight") == self.embedding.weights.get("weight")
 
     def validate(self) -> None:
         from .errors import ConfigError

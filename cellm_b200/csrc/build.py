@@ -104,15 +104,8 @@ def _key(compiler: str, sources: list[str], flags: list[str]) -> str:
     return h.hexdigest()[:16]
 
 
-def _extra_flags(compiler: str) -> list[str]:
-    """Further compiler flags from the environment (CELLM_B200_NVCC_FLAGS for the kernels), for
-    experiments with a kernel's compile-time constants; they take part in the binary's key."""
-    return os.environ.get("CELLM_B200_NVCC_FLAGS", "").split() if compiler == "nvcc" else []
-
-
 def library_path(name: str) -> str:
     compiler, sources, extra = LIBRARIES[name]
-    extra = extra + _extra_flags(compiler)
     flags = (NVCC_FLAGS if compiler == "nvcc" else CXX_FLAGS) + extra
     return os.path.join(build_dir(), f"lib{name}-{_key(compiler, sources, flags)}.so")
 
@@ -138,7 +131,6 @@ def _run(cmd: list[str], what: str) -> None:
 def build(name: str, force: bool = False) -> str:
     """Compile library `name` if its binary is missing; return the path."""
     compiler, sources, extra = LIBRARIES[name]
-    extra = extra + _extra_flags(compiler)
     path = library_path(name)
     if os.path.isfile(path) and not force:
         return path
@@ -158,9 +150,9 @@ def build(name: str, force: bool = False) -> str:
         if os.path.exists(tmp):
             os.unlink(tmp)
     _say(f"compiled {name} in {time.time() - t0:.1f} s")
-    # older binaries of this library are of no use any more (an experiment's binary leaves the others alone)
+    # older binaries of this library are of no use any more
     prefix = f"lib{name}-"
-    for f in ([] if _extra_flags(compiler) else os.listdir(os.path.dirname(path))):
+    for f in os.listdir(os.path.dirname(path)):
         if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(path):
             try:
                 os.unlink(os.path.join(os.path.dirname(path), f))

@@ -86,22 +86,22 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // it writes anything an earlier kernel may still read; what comes before the
 // wait (barrier set-up, tensor-memory allocation, loads of weights) overlaps
 // the tail of the previous kernel. pdl_trigger() lets the following kernel
-// begin its own preamble. CELLM_B200_PDL=0 in the environment turns the
-// attribute off (the instructions are then no-ops).
+// begin its own preamble.
+//
+// Some kernels go further and read, before their wait, data that only an
+// EARLIER STEP wrote (the convolution's state, keys and values that were in
+// the cache before this step). With small grids several kernels can be in
+// flight at once, so this is safe only if a step's kernels cannot overlap the
+// previous step's. The invariant: the first kernel of every forward pass (the
+// embedding) is launched WITHOUT the attribute (cellm_launch_serial), so it
+// starts only when everything before it on the stream has finished, and every
+// later kernel of the pass waits, directly or through its predecessors, on it.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-inline int cellm_pdl_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = std::getenv("CELLM_B200_PDL");
-        v = (e && e[0] == '0') ? 0 : 1;
-    }
-    return v;
-}
 template <typename... KArgs, typename... Args>
-inline cudaError_t cellm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                Args&&... args) {
+inline cudaError_t cellm_launch_with(int overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -109,15 +109,32 @@ inline cudaError_t cellm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block,
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = cellm_pdl_enabled();
+    attr[0].val.programmaticStreamSerializationAllowed = overlap;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t cellm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args&&... args) {
+    return cellm_launch_with(1, kernel, grid, block, smem, stream, std::forward<Args>(args)...);
+}
+// The launch of a step's first kernel: it may not begin before the stream's earlier work has finished.
+template <typename... KArgs, typename... Args>
+inline cudaError_t cellm_launch_serial(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                       Args&&... args) {
+    return cellm_launch_with(0, kernel, grid, block, smem, stream, std::forward<Args>(args)...);
 }
 
 #define CELLM_RUN(kernel, grid, block, smem, stream, ...)                                   \
     do {                                                                                    \
         cudaError_t e__ = cellm_launch(kernel, dim3(grid), dim3(block), smem, stream, __VA_ARGS__); \
+        if (e__ != cudaSuccess) return (int)e__;                                            \
+    } while (0)
+
+#define CELLM_RUN_SERIAL(kernel, grid, block, smem, stream, ...)                            \
+    do {                                                                                    \
+        cudaError_t e__ = cellm_launch_serial(kernel, dim3(grid), dim3(block), smem, stream, __VA_ARGS__); \
         if (e__ != cudaSuccess) return (int)e__;                                            \
     } while (0)
 

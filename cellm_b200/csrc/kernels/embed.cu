@@ -26,14 +26,16 @@ CELLM_API int cellm_upload(void* dst, const void* pinned_src, long long bytes, c
     return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
+// The embedding is the first kernel of a forward pass: it is launched without the attribute that lets a kernel
+// start under its predecessor (see common.cuh), so that no kernel of this pass overlaps the pass before it.
 CELLM_API int cellm_embed(float* out, const void* table, int table_dtype, const int* ids, int T, int H,
                           int V, int* err, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == CELLM_F32)
-        CELLM_RUN(embed_kernel<float>, T, threads, 0, stream, out, (const float*)table, ids, H, V, err);
+        CELLM_RUN_SERIAL(embed_kernel<float>, T, threads, 0, stream, out, (const float*)table, ids, H, V, err);
     else if (table_dtype == CELLM_BF16)
-        CELLM_RUN(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, out, (const __nv_bfloat16*)table, ids, H, V, err);
+        CELLM_RUN_SERIAL(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, out, (const __nv_bfloat16*)table, ids, H, V, err);
     else
         return CELLM_ERR_DTYPE;
     return CELLM_OK;

@@ -43,12 +43,8 @@
 
 namespace {
 
-#ifndef CELLM_CLUSTER_TOKENS_IN_FLIGHT
-// Tokens whose pieces a CTA asks its cluster peers for at once. Measured at 1 and 4 (LFM2-1.2B sizes, 1, 8 and
-// 64 requests): four in flight cost 3 to 5 % of the decode step (30 more registers a thread, predicated loads)
-// and gained nothing, so one it is.
+// Tokens whose pieces a CTA asks its cluster peers for at once (more in flight cost registers and gained nothing).
 #define CELLM_CLUSTER_TOKENS_IN_FLIGHT 1
-#endif
 
 constexpr int BM = 128;
 constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
@@ -1040,7 +1036,7 @@ int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* w
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = cellm_pdl_enabled();
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (CLUSTER) {      // the K split of a tile is one cluster along z
@@ -1122,10 +1118,9 @@ static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K,
     long long ws_floats;
     int split;
     cellm_gemm_tcgen05_plan(M, N, K, bn, split_k, epilogue, &ws_floats, &split);
-    static const bool use_cluster = [] { const char* e = std::getenv("CELLM_B200_CLUSTER_REDUCE"); return !(e && e[0] == '0'); }();
     // swapped tiles whose K split fits a cluster (2..8 CTAs) sum their pieces through shared memory
     // (an unsplit SwiGLU tile takes the same road as a cluster of one: gate and up meet in shared memory)
-    const bool in_cluster = swap && use_cluster && ((split >= 2 && split <= 8) || (split == 1 && epilogue >= 1));
+    const bool in_cluster = swap && ((split >= 2 && split <= 8) || (split == 1 && epilogue >= 1));
     if (in_cluster) ws_floats = 0;
     if (epilogue >= 2 && !in_cluster) return CELLM_ERR_ARG;      // the convolution and rotation epilogues exist for clustered swapped tiles only
     const int kblocks = (K + BK - 1) / BK;

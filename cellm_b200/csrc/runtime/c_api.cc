@@ -269,15 +269,26 @@ API void cellm_sched_stats(void* s, long long* stats) {
 // ------------------------------------------------------------------ executor
 #include "executor.h"
 
-// Sizes of the executor's structs (0 ExecLinear, 1 ExecLayer, 2 ExecProgram, 3 ExecItem, 4 ExecStep), for the
-// caller to check its own layout against.
+// Sizes of the executor's structs, for the caller to check its own layout against: 0 ExecLinear, 1 ExecOp,
+// 2 ExecProgram, 3 ExecItem, 4 ExecStep, 5 ExecRegs, 6 EmbedParams, 7 RmsNormParams, 8 ShortConvParams,
+// 9 AttentionParams, 10 SwiGLUParams, 11 HeadParams, 12 PythonParams, 13 ExecOps, 14 LinearParams.
 API long long cellm_exec_sizeof(int which) {
     switch (which) {
         case 0: return sizeof(cellm::ExecLinear);
-        case 1: return sizeof(cellm::ExecLayer);
+        case 1: return sizeof(cellm::ExecOp);
         case 2: return sizeof(cellm::ExecProgram);
         case 3: return sizeof(cellm::ExecItem);
         case 4: return sizeof(cellm::ExecStep);
+        case 5: return sizeof(cellm::ExecRegs);
+        case 6: return sizeof(cellm::EmbedParams);
+        case 7: return sizeof(cellm::RmsNormParams);
+        case 8: return sizeof(cellm::ShortConvParams);
+        case 9: return sizeof(cellm::AttentionParams);
+        case 10: return sizeof(cellm::SwiGLUParams);
+        case 11: return sizeof(cellm::HeadParams);
+        case 12: return sizeof(cellm::PythonParams);
+        case 13: return sizeof(cellm::ExecOps);
+        case 14: return sizeof(cellm::LinearParams);
         default: return -1;
     }
 }
@@ -292,6 +303,13 @@ API int cellm_exec_need(const void* program, void* step, long long* out) {
 API int cellm_exec_forward(const void* program, void* step) {
     return guarded([&] {
         return cellm::exec_forward(*static_cast<const cellm::ExecProgram*>(program), *static_cast<cellm::ExecStep*>(step));
+    });
+}
+// One mixer or feed-forward record by itself (see exec_part); with dry != 0 it only fills need[0..2].
+API int cellm_exec_part(const void* program, void* step, const void* op, const void* y_in, void* out, int dry, long long* need) {
+    return guarded([&] {
+        return cellm::exec_part(*static_cast<const cellm::ExecProgram*>(program), *static_cast<cellm::ExecStep*>(step),
+                                *static_cast<const cellm::ExecOp*>(op), y_in, out, dry != 0, need);
     });
 }
 API int cellm_exec_plan_tiles(long long M, long long N, long long K, long long sms, long long* out) {

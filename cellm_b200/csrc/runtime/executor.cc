@@ -13,7 +13,8 @@ typedef void* P;
 typedef const void* CP;
 typedef int (*EmbedFn)(P out, CP table, int tag, CP ids, int T, int H, int V, P err, P stream);
 typedef int (*AddRmsnormFn)(P x, CP delta, CP w, int w_tag, P y, CP rows, int n, int H, float eps, int act_tag, P stream);
-typedef int (*SwigluFn)(P h, CP gu, int T, int ff, int tag, P stream);
+typedef int (*ResidualAddFn)(P x, CP delta, i64 n, int act_tag, P stream);
+typedef int (*SwigluFn)(P h, CP gu, int T, int ff, int tag, int gu_tag, P stream);
 typedef int (*ShortConvFn)(P y, CP bcx, CP w, CP bias, int w_tag, P state, i64 slot_stride, CP slot_ids, CP seq, CP cu, int T,
                            int B, int H, int taps, int n_slots, int max_q_len, int act_tag, P err, P stream);
 typedef int (*QkNormRopeFn)(P q, CP qkv, i64 row_stride, CP q_w, CP k_w, int w_tag, float eps, CP positions, CP seq, CP bt,
@@ -38,6 +39,7 @@ typedef int (*GemmRopeFn)(P q, CP a, CP w, int M, int K, i64 lda, i64 ldw, int b
                           CP positions, CP bt, int bt_stride, P kp, P vp, int pages, int page_size, int nh, int nkv, CP inv_freq,
                           int w_is_static, P err, P stream);
 
+
 struct KernelError : std::runtime_error {
     int code;
     KernelError(const char* what, int c) : std::runtime_error(std::string(what) + ": status " + std::to_string(c)), code(c) {}
@@ -54,7 +56,7 @@ i64 effective_split(i64 K, i64 split_k) {
 }
 
 // Bump allocation out of the step's arena: `x` and the two output slots live for the whole step, the rest of a
-// half layer's buffers are given back when the next half begins.
+// half layer's buffers are given back when the next norm begins.
 struct Arena {
     char* base;
     i64 size, top = 0, mark = 0, peak = 0;
@@ -77,11 +79,21 @@ struct Run {
     i64 act;        // element type of the activations
     bool dry = false;       // walk the step and note what it needs, launch nothing
     i64 launches = 0, need_gemm_ws = 0, need_attn_ws = 0;
+    // the registers, and the two buffers that native parts leave their outputs in by turns
+    ExecRegs regs{};
+    void* slot[2] = {nullptr, nullptr};
+    int turn = 0;
 
-    template <typename F> F fn(ExecFn which) const { return reinterpret_cast<F>(p.fns[which]); }
+    ExecFn last_fn = FN_COUNT;
+    template <typename F> F fn(ExecFn which) {
+        if (!p.fns[which]) throw std::runtime_error("executor: entry point " + std::to_string((int)which) + " is not loaded");
+        last_fn = which;
+        return reinterpret_cast<F>(p.fns[which]);
+    }
     void ok(int code, const char* what) {
         if (code != 0) throw KernelError(what, code);
         ++launches;
+        if (last_fn < FN_COUNT) ++s.calls[last_fn];
     }
 #define LAUNCH(call, what) ok(dry ? 0 : (call), what)
 
@@ -97,7 +109,9 @@ struct Run {
     void gemm_tc(void* c, const void* a, const ExecLinear& l, i64 M, i64 N, i64 lda, i64 out_dtype, i64 bn, i64 split_k,
                  i64 epilogue) {
         const i64 split = effective_split(l.K, split_k);
-        const bool in_cluster = bn < 0 && p.cluster_reduce && ((split >= 2 && split <= 8) || (split == 1 && epilogue == 1));
+        // swapped tiles whose K split is one thread-block cluster (2..8 CTAs) sum their pieces through shared
+        // memory: no workspace, no counters
+        const bool in_cluster = bn < 0 && ((split >= 2 && split <= 8) || (split == 1 && epilogue == 1));
         const bool through_ws = !in_cluster && (split > 1 || (epilogue == 1 && bn < 0));
         void* ws = nullptr;
         if (through_ws) {
@@ -105,6 +119,8 @@ struct Run {
             if (!dry && split * M * N > s.gemm_ws_floats) throw std::runtime_error("executor: the products' workspace is too small");
             ws = s.gemm_ws;
         }
+        // plain tiles leave the sum of their K-split pieces to a second kernel; swapped tiles outside a cluster let
+        // the last CTA of a tile sum them
         void* counters = (split > 1 && !in_cluster && bn < 0) ? s.counters : nullptr;
         LAUNCH(fn<GemmTcFn>(FN_GEMM_TCGEN05)(c, a, l.w, (int)M, (int)N, (int)l.K, lda, l.ldw, epilogue ? N / 2 : N, (int)out_dtype, (int)bn,
                                          (int)split_k, (int)epilogue, (int)p.static_flag, ws, counters, s.err, s.stream),
@@ -112,11 +128,10 @@ struct Run {
         if (bn > 0 && split > 1) ++launches;          // the kernel that sums the K-split pieces
     }
 
-    // a [M, K] (row pitch lda) . w^T -> a new [M, N] of out_dtype
-    void* linear(const void* a, const ExecLinear& l, i64 M, i64 lda, i64 out_dtype, i64 N = -1) {
+    // a [M, K] (row pitch lda) . w^T -> c [M, N] of out_dtype
+    void product(void* c, const void* a, const ExecLinear& l, i64 M, i64 lda, i64 out_dtype, i64 N = -1) {
         if (N < 0) N = l.N;
         if (l.dtype != act) throw std::runtime_error("executor: a weight whose element type differs from the activations'");
-        void* c = arena.take(M * N * elt(out_dtype));
         if (act == EXEC_F32 || !tc_ok(l, lda)) {
             gemm_plain(c, a, l, M, N, lda, out_dtype);
         } else {
@@ -124,47 +139,117 @@ struct Run {
             plan_tiles(M, N, l.K, p.sms, &bn, &split);
             gemm_tc(c, a, l, M, N, lda, out_dtype, bn, split, 0);
         }
+    }
+    void* linear(const void* a, const ExecLinear& l, i64 M, i64 lda, i64 out_dtype, i64 N = -1) {
+        void* c = arena.take(M * (N < 0 ? l.N : N) * elt(out_dtype));
+        product(c, a, l, M, lda, out_dtype, N);
         return c;
     }
 
     // the plan of a decode product with an epilogue of its own, or false
     bool epilogue_plan(i64 M, i64 N, i64 K, i64* bn, i64* split) const {
-        if (!p.cluster_reduce) return false;
         plan_tiles(M, N, K, p.sms, bn, split);
         return *bn < 0 && ceil_div(M, -*bn) == 1 && effective_split(K, *split) <= 8;
     }
 
-    void* add_rmsnorm(void* x, const void* delta, const void* w, i64 w_dtype, double eps, const void* rows, i64 n) {
-        void* y = arena.take(n * p.H * elt(act));
-        LAUNCH(fn<AddRmsnormFn>(FN_ADD_RMSNORM)(x, delta, w, (int)w_dtype, y, rows, (int)n, (int)p.H, (float)eps, (int)act, s.stream),
+    // ---- registers -----------------------------------------------------------------------------------------------
+    // a part's output becomes the addend that waits; one that waits already goes into the stream first
+    void set_pending(const void* out) {
+        if (regs.pending)
+            LAUNCH(fn<ResidualAddFn>(FN_RESIDUAL_ADD)(regs.x, regs.pending, s.T * p.H, (int)act, s.stream), "residual_add");
+        regs.pending = out;
+    }
+    const void* input() const {
+        if (!regs.y) throw std::runtime_error("executor: a part wants activations before any norm has left some");
+        return regs.y;
+    }
+
+    void embed(const EmbedParams& e) {
+        LAUNCH(fn<EmbedFn>(FN_EMBED)(regs.x, e.table, (int)e.dtype, s.ids, (int)s.T, (int)p.H, (int)p.V, s.err, s.stream), "embed");
+    }
+    void rms_norm(const RmsNormParams& n) {
+        const bool rows = regs.phase == 2;
+        arena.release();
+        const i64 count = rows ? s.R : s.T;
+        void* y = arena.take(count * p.H * elt(act));
+        LAUNCH(fn<AddRmsnormFn>(FN_ADD_RMSNORM)(regs.x, regs.pending, n.w, (int)n.dtype, y, rows ? s.rows : nullptr, (int)count, (int)p.H,
+                                            (float)n.eps, (int)act, s.stream),
            "add_rmsnorm");
-        return y;
+        if (!rows) regs.pending = nullptr;      // with rows given the stream itself is not touched
+        regs.y = y;
+    }
+    void head(const HeadParams& h) {
+        if (regs.phase != 2) throw std::runtime_error("executor: the output product belongs to the epilogue");
+        if (h.w.dtype != act) throw std::runtime_error("executor: a head whose element type differs from the activations'");
+        product(regs.logits, input(), h.w, s.R, p.H, EXEC_F32);
+    }
+    void python(const PythonParams& py) {
+        if (dry) return;
+        if (!p.python) throw std::runtime_error("executor: a Python part in a program without a callback");
+        if (p.python(py.token, &regs) != 0) throw std::runtime_error("executor: a Python part raised");
     }
 
-    void* feed_forward(const ExecLayer& L, const void* x, void* out);
-    void* short_conv(const ExecLayer& L, const ExecItem& it, const void* x, void* out);
-    void* attention(const ExecLayer& L, const ExecItem& it, const void* x, void* out);
-    void* attend(const ExecLayer& L, const ExecItem& it, const void* q);
-    void into(void* out, const void* a, const ExecLinear& l, i64 M, i64 lda);
+    void feed_forward(const SwiGLUParams& L, const void* x, void* out);
+    void short_conv(const ShortConvParams& L, const ExecItem& it, const void* x, void* out);
+    void attention(const AttentionParams& L, const ExecItem& it, const void* x, void* out);
+    void* attend(const AttentionParams& L, const ExecItem& it, const void* q, void* o = nullptr);
+
+    // a mixer or feed-forward record: reads `in`, writes `out`
+    void produce(const ExecOp& op, const ExecItem* it, const void* in, void* out) {
+        switch (op.kind) {
+            case OP_SHORT_CONV:
+                if (!it) throw std::runtime_error("executor: a mixer outside the layers");
+                short_conv(*static_cast<const ShortConvParams*>(op.params), *it, in, out);
+                break;
+            case OP_ATTENTION:
+                if (!it) throw std::runtime_error("executor: a mixer outside the layers");
+                attention(*static_cast<const AttentionParams*>(op.params), *it, in, out);
+                break;
+            case OP_SWIGLU: feed_forward(*static_cast<const SwiGLUParams*>(op.params), in, out); break;
+            case OP_LINEAR: {
+                const LinearParams& l = *static_cast<const LinearParams*>(op.params);
+                product(out, in, l.w, s.T, l.lda, l.out_dtype);
+                break;
+            }
+            case OP_ATTEND: {
+                if (!it) throw std::runtime_error("executor: attention outside the layers");
+                attend(*static_cast<const AttentionParams*>(op.params), *it, in, out);
+                break;
+            }
+            default: throw std::runtime_error("executor: record kind " + std::to_string(op.kind) + " produces nothing");
+        }
+    }
+
+    void run(const ExecOp& op) {
+        const ExecItem* it = regs.phase == 1 ? &s.items[regs.item] : nullptr;
+        switch (op.kind) {
+            case OP_EMBED: embed(*static_cast<const EmbedParams*>(op.params)); break;
+            case OP_RMS_NORM: rms_norm(*static_cast<const RmsNormParams*>(op.params)); break;
+            case OP_HEAD: head(*static_cast<const HeadParams*>(op.params)); break;
+            case OP_PYTHON: python(*static_cast<const PythonParams*>(op.params)); break;
+            case OP_SHORT_CONV: case OP_ATTENTION: case OP_SWIGLU: {
+                void* out = slot[turn];
+                produce(op, it, input(), out);
+                set_pending(out);
+                turn ^= 1;
+                break;
+            }
+            default: throw std::runtime_error("executor: unknown record kind " + std::to_string(op.kind));
+        }
+    }
+    void run(const ExecOps& ops) {
+        for (i64 i = 0; i < ops.n; ++i) run(ops.ops[i]);
+    }
 };
-
-// the last product of a half layer writes into the step's output slot instead of the scratch arena
-void Run::into(void* out, const void* a, const ExecLinear& l, i64 M, i64 lda) {
-    if (l.dtype != act) throw std::runtime_error("executor: a weight whose element type differs from the activations'");
-    if (act == EXEC_F32 || !tc_ok(l, lda)) {
-        gemm_plain(out, a, l, M, l.N, lda, act);
-    } else {
-        i64 bn, split;
-        plan_tiles(M, l.N, l.K, p.sms, &bn, &split);
-        gemm_tc(out, a, l, M, l.N, lda, act, bn, split, 0);
-    }
-}
 
 }  // namespace
 
 void plan_tiles(i64 M, i64 N, i64 K, i64 sms, i64* bn_out, i64* split_out) {
     const i64 kblocks = ceil_div(K, 64);
     if (M <= 64) {
+        // Swapped tiles: 128 weight rows by 16, 32 or 64 tokens. Enough CTAs to fill the SMs, and no CTA with much
+        // more than ~300 KB of weights to stream by itself; at most 8 (the split of a tile is one thread-block
+        // cluster) and at least four K blocks each. Products with tiles to spare are not split.
         const i64 narrow = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
         const i64 tiles = ceil_div(N, 128);
         i64 split;
@@ -181,6 +266,7 @@ void plan_tiles(i64 M, i64 N, i64 K, i64 sms, i64* bn_out, i64* split_out) {
     }
     i64 bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
     if (bn == 256) {
+        // 128-wide tiles cost about 0.55 of a 256-wide one; take them when their waves finish sooner
         const i64 mt = ceil_div(M, 128);
         const i64 waves256 = ceil_div(mt * ceil_div(N, 256), sms);
         const i64 waves128 = ceil_div(mt * ceil_div(N, 128), sms);
@@ -188,13 +274,17 @@ void plan_tiles(i64 M, i64 N, i64 K, i64 sms, i64* bn_out, i64* split_out) {
     }
     i64 tiles = ceil_div(N, bn) * ceil_div(M, 128);
     if (tiles < sms / 2) {
+        // Too few plain tiles to fill the GPU (a few hundred tokens, or a narrow product).
         if (M <= 128) {
+            // up to two token tiles: swapped tiles of 128 weight rows by 64 tokens, the K split summed in a cluster
             const i64 stiles = ceil_div(N, 128) * ceil_div(M, 64);
             const i64 want = sms * 85 / 100;
             *bn_out = -64;
             *split_out = stiles >= want ? 1 : std::max<i64>(1, std::min({ceil_div(want, stiles), kblocks / 4, (i64)8}));
             return;
         }
+        // more tokens: tiles of 128 x 128 with K split until the SMs are filled; the pieces go through the
+        // workspace and a second kernel sums them
         bn = N > 64 ? 128 : 64;
         tiles = ceil_div(N, bn) * ceil_div(M, 128);
         *bn_out = bn;
@@ -207,30 +297,30 @@ void plan_tiles(i64 M, i64 N, i64 K, i64 sms, i64* bn_out, i64* split_out) {
 
 namespace {
 
-void* Run::feed_forward(const ExecLayer& L, const void* x, void* out) {
+void Run::feed_forward(const SwiGLUParams& L, const void* x, void* out) {
     const i64 T = s.T, H = p.H;
     void* h;
-    if (L.ff_fused && act == EXEC_BF16 && tc_ok(L.gate_up, H)) {
+    if (L.fused && act == EXEC_BF16 && tc_ok(L.gate_up, H)) {
         i64 bn, split;
         plan_tiles(T, L.gate_up.N, L.gate_up.K, p.sms, &bn, &split);
         if (bn == 64) bn = 128;
         h = arena.take(T * L.ff * elt(act));
         gemm_tc(h, x, L.gate_up, T, L.gate_up.N, H, act, bn, split, 1);
-    } else if (L.ff_fused) {
+    } else if (L.fused) {
         throw std::runtime_error("executor: activations do not fit the fused SwiGLU kernel");
     } else {
-        void* gu = linear(x, L.gate_up, T, H, act);
+        // gate and up stay in 32-bit until silu(g) * u is formed, as in the fused epilogue: one rounding, not three
+        void* gu = linear(x, L.gate_up, T, H, EXEC_F32);
         h = arena.take(T * L.ff * elt(act));
-        LAUNCH(fn<SwigluFn>(FN_SWIGLU)(h, gu, (int)T, (int)L.ff, (int)act, s.stream), "swiglu");
+        LAUNCH(fn<SwigluFn>(FN_SWIGLU)(h, gu, (int)T, (int)L.ff, (int)act, (int)EXEC_F32, s.stream), "swiglu");
     }
-    into(out, h, L.down, T, L.ff);
-    return out;
+    product(out, h, L.down, T, L.ff, act);
 }
 
-void* Run::short_conv(const ExecLayer& L, const ExecItem& it, const void* x, void* out) {
+void Run::short_conv(const ShortConvParams& L, const ExecItem& it, const void* x, void* out) {
     const i64 T = s.T, H = p.H;
     void* y = nullptr;
-    if (L.in_proj_tiled && s.max_q_len == 1 && act == EXEC_BF16) {
+    if (p.fused_conv && L.in_proj_tiled && s.max_q_len == 1 && act == EXEC_BF16) {
         ExecLinear tiled = L.in_proj;
         tiled.w = L.in_proj_tiled;
         tiled.N = L.tiled_rows;
@@ -239,7 +329,7 @@ void* Run::short_conv(const ExecLayer& L, const ExecItem& it, const void* x, voi
         if (tc_ok(tiled, H) && epilogue_plan(T, L.tiled_rows, H, &bn, &split)) {
             y = arena.take(T * H * elt(act));
             LAUNCH(fn<GemmConvFn>(FN_GEMM_CONV)(y, x, L.in_proj_tiled, (int)T, (int)L.tiled_rows, (int)H, H, tiled.ldw, (int)H, (int)bn,
-                                            (int)split, L.taps, L.conv_bias, (int)L.n_taps, it.state, it.slot_stride, s.slot_ids,
+                                            (int)split, L.taps, L.bias, (int)L.n_taps, it.state, it.slot_stride, s.slot_ids,
                                             (int)it.n_slots, (int)p.static_flag, s.err, s.stream),
                "gemm_conv_tcgen05");
         }
@@ -247,23 +337,23 @@ void* Run::short_conv(const ExecLayer& L, const ExecItem& it, const void* x, voi
     if (!y) {
         void* bcx = linear(x, L.in_proj, T, H, act);
         y = arena.take(T * H * elt(act));
-        LAUNCH(fn<ShortConvFn>(FN_SHORT_CONV)(y, bcx, L.taps, L.conv_bias, (int)L.taps_dtype, it.state, it.slot_stride, s.slot_ids,
+        LAUNCH(fn<ShortConvFn>(FN_SHORT_CONV)(y, bcx, L.taps, L.bias, (int)L.taps_dtype, it.state, it.slot_stride, s.slot_ids,
                                           s.seq_of_token, s.cu_seqlens, (int)T, (int)s.B, (int)H, (int)L.n_taps, (int)it.n_slots,
                                           (int)s.max_q_len, (int)act, s.err, s.stream),
            "short_conv");
         if (L.n_taps > 1 && !(s.max_q_len > 0 && s.max_q_len <= 4)) ++launches;     // the state update is a launch of its own
     }
-    into(out, y, L.conv_out, T, H);
-    return out;
+    product(out, y, L.out_proj, T, H, act);
 }
 
-void* Run::attend(const ExecLayer& L, const ExecItem& it, const void* q) {
+void* Run::attend(const AttentionParams& L, const ExecItem& it, const void* q, void* o) {
     const i64 T = s.T, nh = L.nh, nkv = L.nkv, hd = L.hd;
-    void* o = arena.take(T * nh * hd * elt(act));
+    if (!o) o = arena.take(T * nh * hd * elt(act));
     const float scale = (float)L.scale;
     if (act == EXEC_BF16 && (hd == 32 || hd == 64 || hd == 128) && L.scale > 0) {
         const i64 G = nh / nkv;
         if (s.max_q_len * G <= 16) {
+            // decoded tokens: one CTA per (request, kv head, piece of the keys)
             const i64 blocks = ceil_div(s.max_total_len, 64);
             const i64 nsplit = std::max<i64>(1, std::min(4 * p.sms / (s.B * nkv), blocks / 4));
             void *part_o = nullptr, *part_ml = nullptr, *counters = nullptr;
@@ -283,6 +373,8 @@ void* Run::attend(const ExecLayer& L, const ExecItem& it, const void* q) {
                "attention_decode");
             return o;
         }
+        // prompt portions that fill the tcgen05 kernel's pairs of 128-row tiles and enough CTAs (below that the
+        // mma.sync kernel with its split over the keys fills the GPU better)
         const i64 ps = it.page_size;
         if (hd == 64 && G <= 128 && 128 % G == 0 && (ps == 8 || ps == 16 || ps == 32 || ps == 64 || ps == 128)) {
             const i64 per_tile = 256 / G;
@@ -297,6 +389,8 @@ void* Run::attend(const ExecLayer& L, const ExecItem& it, const void* q) {
                 return o;
             }
         }
+        // How many CTAs share the keys of one tile: enough to fill the GPU when the batch alone does not, but at
+        // least two blocks of 64 keys each.
         const bool wide = s.max_q_len * G > 16;
         const i64 bm = wide ? 64 : 16;
         i64 n_tiles = 0;
@@ -320,6 +414,7 @@ void* Run::attend(const ExecLayer& L, const ExecItem& it, const void* q) {
         if (nsplit > 1) ++launches;                    // the merge of the pieces
         return o;
     }
+    // 32-bit, other head sizes: one block per (token, head) over the block table
     LAUNCH(fn<AttentionPlainFn>(FN_ATTENTION_PLAIN)(o, q, it.k, it.v, s.positions, s.seq_of_token, it.block_table, (int)it.bt_stride,
                                                 (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, (int)nkv, (int)hd, scale,
                                                 (int)L.window, (int)act, s.err, s.stream),
@@ -327,10 +422,12 @@ void* Run::attend(const ExecLayer& L, const ExecItem& it, const void* q) {
     return o;
 }
 
-void* Run::attention(const ExecLayer& L, const ExecItem& it, const void* x, void* out) {
+void Run::attention(const AttentionParams& L, const ExecItem& it, const void* x, void* out) {
     const i64 T = s.T, H = p.H, nh = L.nh, hd = L.hd;
     const i64 nkv = it.writes ? L.nkv : 0;
     void* q = nullptr;
+    // decode steps, bfloat16, heads of 64 turned whole in the "half" layout, a cache of the item's own: the product,
+    // the heads' norm, the rotation and the cache write as one kernel
     const bool rope_fused = p.fused_rope && s.max_q_len == 1 && it.writes && hd == 64 && act == EXEC_BF16 &&
                             L.qkv.dtype == EXEC_BF16 && L.q_norm_w && L.qk_dtype == EXEC_BF16 && L.rot == 64 && !L.interleaved &&
                             L.inv_freq && tc_ok(L.qkv, H);
@@ -354,49 +451,34 @@ void* Run::attention(const ExecLayer& L, const ExecItem& it, const void* x, void
            "qk_norm_rope");
     }
     void* o = attend(L, it, q);
-    into(out, o, L.attn_out, T, nh * hd);
-    return out;
+    product(out, o, L.out_proj, T, nh * hd, act);
 }
 
-}  // namespace
-
-namespace {
 int walk(const ExecProgram& p, ExecStep& s, bool dry, i64* need) {
     Run r{p, s, Arena{static_cast<char*>(s.arena), s.arena_bytes}, p.act_dtype};
     r.dry = r.arena.dry = dry;
     const i64 T = s.T, H = p.H, e = elt(p.act_dtype);
     s.launches = 0;
+    for (i64& c : s.calls) c = 0;
     if (T <= 0) return 0;
     if (s.n_order > p.n_order) throw std::runtime_error("executor: more order items than the program has");
-    void* x = r.arena.take(T * H * 4);
-    void* slot[2] = {r.arena.take(T * H * e), r.arena.take(T * H * e)};
+    r.regs.x = r.arena.take(T * H * 4);
+    r.slot[0] = r.arena.take(T * H * e);
+    r.slot[1] = r.arena.take(T * H * e);
     r.arena.keep();
-    r.ok(r.dry ? 0 : r.fn<EmbedFn>(FN_EMBED)(x, p.embedding, (int)p.embedding_dtype, s.ids, (int)T, (int)H, (int)p.V, s.err, s.stream), "embed");
-    const void* pending = nullptr;
-    int turn = 0;
+    r.regs.phase = 0;
+    r.run(p.prologue);
+    r.regs.phase = 1;
     for (i64 i = 0; i < s.n_order; ++i) {
-        const ExecLayer& L = p.layers[p.order[i]];
-        const ExecItem& it = s.items[i];
-        r.arena.release();
-        void* y = r.add_rmsnorm(x, pending, L.norm1_w, L.norm1_dtype, L.norm1_eps, nullptr, T);
-        pending = L.kind == 0 ? r.short_conv(L, it, y, slot[turn]) : r.attention(L, it, y, slot[turn]);
-        turn ^= 1;
-        r.arena.release();
-        y = r.add_rmsnorm(x, pending, L.norm2_w, L.norm2_dtype, L.norm2_eps, nullptr, T);
-        pending = r.feed_forward(L, y, slot[turn]);
-        turn ^= 1;
+        const i64 layer = p.order[i];
+        if (layer < 0 || layer >= p.n_layers) throw std::runtime_error("executor: the run order names a layer the program lacks");
+        r.regs.item = i;
+        r.run(p.layers[layer]);
     }
     if (s.R > 0) {
-        r.arena.release();
-        void* xf = r.add_rmsnorm(x, pending, p.final_w, p.final_dtype, p.final_eps, s.rows, s.R);
-        if (p.head.dtype != p.act_dtype) throw std::runtime_error("executor: a head whose element type differs from the activations'");
-        if (p.act_dtype == EXEC_F32 || !r.tc_ok(p.head, H)) {
-            r.gemm_plain(s.logits, xf, p.head, s.R, p.head.N, H, EXEC_F32);
-        } else {
-            i64 bn, split;
-            plan_tiles(s.R, p.head.N, p.head.K, p.sms, &bn, &split);
-            r.gemm_tc(s.logits, xf, p.head, s.R, p.head.N, H, EXEC_F32, bn, split, 0);
-        }
+        r.regs.phase = 2;
+        r.regs.logits = s.logits;
+        r.run(p.epilogue);
     }
     s.launches = r.launches;
     if (need) { need[0] = r.arena.peak; need[1] = r.need_gemm_ws; need[2] = r.need_attn_ws; }
@@ -407,5 +489,19 @@ int walk(const ExecProgram& p, ExecStep& s, bool dry, i64* need) {
 int exec_forward(const ExecProgram& p, ExecStep& s) { return walk(p, s, false, nullptr); }
 
 void exec_need(const ExecProgram& p, ExecStep& s, i64* need) { walk(p, s, true, need); }
+
+int exec_part(const ExecProgram& p, ExecStep& s, const ExecOp& op, const void* y_in, void* out, bool dry, i64* need) {
+    Run r{p, s, Arena{static_cast<char*>(s.arena), s.arena_bytes}, p.act_dtype};
+    r.dry = r.arena.dry = dry;
+    s.launches = 0;
+    for (i64& c : s.calls) c = 0;
+    if (s.T > 0) {
+        r.regs.phase = 1;
+        r.produce(op, s.items, y_in, out);
+    }
+    s.launches = r.launches;
+    if (need) { need[0] = r.arena.peak; need[1] = r.need_gemm_ws; need[2] = r.need_attn_ws; }
+    return 0;
+}
 
 }  // namespace cellm

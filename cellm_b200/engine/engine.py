@@ -46,7 +46,7 @@ class Engine:
             raise ValueError(f"the loaded model computes in {self.model.dtype}, the engine was asked for {c.dtype}")
         self.cache = CacheManager(self.model.cache_needs(), [e.cache_of for e in self.plan.order],
                                   c.tokens_per_block, c.total_blocks, c.max_num_seqs, c.dtype, c.device)
-        self.runner = StepRunner(self.model, self.cache, use_graphs=c.use_cuda_graphs, native_steps=c.native_steps)
+        self.runner = StepRunner(self.model, self.cache, use_graphs=c.use_cuda_graphs)
         self.scheduler = Scheduler(self.cache, c.max_batch_tokens, c.prefill_chunk, self.plan.max_positions)
         self._samplers: dict[int, RequestSampler] = {}
         self._outputs: dict[int, RequestOutput] = {}

@@ -11,7 +11,6 @@ portions of a step run as one batch.
 """
 from __future__ import annotations
 
-import os
 from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
@@ -42,23 +41,11 @@ _ERR_BITS = {1: "token id outside the vocabulary", 2: "page id outside the pool"
 
 
 class StepRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager, use_graphs: bool = False,
-                 native_steps: Optional[bool] = None):
-        """`native_steps`: steps that are not replayed as CUDA graphs are launched by the runtime's executor
-        (engine/native_exec.py) where the model consists of parts it knows; others keep the Python parts.
-        None: as the environment says (CELLM_B200_NATIVE_STEPS=1), else off."""
-        if native_steps is None:
-            native_steps = os.environ.get("CELLM_B200_NATIVE_STEPS", "0") == "1"
+    def __init__(self, model: DecoderModel, cache: CacheManager, use_graphs: bool = False):
         self.model, self.cache = model, cache
         self.device = model.device
         self._forward = model.forward
-        self.native_reason = "not asked for"
-        if native_steps:
-            from .native_exec import NativeForward, unsupported
-            self.native_reason = unsupported(model)
-            if self.native_reason is None:
-                self._forward = NativeForward(model).forward
-        from ..ops.gemm_bf16 import error_word
+        from ..ops._state import error_word
         self.err = error_word(self.device)      # one error word for every kernel on this device
         self._pinned = [None, None]
         self._events = [None, None]        # one reusable event per staging buffer: recorded after its upload

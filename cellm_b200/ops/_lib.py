@@ -22,7 +22,7 @@ _SIGNATURES = {
         "cellm_upload": [P, P, L, P],
         "cellm_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P],
         "cellm_residual_add": [P, P, L, I, P],
-        "cellm_swiglu": [P, P, I, I, I, P],
+        "cellm_swiglu": [P, P, I, I, I, I, P],
         "cellm_short_conv": [P, P, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, P, P],
         "cellm_qk_norm_rope": [P, P, L, P, P, I, F, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, I, P, P],
         "cellm_attention_plain": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P],

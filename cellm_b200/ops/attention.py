@@ -6,9 +6,6 @@ from ._lib import check, count_launch, fn, ptr, require_cuda, stream_of
 from .basic import attention_plain
 
 _FLASH_HEAD_SIZES = (32, 64, 128)
-# When prompt portions go to the tcgen05 kernel: at least `min_ctas` CTAs (None: an eighth of the SMs; below that the mma.sync kernel with its split over the keys fills the GPU better)
-# and at least `min_fill` of the tiles' rows in use. Tests lower both to drive small cases there.
-TC_POLICY = {"min_ctas": None, "min_fill": 0.5}
 _WORKSPACE: dict[torch.device, torch.Tensor] = {}
 
 
@@ -21,14 +18,6 @@ def _workspace(device, n_floats: int) -> torch.Tensor:
         ws = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
         _WORKSPACE[device] = ws
     return ws
-
-
-def plan_splits(n_tiles: int, nkv: int, max_total_len: int, sms: int) -> int:
-    """How many CTAs share the keys of one tile: enough to fill the GPU when the
-    batch alone does not, but at least two blocks of 64 keys each."""
-    blocks = (max_total_len + 63) // 64
-    target = (4 * sms + n_tiles * nkv - 1) // (n_tiles * nkv)
-    return max(1, min(target, blocks // 2))
 
 
 def attention_flash(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, cu_seqlens: torch.Tensor,
@@ -76,7 +65,7 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     out = torch.empty_like(q)
     part_o = part_ml = counters = None
     if nsplit > 1:
-        from .gemm_bf16 import MAX_COUNTERS, _counters
+        from ._state import MAX_COUNTERS, counters as _counters
         if B * nkv > MAX_COUNTERS:
             raise ValueError("attention_decode: too many (request, kv head) pairs for the counters")
         rows = T * nh
@@ -121,33 +110,17 @@ def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, cu
 
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, block_table: torch.Tensor,
               nh: int, scale: float, window: int) -> torch.Tensor:
-    """Attention of every token of the step over its request's pages. bfloat16
-    with a head size the tensor-core kernels are built for runs there (decoded
-    tokens in the decode kernel, large batches of prompt tokens with heads of 64
-    on tcgen05, the rest on mma.sync); everything else (32-bit, other head sizes)
-    runs the plain kernel."""
-    hd = k_pool.shape[3]
-    if q.dtype == torch.bfloat16 and hd in _FLASH_HEAD_SIZES and scale > 0:
-        from .gemm_bf16 import _sms
-        G = nh // k_pool.shape[1]
-        if ctx.max_q_len * G <= 16:
-            blocks = (ctx.max_total_len + 63) // 64
-            nsplit = max(1, min(4 * _sms(q.device) // (ctx.B * k_pool.shape[1]), blocks // 4))
-            return attention_decode(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.B, nh, scale,
-                                    window, ctx.err, nsplit)
-        # prompt portions that fill the tcgen05 kernel's pairs of 128-row tiles and enough CTAs
-        if attention_tc_supports(hd, nh, k_pool.shape[1], k_pool.shape[2]):
-            per_tile = 256 // G
-            tc_tiles = sum((n + per_tile - 1) // per_tile for n in ctx.q_lens)
-            min_ctas = _sms(q.device) // 8 if TC_POLICY["min_ctas"] is None else TC_POLICY["min_ctas"]
-            if tc_tiles * k_pool.shape[1] >= min_ctas and ctx.T >= TC_POLICY["min_fill"] * tc_tiles * per_tile:
-                return attention_tc(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.q_lens, nh,
-                                    scale, window, ctx.err)
-        wide = ctx.max_q_len * G > 16
-        bm = 64 if wide else 16
-        n_tiles = sum((n * G + bm - 1) // bm for n in ctx.q_lens)
-        nsplit = plan_splits(n_tiles, k_pool.shape[1], ctx.max_total_len, _sms(q.device))
-        return attention_flash(q, k_pool, v_pool, ctx.cu_seqlens, ctx.ctx_lens, block_table, ctx.q_lens, nh, scale,
-                               window, ctx.err, nsplit, wide)
-    return attention_plain(q, k_pool, v_pool, ctx.positions, ctx.seq_of_token, block_table, nh, scale,
-                           window, ctx.err)
+    """Attention of every token of the step over its request's pages, by the kernel the native executor chooses:
+    bfloat16 with a head size the tensor-core kernels are built for runs there (decoded tokens in the decode
+    kernel, large batches of prompt tokens with heads of 64 on tcgen05, the rest on mma.sync); everything else
+    (32-bit, other head sizes) runs the plain kernel. q [T, nh * hd] (normed, turned) -> [T, nh * hd]."""
+    from ..parts.base import CacheBinding
+    from ..runtime import records as R
+    from ..runtime.program import part_program
+    pages, nkv, page_size, hd = k_pool.shape
+    p = R.AttentionParams()
+    p.nh, p.nkv, p.hd, p.window, p.scale = nh, nkv, hd, int(window), float(scale)
+    out = torch.empty_like(q)
+    binding = CacheBinding(k=k_pool, v=v_pool, block_table=block_table, page_size=page_size, num_pages=pages)
+    part_program(q.dtype, q.device, q.shape[1]).run_part(R.Record(R.ATTEND, p), q, ctx, binding, out=out)
+    return out

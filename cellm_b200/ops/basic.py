@@ -53,12 +53,13 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
     check(fn(_LIB, "cellm_residual_add")(ptr(x), ptr(delta), x.numel(), tag(delta), stream_of(x)), "residual_add")
 
 
-def swiglu(gu: torch.Tensor) -> torch.Tensor:
-    """gu [T, 2*ff] = [gate | up] -> silu(gate) * up [T, ff]."""
+def swiglu(gu: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """gu [T, 2*ff] = [gate | up] -> silu(gate) * up [T, ff] of `out_dtype` (default: gu's; float32 gate and up
+    may give a bfloat16 result)."""
     require_cuda(gu)
     T, two_ff = gu.shape
-    h = torch.empty((T, two_ff // 2), dtype=gu.dtype, device=gu.device)
-    check(fn(_LIB, "cellm_swiglu")(ptr(h), ptr(gu), T, two_ff // 2, tag(gu), stream_of(gu)), "swiglu")
+    h = torch.empty((T, two_ff // 2), dtype=out_dtype or gu.dtype, device=gu.device)
+    check(fn(_LIB, "cellm_swiglu")(ptr(h), ptr(gu), T, two_ff // 2, tag(h), tag(gu), stream_of(gu)), "swiglu")
     return h
 
 

@@ -20,12 +20,21 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None =
     return c
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-         w_is_static: bool = False) -> torch.Tensor:
-    """The product a . w^T by the kernel that serves the operands' element type:
-    32-bit operands run the plain 32-bit kernel; bfloat16 operands run the
-    tensor-core kernels."""
-    if a.dtype == torch.float32:
-        return gemm_plain(a, w, out_dtype)
-    from .gemm_bf16 import gemm_bf16
-    return gemm_bf16(a, w, out_dtype, w_is_static)
+def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """The product a [M, K] . w [N, K]^T by the kernel the native executor chooses for the operands: 32-bit
+    operands run the plain 32-bit kernel; bfloat16 operands run the tensor-core kernel in the tile shape and K
+    split that fit M, N and K (or the plain kernel where K or the rows' alignment do not fit it). `w` is taken
+    for a weight that nothing on the stream writes."""
+    from ..runtime import records as R
+    from ..runtime.program import part_program
+    if a.dtype != w.dtype or a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1] or a.stride(1) != 1 or w.stride(1) != 1:
+        raise ValueError(f"gemm: a {tuple(a.shape)} {a.dtype} and w {tuple(w.shape)} {w.dtype} do not fit")
+    out_dtype = out_dtype or a.dtype
+    c = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype, device=a.device)
+    if a.shape[0] == 0:
+        return c
+    rec = R.Record(R.LINEAR, R.LinearParams(R.linear(w), a.stride(0), tag(out_dtype)))
+    if a.data_ptr() % 16:
+        rec.params.w.tc_ok = 0
+    part_program(a.dtype, a.device, a.shape[1]).run_part(rec, a, None, out=c, rows=a.shape[0])
+    return c

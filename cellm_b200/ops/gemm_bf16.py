@@ -3,27 +3,15 @@ tile shape and K split for the sizes at hand."""
 from __future__ import annotations
 
 import functools
-import os
 
 import torch
 
 from ._lib import check, count_launch, fn, ptr, stream_of, tag
 from .gemm import gemm_plain
 
-_SM_COUNT: dict[int, int] = {}
+from ._state import MAX_COUNTERS, STATIC_WEIGHTS_FLAG as _STATIC_FLAG, counters as _counters, error_word, sm_count as _sms
+
 _WORKSPACE: dict[torch.device, torch.Tensor] = {}
-_COUNTERS: dict[torch.device, torch.Tensor] = {}
-_ERR: dict[torch.device, torch.Tensor] = {}
-MAX_COUNTERS = 65536
-_STATIC_FLAG = max(1, int(os.environ.get("CELLM_B200_L2_PREFETCH_BLOCKS", "1")))
-_CLUSTER_REDUCE = os.environ.get("CELLM_B200_CLUSTER_REDUCE", "1") != "0"
-
-
-def _sms(device) -> int:
-    i = torch.device(device).index or 0
-    if i not in _SM_COUNT:
-        _SM_COUNT[i] = torch.cuda.get_device_properties(i).multi_processor_count
-    return _SM_COUNT[i]
 
 
 def _workspace(device, n_floats: int) -> torch.Tensor:
@@ -37,66 +25,12 @@ def _workspace(device, n_floats: int) -> torch.Tensor:
     return ws
 
 
-def _counters(device) -> torch.Tensor:
-    """Tile counters of split products: zero between products, shared by all
-    products of one stream (each leaves them zero), never reallocated."""
-    c = _COUNTERS.get(device)
-    if c is None:
-        c = torch.zeros(MAX_COUNTERS, dtype=torch.int32, device=device)
-        _COUNTERS[device] = c
-    return c
-
-
-def error_word(device) -> torch.Tensor:
-    """The device error word the kernels report a bad index or a timed-out wait in."""
-    device = torch.device(device)
-    e = _ERR.get(device)
-    if e is None:
-        e = torch.zeros(1, dtype=torch.int32, device=device)
-        _ERR[device] = e
-    return e
-
-
 @functools.lru_cache(maxsize=4096)
 def plan_tiles(M: int, N: int, K: int, sms: int) -> tuple[int, int]:
-    """(bn, split_k) for a product of these sizes: bn > 0 plain tiles of 128 x bn,
-    bn < 0 swapped tiles of 128 weight rows x -bn tokens."""
-    kblocks = (K + 63) // 64
-    if M <= 64:
-        narrow = 16 if M <= 16 else (32 if M <= 32 else 64)
-        tiles = (N + 127) // 128
-        # Enough CTAs to fill the SMs, and no CTA with much more than ~300 KB of weights to
-        # stream by itself; at most 8 (the split of a tile is one thread-block cluster) and
-        # at least four K blocks each. Products with tiles to spare are not split.
-        if tiles >= 2 * sms:
-            split = 1
-        else:
-            fill = -(-(sms * 85 // 100) // tiles)
-            stream = -(-(128 * K * 2) // (300 * 1024))
-            split = max(1, min(max(fill, stream), kblocks // 4, 8))
-        return -narrow, split
-    bn = 256 if N >= 256 else (128 if N > 64 else 64)
-    if bn == 256:
-        # 128-wide tiles cost about 0.55 of a 256-wide one; take them when their waves finish sooner
-        mt = (M + 127) // 128
-        waves256 = -(-(mt * ((N + 255) // 256)) // sms)
-        waves128 = -(-(mt * ((N + 127) // 128)) // sms)
-        if waves128 * 0.55 < waves256 * 0.95:
-            bn = 128
-    tiles = ((N + bn - 1) // bn) * ((M + 127) // 128)
-    if tiles < sms // 2:
-        # Too few plain tiles to fill the GPU (a few hundred tokens, or a narrow product).
-        if M <= 128:
-            # up to two token tiles: swapped tiles of 128 weight rows by 64 tokens, the K split summed in a cluster
-            stiles = ((N + 127) // 128) * ((M + 63) // 64)
-            split = 1 if stiles >= sms * 85 // 100 else max(1, min(-(-(sms * 85 // 100) // stiles), kblocks // 4, 8))
-            return -64, split
-        # more tokens: tiles of 128 x 128 with K split until the SMs are filled; the pieces go through the
-        # workspace and a second kernel sums them (measured at 512 tokens: 23 us against 29 us for swapped tiles)
-        bn = 128 if N > 64 else 64
-        tiles = ((N + bn - 1) // bn) * ((M + 127) // 128)
-        return bn, max(1, min(-(-(sms * 85 // 100) // tiles), kblocks // 4, 16))
-    return bn, 1
+    """(bn, split_k) for a product of these sizes, as the native executor plans it: bn > 0 plain tiles of
+    128 x bn, bn < 0 swapped tiles of 128 weight rows x -bn tokens."""
+    from ..runtime.program import plan_tiles as planned
+    return planned(M, N, K, sms)
 
 
 @functools.lru_cache(maxsize=4096)
@@ -118,7 +52,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bn: i
     split = _effective_split(K, split_k)
     # swapped tiles whose K split is one thread-block cluster (2..8 CTAs) sum their pieces
     # through shared memory: no workspace, no counters
-    in_cluster = bn < 0 and _CLUSTER_REDUCE and (2 <= split <= 8 or (split == 1 and epilogue == 1))
+    in_cluster = bn < 0 and (2 <= split <= 8 or (split == 1 and epilogue == 1))
     through_ws = not in_cluster and (split > 1 or (epilogue == 1 and bn < 0))
     ws = _workspace(a.device, split * M * N) if through_ws else None
     # plain tiles leave the sum of their K-split pieces to a second kernel (no counters); swapped tiles outside a
@@ -138,19 +72,6 @@ def tensor_core_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
     K = a.shape[1]
     return not ((K % 8) or a.stride(1) != 1 or w.stride(1) != 1 or (a.stride(0) % 8) or (w.stride(0) % 8)
                 or (a.data_ptr() % 16) or (w.data_ptr() % 16))
-
-
-def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-              w_is_static: bool = False) -> torch.Tensor:
-    """a [M, K] . w [N, K]^T for bfloat16 operands, 32-bit accumulation, output
-    bfloat16 or float32. Sizes the tensor-core kernel does not take (K not a
-    multiple of 8, unaligned rows) go to the plain kernel. `w_is_static`: w is a
-    weight that nothing on the stream writes (its loads may then start early)."""
-    out_dtype = out_dtype or a.dtype
-    if not tensor_core_ok(a, w):
-        return gemm_plain(a, w, out_dtype)
-    bn, split = plan_tiles(a.shape[0], w.shape[0], a.shape[1], _sms(a.device))
-    return gemm_tcgen05(a, w, out_dtype, bn, split, w_is_static=w_is_static)
 
 
 def gemm_swiglu_bf16(a: torch.Tensor, w_blocked: torch.Tensor, w_is_static: bool = False) -> torch.Tensor:
@@ -185,8 +106,6 @@ def tile_in_proj_for_conv(in_proj: torch.Tensor) -> torch.Tensor:
 def gemm_conv_plan(M: int, H: int, K: int, device) -> tuple[int, int] | None:
     """(bn, split_k) for the product with the convolution in its epilogue, or None if these
     sizes do not run it (it needs swapped tiles whose K split is one cluster)."""
-    if not _CLUSTER_REDUCE:
-        return None
     tiles = (H + CONV_TILE_CHANNELS - 1) // CONV_TILE_CHANNELS
     bn, split = plan_tiles(M, tiles * 128, K, _sms(device))
     if bn >= 0 or (M + -bn - 1) // -bn != 1 or _effective_split(K, split) > 8:
@@ -220,7 +139,7 @@ def gemm_conv_bf16(a: torch.Tensor, w_tiled: torch.Tensor, H: int, taps: torch.T
 def gemm_rope_plan(M: int, nh: int, nkv: int, hd: int, K: int, device) -> tuple[int, int] | None:
     """(bn, split_k) for the q/k/v product with norm, rotation and cache write in its epilogue, or
     None if these sizes do not run it (heads of 64; swapped tiles whose K split is one cluster)."""
-    if not _CLUSTER_REDUCE or hd != 64:
+    if hd != 64:
         return None
     bn, split = plan_tiles(M, (nh + 2 * nkv) * hd, K, _sms(device))
     if bn >= 0 or (M + -bn - 1) // -bn != 1 or _effective_split(K, split) > 8:

@@ -4,11 +4,8 @@ q and k head, position encoding, keys and values written to the request's
 pages, softmax(q.k * scale) over all earlier keys (or a window), out_proj."""
 from __future__ import annotations
 
-import os
-
 import torch
 
-from .. import ops
 from ..config.errors import ConfigError
 from ..config.plan import PartSpec
 from .base import CacheBinding, Mixer, PagedKV, StepContext, TensorSpec
@@ -41,6 +38,7 @@ class AttentionMixer(Mixer):
         return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), int(params.get("window", 0)))
 
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        self.H = int(params["hidden_size"])
         self.nh, self.nkv, self.hd = int(params["num_heads"]), int(params["num_kv_heads"]), int(params["head_dim"])
         if self.nh % self.nkv:
             raise ConfigError(f"attention: {self.nh} heads are not a multiple of {self.nkv} key/value heads")
@@ -56,43 +54,61 @@ class AttentionMixer(Mixer):
         self.norm_eps = 0.0
         if qk is not None:
             if qk.kind != "rms_norm":
-                raise ConfigError(f"attention: head norm of kind {qk.kind!r}; the fused kernel takes 'rms_norm'")
+                raise ConfigError(f"attention: head norm of kind {qk.kind!r}; the kernels take 'rms_norm'")
             self.norm_eps = float(qk.params["eps"])
             self.q_norm_w = weights["q_norm"].contiguous()
             self.k_norm_w = weights["k_norm"].to(self.q_norm_w.dtype).contiguous()
         pos: PartSpec | None = params.get("position")
         self.position = part_class("position", pos.kind)(pos.params, dev) if pos is not None else None
+        self._record = self._attend = None
 
-    def _fused_rope_ok(self, x, ctx, cache, rot) -> bool:
-        """One token per request, bfloat16 throughout, heads of 64 turned whole in the "half" layout, own cache.
-        Asked for with CELLM_B200_FUSED_ROPE=1: the kernel is tested, its effect on a step's time is not measured yet."""
-        bf = torch.bfloat16
-        return (ctx.max_q_len == 1 and cache.writes and self.hd == 64 and x.dtype == bf and self.qkv.weight.dtype == bf
-                and self.q_norm_w is not None and self.q_norm_w.dtype == bf and rot is not None
-                and rot[0] == 64 and not rot[1] and cache.k.dtype == bf
-                and os.environ.get("CELLM_B200_FUSED_ROPE", "0") == "1" and ops.tensor_core_ok(x, self.qkv.weight))
+    def record(self):
+        """The part as an op record of the native executor. None if its matrices are kept in another element type
+        than the activations, or if its position encoding is no rotation the kernels apply (forward() then runs
+        the head norms, the encoding's own apply() and the cache write as separate steps)."""
+        from ..ops._lib import tag
+        from ..runtime import records as R
+        rot = self.position.rotation() if self.position is not None else (0, False, None)
+        if self._record is None and rot is not None and self.qkv.weight.dtype == self.dtype == self.out_proj.weight.dtype:
+            p = self._attend_params()
+            p.qkv, p.out_proj = R.linear(self.qkv.weight), R.linear(self.out_proj.weight)
+            if self.q_norm_w is not None:
+                p.q_norm_w, p.k_norm_w = self.q_norm_w.data_ptr(), self.k_norm_w.data_ptr()
+                p.qk_dtype, p.qk_eps = tag(self.q_norm_w), self.norm_eps
+            p.rot, p.interleaved, p.inv_freq = int(rot[0]), int(rot[1]), R.ptr(rot[2])
+            self._record = R.Record(R.ATTENTION, p, keep=[rot[2]], part=self)
+        return self._record
+
+    def _attend_params(self):
+        from ..runtime import records as R
+        p = R.AttentionParams()
+        p.nh, p.nkv, p.hd, p.window, p.scale = self.nh, self.nkv, self.hd, self.window, self.scale
+        return p
+
+    def emit(self, emitter) -> None:
+        rec = self.record()
+        if rec is None:
+            return super().emit(emitter)
+        emitter.records.append(rec)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        from .. import ops
+        from ..runtime import records as R
+        from ..runtime.program import part_program
+        rec = self.record()
+        if rec is not None:
+            return part_program(self.dtype, x.device, self.H).run_part(rec, x, ctx, cache)
         nh, nkv, hd = self.nh, (self.nkv if cache.writes else 0), self.hd
-        rot = self.position.rotation() if self.position is not None else (0, False, None)
         bt, kp, vp = (cache.block_table, cache.k, cache.v) if nkv else (None, None, None)
-        if self._fused_rope_ok(x, ctx, cache, rot):
-            # decode steps: the product, the heads' norm, the rotation and the cache write as one kernel
-            from ..ops import gemm_bf16 as tc
-            plan = tc.gemm_rope_plan(ctx.T, nh, nkv, hd, x.shape[1], x.device)
-            if plan is not None:
-                q = tc.gemm_rope_bf16(x, self.qkv.weight, self.q_norm_w, self.k_norm_w, self.norm_eps, ctx.positions,
-                                      bt, kp, vp, nh, nkv, rot[2], plan, ctx.err)
-                o = ops.attention(q, cache.k, cache.v, ctx, cache.block_table, nh, self.scale, self.window)
-                return self.out_proj(o)
         qkv = self.qkv(x) if cache.writes else self.q_only(x)
+        rot = self.position.rotation() if self.position is not None else (0, False, None)
         if rot is not None:
             rotary_dim, interleaved, inv_freq = rot
             q = ops.qk_norm_rope(qkv, self.q_norm_w, self.k_norm_w, self.norm_eps, ctx.positions,
                                  ctx.seq_of_token, bt, kp, vp, cache.page_size, nh, nkv, hd, rotary_dim,
                                  interleaved, inv_freq, ctx.err)
         else:
-            # A position encoding that is no rotation the fused kernel knows: head norms,
+            # A position encoding that is no rotation the kernels know: head norms,
             # the part's own apply(), then the write into the pages, as three steps.
             q = ops.qk_norm_rope(qkv[:, :nh * hd], self.q_norm_w, self.q_norm_w, self.norm_eps, ctx.positions,
                                  ctx.seq_of_token, None, None, None, cache.page_size, nh, 0, hd, 0, False,
@@ -108,7 +124,11 @@ class AttentionMixer(Mixer):
                 kv = torch.cat([k.reshape(-1, nkv * hd), qkv[:, (nh + nkv) * hd:]], dim=1).contiguous()
                 ops.qk_norm_rope(kv, None, None, 0.0, ctx.positions, ctx.seq_of_token, bt, kp, vp,
                                  cache.page_size, 0, nkv, hd, 0, False, None, ctx.err)
-        o = ops.attention(q, cache.k, cache.v, ctx, cache.block_table, nh, self.scale, self.window)
+        # the attention itself by the executor's choice of kernel
+        if self._attend is None:
+            self._attend = R.Record(R.ATTEND, self._attend_params(), part=self)
+        o = torch.empty_like(q)
+        part_program(q.dtype, q.device, self.H).run_part(self._attend, q, ctx, cache, out=o)
         return self.out_proj(o)
 
 

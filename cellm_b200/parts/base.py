@@ -3,14 +3,23 @@
 A part is built from its own parameters (`PartSpec.params`) and the tensors
 the loader found for it. It never sees the model's configuration or name.
 
+  Embedding       forward(token_ids, ctx) -> the 32-bit residual stream [T, hidden]
   Norm            forward(residual) -> normed activations
   Position        rotation(...) describes itself to a fused kernel, or apply(q, k, positions)
   Mixer           forward(x, ctx, cache) -> [T, hidden]; declares what cache it needs
   FeedForward     forward(x, ctx) -> [T, hidden]
   Block           forward(residual, ctx, cache): the arrangement of the above in a layer
+  Head            forward(x) -> float32 logits [rows, vocab]
 
 `weight_specs(params)` lists the tensors a part reads, with the shape each
 must have in the file and the class of values a random model gives it.
+
+`emit(emitter)` describes the part to the native executor
+(cellm_b200/runtime): a built-in part appends its own op record
+(`emitter.native(kind, params)`), and the defaults below append a Python
+record, for which the executor calls the part's forward() on its registers. So
+a part defined outside the package needs forward() only, and runs between
+native parts without slowing them.
 """
 from __future__ import annotations
 
@@ -128,7 +137,28 @@ class Part:
         return {}
 
 
+class Embedding(Part):
+    def forward(self, token_ids: torch.Tensor, ctx: "StepContext") -> torch.Tensor:
+        """The start of the residual stream: float32 [T, hidden]."""
+        raise NotImplementedError
+
+    def emit(self, emitter) -> None:
+        emitter.python("embedding", self)
+
+
+class Head(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """float32 logits [rows, vocab] of the normed rows x [rows, hidden]."""
+        raise NotImplementedError
+
+    def emit(self, emitter) -> None:
+        emitter.python("head", self)
+
+
 class Norm(Part):
+    def emit(self, emitter) -> None:
+        emitter.python("norm", self)
+
     def forward(self, residual: Residual, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Adds the pending addend into the stream and returns the normed rows
         (all rows, or the given row indices without touching the stream)."""
@@ -157,12 +187,21 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         raise NotImplementedError
 
+    def emit(self, emitter) -> None:
+        emitter.python("mixer", self)
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
+    def emit(self, emitter) -> None:
+        emitter.python("feed_forward", self)
+
 
 class Block(Part):
     def forward(self, residual: Residual, ctx: StepContext, cache: CacheBinding) -> None:
         raise NotImplementedError
+
+    def emit(self, emitter) -> None:
+        emitter.python("block", self)

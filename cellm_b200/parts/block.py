@@ -13,6 +13,11 @@ class PreNormBlock(Block):
         self.mixer_norm, self.mixer = mixer_norm, mixer
         self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
 
+    def emit(self, emitter) -> None:
+        """The layer as records: each of the four parts emits its own, in the order they run."""
+        for part in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward):
+            part.emit(emitter)
+
     def forward(self, residual: Residual, ctx: StepContext, cache: CacheBinding) -> None:
         residual.add(self.mixer.forward(self.mixer_norm.forward(residual), ctx, cache))
         residual.add(self.feed_forward.forward(self.feed_forward_norm.forward(residual), ctx))

@@ -16,7 +16,7 @@ class Linear:
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         out_dtype = out_dtype or self.act_dtype
         if self.weight.dtype == x.dtype:
-            return ops.gemm(x, self.weight, out_dtype, w_is_static=True)
+            return ops.gemm(x, self.weight, out_dtype)
         # A matrix kept in 32-bit under bfloat16 activations runs the 32-bit product.
         y = ops.gemm(x.to(self.weight.dtype), self.weight, torch.float32)
         return y if out_dtype == torch.float32 else y.to(out_dtype)

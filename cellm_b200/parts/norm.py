@@ -26,6 +26,11 @@ class RMSNorm(Norm):
         self.weight = weights["weight"].contiguous()
         self.dtype = dtype
 
+    def emit(self, emitter) -> None:
+        from ..ops._lib import tag
+        from ..runtime import records as R
+        emitter.native(R.RMS_NORM, R.RmsNormParams(self.weight.data_ptr(), tag(self.weight), self.eps), part=self)
+
     def forward(self, residual: Residual, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         delta, residual.pending = residual.pending, None
         y = ops.add_rmsnorm(residual.x, delta, self.weight, self.eps, self.dtype, rows)

@@ -1,11 +1,12 @@
 """Registries of part kinds. A new mixer, feed-forward, norm, position
-encoding or block arrangement is one class and one `register_*` call; nothing
+encoding, block arrangement, embedding or head is one class and one `register_*` call; nothing
 else in the package names the kinds."""
 from __future__ import annotations
 
 from ..config.errors import ConfigError
 
-_REGISTRIES: dict[str, dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}
+_REGISTRIES: dict[str, dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+                                           "embedding": {}, "head": {}}
 
 
 def _register(family: str, kind: str, cls: type) -> type:
@@ -19,6 +20,8 @@ def register_feed_forward(kind, cls): return _register("feed_forward", kind, cls
 def register_norm(kind, cls): return _register("norm", kind, cls)
 def register_position(kind, cls): return _register("position", kind, cls)
 def register_block(kind, cls): return _register("block", kind, cls)
+def register_embedding(kind, cls): return _register("embedding", kind, cls)
+def register_head(kind, cls): return _register("head", kind, cls)
 
 
 def part_class(family: str, kind: str) -> type:

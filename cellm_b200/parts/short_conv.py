@@ -4,11 +4,8 @@ values of B*x, times C, out_proj. Its per-request state is the last taps-1
 values of B*x, in a slot of fixed size."""
 from __future__ import annotations
 
-import os
-
 import torch
 
-from .. import ops
 from ..config.errors import ConfigError
 from .base import CacheBinding, FixedState, Mixer, StepContext, TensorSpec
 from .linear import Linear
@@ -35,7 +32,7 @@ class ShortConvMixer(Mixer):
         return FixedState((max(int(params["taps"]) - 1, 0), int(params["hidden_size"])), torch.float32)
 
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
-        self.H, self.taps = int(params["hidden_size"]), int(params["taps"])
+        self.H, self.taps, self.dtype = int(params["hidden_size"]), int(params["taps"]), dtype
         if not 1 <= self.taps <= 16:
             raise ConfigError(f"short_conv: {self.taps} taps; the kernel takes 1 to 16")
         self.in_proj = Linear(weights["in_proj"], dtype)
@@ -50,18 +47,36 @@ class ShortConvMixer(Mixer):
         self.in_proj_tiled = None
         w = self.in_proj.weight
         if (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and self.conv_w.dtype == torch.bfloat16
-                and self.taps <= tc.CONV_MAX_TAPS and self.H % 8 == 0 and w.is_cuda
-                and os.environ.get("CELLM_B200_FUSED_CONV", "1") != "0"):
+                and self.taps <= tc.CONV_MAX_TAPS and self.H % 8 == 0):
             self.in_proj_tiled = tc.tile_in_proj_for_conv(w)
+        self._record = None
+
+    def record(self):
+        """The part as an op record of the native executor (None: its matrices are kept in another element type
+        than the activations)."""
+        from ..ops._lib import tag
+        from ..runtime import records as R
+        if self._record is None and self.in_proj.weight.dtype == self.dtype == self.out_proj.weight.dtype:
+            p = R.ShortConvParams(R.linear(self.in_proj.weight), R.linear(self.out_proj.weight))
+            if self.in_proj_tiled is not None:
+                p.in_proj_tiled, p.tiled_rows = self.in_proj_tiled.data_ptr(), self.in_proj_tiled.shape[0]
+            p.taps, p.bias = self.conv_w.data_ptr(), R.ptr(self.conv_b)
+            p.taps_dtype, p.n_taps = tag(self.conv_w), self.taps
+            self._record = R.Record(R.SHORT_CONV, p, part=self)
+        return self._record
+
+    def emit(self, emitter) -> None:
+        rec = self.record()
+        if rec is None:
+            return super().emit(emitter)
+        emitter.records.append(rec)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
-        if self.in_proj_tiled is not None and ctx.max_q_len == 1 and x.dtype == torch.bfloat16:
-            from ..ops import gemm_bf16 as tc
-            plan = tc.gemm_conv_plan(ctx.T, self.H, x.shape[1], x.device) if tc.tensor_core_ok(x, self.in_proj_tiled) else None
-            if plan is not None:
-                y = tc.gemm_conv_bf16(x, self.in_proj_tiled, self.H, self.conv_w, self.conv_b, cache.state, ctx.slot_ids,
-                                      plan, ctx.err)
-                return self.out_proj(y)
+        from .. import ops
+        from ..runtime.program import part_program
+        rec = self.record()
+        if rec is not None:
+            return part_program(self.dtype, x.device, self.H).run_part(rec, x, ctx, cache)
         bcx = self.in_proj(x)
         y = ops.short_conv(bcx, self.conv_w, self.conv_b, cache.state, ctx.slot_ids, ctx.seq_of_token,
                            ctx.cu_seqlens, ctx.err, ctx.max_q_len)

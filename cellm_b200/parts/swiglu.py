@@ -5,7 +5,6 @@ from __future__ import annotations
 
 import torch
 
-from .. import ops
 from .base import FeedForward, StepContext, TensorSpec
 from .linear import Linear, stack_rows
 from .registry import register_feed_forward
@@ -27,6 +26,7 @@ class SwiGLU(FeedForward):
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
         w1, w3 = weights["w1"], weights["w3"]
         ff, H = w1.shape
+        self.ff, self.H, self.dtype = ff, H, dtype
         # bfloat16 with a width that is a multiple of 64: gate and up rows are
         # interleaved block by block, so that the product's epilogue has a gate and
         # its up side by side and applies silu(g) * u before anything is stored.
@@ -39,13 +39,32 @@ class SwiGLU(FeedForward):
         else:
             self.gate_up = Linear(stack_rows(w1, w3), dtype)
         self.down = Linear(weights["w2"], dtype)
+        self._record = None
+
+    def record(self):
+        """The part as an op record of the native executor (None: its weights do not fit the activations'
+        element type, and forward() below runs it kernel by kernel)."""
+        from ..runtime import records as R
+        if self._record is None and self.gate_up.weight.dtype == self.dtype == self.down.weight.dtype:
+            self._record = R.Record(R.SWIGLU, R.SwiGLUParams(R.linear(self.gate_up.weight), R.linear(self.down.weight),
+                                                             self.ff, int(self.fused)), part=self)
+        return self._record
+
+    def emit(self, emitter) -> None:
+        rec = self.record()
+        if rec is None:
+            return super().emit(emitter)
+        emitter.records.append(rec)
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        if self.fused and x.dtype == torch.bfloat16 and ops.tensor_core_ok(x, self.gate_up.weight):
-            return self.down(ops.gemm_swiglu_bf16(x, self.gate_up.weight, w_is_static=True))
-        if self.fused:
-            raise ValueError("swiglu: activations do not fit the fused kernel (bfloat16, 16-byte aligned rows)")
-        return self.down(ops.swiglu(self.gate_up(x)))
+        from .. import ops
+        from ..runtime.program import part_program
+        rec = self.record()
+        if rec is not None:
+            return part_program(self.dtype, x.device, self.H).run_part(rec, x, ctx)
+        # matrices kept in another element type than the activations: product, gate, product
+        gu = self.gate_up(x, out_dtype=torch.float32)
+        return self.down(ops.swiglu(gu, self.dtype))
 
 
 register_feed_forward("swiglu", SwiGLU)

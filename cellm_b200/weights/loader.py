@@ -34,16 +34,18 @@ def _part_tensors(family: str, spec: PartSpec, out: dict[str, TensorSpec]) -> No
             if ts.optional:
                 continue
             raise WeightError(f"plan error: part {spec.kind!r} has no file tensor for its weight {local!r}")
-        if name in out and out[name].shape != ts.shape:
-            raise WeightError(f"plan error: tensor {name!r} is used with shapes {out[name].shape} and {ts.shape}")
+        if name in out:
+            if out[name].shape != ts.shape:
+                raise WeightError(f"plan error: tensor {name!r} is used with shapes {out[name].shape} and {ts.shape}")
+            continue        # a tensor two parts share (a tied head) keeps the first part's description
         out[name] = ts
 
 
 def expected_tensors(plan: ModelPlan) -> dict[str, TensorSpec]:
     """File tensor name -> shape and value class, for every tensor the model reads."""
-    out: dict[str, TensorSpec] = {plan.embedding: TensorSpec((plan.vocab_size, plan.hidden_size), "embedding")}
-    if plan.head is not None:
-        out[plan.head] = TensorSpec((plan.vocab_size, plan.hidden_size), "linear")
+    out: dict[str, TensorSpec] = {}
+    _part_tensors("embedding", plan.embedding, out)
+    _part_tensors("head", plan.head, out)
     _part_tensors("norm", plan.final_norm, out)
     for layer in plan.layers:
         _part_tensors("norm", layer.mixer_norm, out)

@@ -10,18 +10,19 @@ import torch
 class Recorder:
     def __init__(self, monkeypatch, sms: int = 148, hooks: dict | None = None):
         """Patches (through `monkeypatch`, so that everything is put back) the look-up of the compiled
-        entry points, the checks that operands lie on a GPU, the stream and SM queries. `hooks`: entry point
-        name -> function of its arguments, run in the kernel's place (to leave something in an output)."""
+        entry points, by the Python wrappers and by the native executor alike, the checks that operands lie on a
+        GPU, the stream and SM queries. `hooks`: entry point name -> function of its arguments, run in the
+        kernel's place (to leave something in an output)."""
+        import ctypes
         self.hooks = hooks = dict(hooks or {})
-        from cellm_b200.ops import _lib, basic, gemm_bf16
+        from cellm_b200.ops import _lib, _state, basic, gemm_bf16
+        from cellm_b200.runtime import program, records
         gemm = importlib.import_module("cellm_b200.ops.gemm")
         attention = importlib.import_module("cellm_b200.ops.attention")
-        self.calls: list[tuple[str, dict]] = []
+        self.calls: list[tuple[str, tuple]] = []
         sigs = _lib._SIGNATURES
 
-        def fn(library, name):
-            sig = sigs[library][name]
-
+        def stand_in(name, sig):
             def call(*args):
                 assert len(args) == len(sig), f"{name}: {len(args)} arguments for a signature of {len(sig)}"
                 self.calls.append((name, args))
@@ -29,12 +30,22 @@ class Recorder:
                     hooks[name](*args)
                 return 0
             return call
+
+        def fn(library, name):
+            return stand_in(name, sigs[library][name])
         for m in (_lib, basic, gemm, gemm_bf16, attention):
             for attr, value in (("fn", fn), ("require_cuda", lambda *a: None), ("stream_of", lambda t: 0)):
                 if hasattr(m, attr):
                     monkeypatch.setattr(m, attr, value)
+        # the executor's table of entry points: C call-backs into the same recorders
+        self._thunks = [ctypes.CFUNCTYPE(ctypes.c_int, *sigs[library][name])(stand_in(name, sigs[library][name]))
+                        for library, name in records.ENTRY_POINTS]
+        self.entries = [ctypes.cast(t, ctypes.c_void_p).value for t in self._thunks]
+        monkeypatch.setattr(program, "entry_points", lambda dtype: self.entries)
+        monkeypatch.setattr(program, "sm_count", lambda device: sms)
+        monkeypatch.setattr(program, "_BARE", {})
         monkeypatch.setattr(gemm_bf16, "_sms", lambda device: sms)
-        monkeypatch.setitem(gemm_bf16._ERR, torch.device("cpu"), torch.zeros(1, dtype=torch.int32))
+        monkeypatch.setitem(_state._ERR, torch.device("cpu"), torch.zeros(1, dtype=torch.int32))
         monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
         monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True), raising=False)
         gemm_bf16.plan_tiles.cache_clear()
@@ -62,7 +73,7 @@ class Step:
 
     def __init__(self, model, plan, q_lens, ctx_lens, page: int = 16):
         from cellm_b200.cache.manager import CacheManager
-        from cellm_b200.ops.gemm_bf16 import error_word       # the engine's steps carry the device's one error word
+        from cellm_b200.ops._state import error_word           # the engine's steps carry the device's one error word
         from cellm_b200.parts.base import StepContext
         B, T = len(q_lens), sum(q_lens)
         width = max((c + q + page - 1) // page for c, q in zip(ctx_lens, q_lens)) + 1
@@ -135,7 +146,7 @@ class Names:
             scan(b, f"L{i}")
         scan(model.final_norm, "final_norm")
         scan(model.head, "head")
-        self.add("embedding", model.embedding)
+        scan(model.embedding, "embedding")
 
     def of(self, address):
         if not address:

@@ -67,11 +67,11 @@ def test_bad_configs_are_refused_with_the_key_named(change, needle):
 def test_registry_resolves_by_architecture_then_model_type():
     assert "Lfm2ForCausalLM" in registered_architectures()
     cfg, plan = config_from_dict(TINY_A)
-    assert isinstance(cfg, Lfm2Config) and len(plan.layers) == 4 and plan.head is None
+    assert isinstance(cfg, Lfm2Config) and len(plan.layers) == 4 and plan.tied
     d = dict(TINY_B)
     d.pop("architectures")
     cfg, plan = config_from_dict(dict(d, model_type="lfm"))
-    assert plan.head == "lm_head.weight"
+    assert plan.head.weights == {"weight": "lm_head.weight"} and not plan.tied
     with pytest.raises(ConfigError) as e:
         config_from_dict(dict(TINY_A, architectures=["LlamaForCausalLM"], model_type="llama"))
     assert "LlamaForCausalLM" in str(e.value) and "Lfm2ForCausalLM" in str(e.value)

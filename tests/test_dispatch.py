@@ -24,14 +24,16 @@ def test_decode_step(monkeypatch):
         "cellm_embed",
         "cellm_add_rmsnorm", "cellm_gemm_conv_tcgen05", "cellm_gemm_tcgen05",                     # conv mixer: in_proj + conv, out_proj
         "cellm_add_rmsnorm", "cellm_gemm_tcgen05", "cellm_gemm_tcgen05",                          # feed-forward: w1|w3 + SwiGLU, w2
-        "cellm_add_rmsnorm", "cellm_gemm_tcgen05", "cellm_qk_norm_rope", "cellm_attention_decode", "cellm_gemm_tcgen05",
+        "cellm_add_rmsnorm", "cellm_gemm_rope_tcgen05", "cellm_attention_decode", "cellm_gemm_tcgen05",     # q/k/v + norm + rotation + cache write
         "cellm_add_rmsnorm", "cellm_gemm_tcgen05", "cellm_gemm_tcgen05",
         "cellm_add_rmsnorm", "cellm_gemm_tcgen05"]                                                # final norm on the wanted rows, head
     gemms = rec.of("cellm_gemm_tcgen05")
-    assert [(g[G_M], g[G_N], g[G_K]) for g in gemms] == [(8, H, H), (8, 2 * FF, H), (8, H, FF), (8, 3072, H), (8, H, H),
+    assert [(g[G_M], g[G_N], g[G_K]) for g in gemms] == [(8, H, H), (8, 2 * FF, H), (8, H, FF), (8, H, H),
                                                           (8, 2 * FF, H), (8, H, FF), (8, V, H)]
     assert all(g[G_BN] == -16 for g in gemms)                      # swapped tiles of 16 tokens
-    assert [g[G_EPI] for g in gemms] == [0, 1, 0, 0, 0, 1, 0, 0]
+    assert [g[G_EPI] for g in gemms] == [0, 1, 0, 0, 1, 0, 0]
+    rope = rec.of("cellm_gemm_rope_tcgen05")[0]
+    assert (rope[3], rope[4]) == (8, H) and rope[7] == -16 and 1 <= rope[8] <= 8 and (rope[19], rope[20]) == (32, 8)
     assert all(1 <= g[G_SPLIT] <= 8 and g[G_WS] is None for g in gemms[:-1])      # the K split stays inside a cluster
     assert gemms[-1][G_SPLIT] == 1 and gemms[-1][G_OUT] == 0       # the head has tiles to spare; 32-bit logits
     conv = rec.of("cellm_gemm_conv_tcgen05")[0]
@@ -40,18 +42,18 @@ def test_decode_step(monkeypatch):
     assert (dec[11], dec[12]) == (8, 8) and dec[20] >= 2 and dec[1] is not None       # keys split over CTAs, with a workspace
 
 
-def test_decode_step_with_the_rotation_in_the_product_and_without_the_fused_convolution(monkeypatch):
-    monkeypatch.setenv("CELLM_B200_FUSED_ROPE", "1")
-    monkeypatch.setenv("CELLM_B200_FUSED_CONV", "0")
+def test_decode_step_without_the_fused_decode_kernels(monkeypatch):
+    from cellm_b200.runtime import program
+    monkeypatch.setitem(program.OPTIONS, "fused_rope", False)
+    monkeypatch.setitem(program.OPTIONS, "fused_conv", False)
     rec = Recorder(monkeypatch)
     cfg, plan, model = zero_model(WIDE)
     run_step(model, plan, [1] * 3, [10, 500, 4000])
     names = rec.names()
-    assert "cellm_gemm_rope_tcgen05" in names and "cellm_qk_norm_rope" not in names
+    assert "cellm_gemm_rope_tcgen05" not in names and "cellm_qk_norm_rope" in names
     assert "cellm_short_conv" in names and "cellm_gemm_conv_tcgen05" not in names
-    rope = rec.of("cellm_gemm_rope_tcgen05")[0]
-    assert (rope[3], rope[4]) == (3, H) and rope[7] == -16 and 1 <= rope[8] <= 8 and (rope[19], rope[20]) == (32, 8)
     assert rec.of("cellm_short_conv")[0][15] == 1                  # the one-launch form for single tokens
+    assert [(g[G_M], g[G_N]) for g in rec.of("cellm_gemm_tcgen05")][:2] == [(3, 3 * H), (3, H)]
 
 
 def test_prompt_step(monkeypatch):
@@ -124,7 +126,7 @@ def test_step_runner_builds_the_step_and_runs_it(monkeypatch):
                  intermediate_size=512, block_auto_adjust_ff_dim=False)
     cfg, plan, model = zero_model(small)
     cache = CacheManager(model.cache_needs(), [e.cache_of for e in plan.order], 16, 8, 2, model.dtype, "cpu")
-    runner = StepRunner(model, cache, use_graphs=False, native_steps=False)
+    runner = StepRunner(model, cache, use_graphs=False)
     monkeypatch.setattr(runner, "_staging", lambda n: torch.empty(max(n, 4096), dtype=torch.int32))
     monkeypatch.setattr(runner, "_uploaded", lambda: None)
     cache.add(7)

@@ -27,7 +27,7 @@ def engine(monkeypatch, next_token, **kw):
         calls[0] += 1
     rec = Recorder(monkeypatch, hooks={"cellm_argmax": argmax})
     loaded = zero_model(CONFIG)
-    eng = Engine(loaded, dtype="bfloat16", device="cpu", use_cuda_graphs=False, native_steps=False, **kw)
+    eng = Engine(loaded, dtype="bfloat16", device="cpu", use_cuda_graphs=False, **kw)
     monkeypatch.setattr(eng.runner, "_staging", lambda n: torch.empty(max(n, 4096), dtype=torch.int32))
     monkeypatch.setattr(eng.runner, "_uploaded", lambda: None)
     monkeypatch.setattr(eng.runner, "check", lambda: None)          # reads the device error word
@@ -104,7 +104,7 @@ def test_sampling_inputs_follow_the_requests_streams_and_histories(monkeypatch):
         for r in range(R):
             row[r] = 300 + len(seen)
     Recorder(monkeypatch, hooks={"cellm_sample": sample})
-    eng = Engine(zero_model(CONFIG), dtype="bfloat16", device="cpu", use_cuda_graphs=False, native_steps=False,
+    eng = Engine(zero_model(CONFIG), dtype="bfloat16", device="cpu", use_cuda_graphs=False,
                  tokens_per_block=8, total_blocks=16, max_num_seqs=2)
     monkeypatch.setattr(eng.runner, "_staging", lambda n: torch.empty(max(n, 4096), dtype=torch.int32))
     monkeypatch.setattr(eng.runner, "_uploaded", lambda: None)
@@ -122,34 +122,6 @@ def test_sampling_inputs_follow_the_requests_streams_and_histories(monkeypatch):
             tail = history[r][-4:]
             assert list(recent[r][:len(tail)]) == tail and all(v == -1 for v in recent[r][len(tail):])
             history[r].append(301 + step)
-
-
-def test_engine_steps_through_the_native_executor(monkeypatch):
-    """The same generation with the step's forward pass handed to the runtime's executor (entry points: recording
-    callbacks): the same tokens, the same kernels in the same order."""
-    from cellm_b200 import SamplingParams
-    from cellm_b200.engine.native_exec import ENTRY_POINTS, NativeForward
-    from cellm_b200.ops import _lib
-    prompts = [list(range(1, 20)), [5, 6, 7], list(range(30, 41))]
-    params = SamplingParams.greedy(6, stop_eos=False)
-    kw = dict(tokens_per_block=8, total_blocks=24, max_num_seqs=3, max_batch_tokens=16, prefill_chunk=8)
-    eng, rec = engine(monkeypatch, lambda r, n: 100 + n, **kw)
-    ref = eng.generate(prompts, params)
-    python_names = [n for n in rec.names() if n != "cellm_argmax"]
-
-    eng2, rec2 = engine(monkeypatch, lambda r, n: 100 + n, **kw)
-    native_names, thunks = [], []
-    for library, name in ENTRY_POINTS:
-        def record(*args, _name=name):
-            native_names.append(_name)
-            return 0
-        thunks.append(ctypes.CFUNCTYPE(ctypes.c_int, *_lib._SIGNATURES[library][name])(record))
-    native = NativeForward(eng2.model, [ctypes.cast(t, ctypes.c_void_p).value for t in thunks], sms=148)
-    monkeypatch.setattr(eng2.runner, "_forward", native.forward)
-    assert eng2.generate(prompts, params) == ref
-    assert native_names == python_names and set(rec2.names()) <= {"cellm_argmax"}
-    st = eng2.stats()
-    assert st["idle"] and st["free_pages"] == st["total_pages"]
 
 
 @pytest.mark.parametrize("seed", range(12))

@@ -73,15 +73,12 @@ def test_odd_configuration_in_every_cutting(tmp_path, name, dtype):
 def test_prompt_attention_on_tcgen05_in_every_cutting(tmp_path, monkeypatch, name, page):
     """Small portions are sent to the tcgen05 prompt kernel (which otherwise takes
     only batches that fill the GPU): same traces, same plain implementation."""
-    import importlib
     from cellm_b200.replay import Replayer
+    from cellm_b200.runtime import program
     from cellm_b200.weights import write_random_model
-    att = importlib.import_module("cellm_b200.ops.attention")        # the module, not the function of that name
-    monkeypatch.setitem(att.TC_POLICY, "min_ctas", 0)
-    monkeypatch.setitem(att.TC_POLICY, "min_fill", 0.0)
-    calls = []
-    real = att.attention_tc
-    monkeypatch.setattr(att, "attention_tc", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    monkeypatch.setitem(program.OPTIONS, "attention_tc_min_ctas", 0)
+    monkeypatch.setitem(program.OPTIONS, "attention_tc_min_fill", 0.0)
+    before = program.CALLS["cellm_attention_tc"]
     config = ODD["g16"][0] if name == "g16" else cfg(
         vocab_size=900, hidden_size=192, num_hidden_layers=3, layer_types=["full_attention", "conv", "full_attention"],
         num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=320)
@@ -96,24 +93,17 @@ def test_prompt_attention_on_tcgen05_in_every_cutting(tmp_path, monkeypatch, nam
         got = traces.collect(steps, [rp.step(s["entries"], s["end"]) for s in steps])
         for r, t in reqs.items():
             check_close(traces.as_matrix(got[r], len(t)), ref[r], "bfloat16", f"{name} tc {make.__name__} {r}")
-    assert calls
+    assert program.CALLS["cellm_attention_tc"] > before
 
 
-def test_decode_with_the_rotation_in_the_qkv_product(tmp_path, monkeypatch):
-    """CELLM_B200_FUSED_ROPE=1 sends decode steps of 64-wide heads through the q/k/v product that norms,
-    turns and stores in its epilogue: the same traces, the same plain implementation."""
-    import importlib
+def test_decode_with_and_without_the_fused_decode_kernels(tmp_path, monkeypatch):
+    """Decode steps of 64-wide heads run the q/k/v product that norms, turns and stores in its epilogue, and in_proj
+    with the short convolution in its epilogue. With both switched off the same traces go through the separate
+    kernels: the same plain implementation, and the two ways agree within the bound between cuttings."""
     from cellm_b200.replay import Replayer
+    from cellm_b200.runtime import program
     from cellm_b200.weights import write_random_model
-    tc = importlib.import_module("cellm_b200.ops.gemm_bf16")
-    att = importlib.import_module("cellm_b200.ops.attention")
-    # prompt portions on the tcgen05 kernel, as in the test above: the two differ in the decode steps only
-    monkeypatch.setitem(att.TC_POLICY, "min_ctas", 0)
-    monkeypatch.setitem(att.TC_POLICY, "min_fill", 0.0)
-    monkeypatch.setenv("CELLM_B200_FUSED_ROPE", "1")
-    calls = []
-    real = tc.gemm_rope_bf16
-    monkeypatch.setattr(tc, "gemm_rope_bf16", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    from tolerances import K_SELF
     config = cfg(vocab_size=900, hidden_size=192, num_hidden_layers=3, layer_types=["full_attention", "conv", "full_attention"],
                  num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=320)
     folder = write_random_model(str(tmp_path / "m"), config, seed=32, dtype="bfloat16", init=TEST_INIT)
@@ -121,13 +111,23 @@ def test_decode_with_the_rotation_in_the_qkv_product(tmp_path, monkeypatch):
     rng = np.random.default_rng(8)
     reqs = {f"r{i}": rng.integers(0, config["vocab_size"], n).tolist() for i, n in enumerate((150, 9, 300, 67))}
     ref = {r: plain.forward(c, w, t).numpy() for r, t in reqs.items()}
-    for make in (traces.tail_one_by_one, traces.mixed):
-        steps = make(reqs)
-        rp = Replayer(folder, "bfloat16", traces.max_live_tokens(steps), 32, 4)
-        got = traces.collect(steps, [rp.step(s["entries"], s["end"]) for s in steps])
+    results = {}
+    for fused in (True, False):
+        monkeypatch.setitem(program.OPTIONS, "fused_rope", fused)
+        monkeypatch.setitem(program.OPTIONS, "fused_conv", fused)
+        before = dict(program.CALLS)
+        for make in (traces.tail_one_by_one, traces.mixed):
+            steps = make(reqs)
+            rp = Replayer(folder, "bfloat16", traces.max_live_tokens(steps), 32, 4, use_graphs=False)
+            got = results[fused, make.__name__] = traces.collect(steps, [rp.step(s["entries"], s["end"]) for s in steps])
+            for r, t in reqs.items():
+                check_close(traces.as_matrix(got[r], len(t)), ref[r], "bfloat16", f"fused {fused} {make.__name__} {r}")
+        ran = {k: program.CALLS[k] - before[k] for k in before}
+        assert (ran["cellm_gemm_rope_tcgen05"] > 0) == fused and (ran["cellm_gemm_conv_tcgen05"] > 0) == fused
+    for make in ("tail_one_by_one", "mixed"):
         for r, t in reqs.items():
-            check_close(traces.as_matrix(got[r], len(t)), ref[r], "bfloat16", f"fused rope {make.__name__} {r}")
-    assert calls
+            check_close(traces.as_matrix(results[True, make][r], len(t)), traces.as_matrix(results[False, make][r], len(t)),
+                        "bfloat16", f"fused vs separate kernels {make} {r}", k=K_SELF["bfloat16"])
 
 
 def test_odd_configuration_generates(tmp_path):

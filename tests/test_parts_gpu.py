@@ -185,7 +185,7 @@ def test_a_model_stored_in_32_bit(tmp_path, dtype):
     cfg, w = plain.load_folder(folder)
     toks = np.random.default_rng(9).integers(0, 512, 40).tolist()
     rp = Replayer(folder, dtype, 64, 8)
-    assert rp.model.embedding.dtype == torch.float32
+    assert rp.model.embedding.weight.dtype == torch.float32
     out = rp.step([{"id": "a", "tokens": toks, "want": list(range(40))}], ["a"])
     check_close(out, plain.forward(cfg, w, toks).numpy(), dtype)
 
