@@ -22,6 +22,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "attention_flash_noalloc.h"
 #include "mma_tiles.cuh"
 
 namespace {
@@ -348,6 +349,8 @@ CELLM_API int cellm_attention_flash(void* out, float* part_o, float* part_ml, co
 //   * The first call on a device looks the array's device address up
 //     (cudaGetSymbolAddress with that device current). Make that first call
 //     outside any stream capture.
+//   * T must be the number of tokens the call brings, cu_seqlens[B]: the merge reads the pieces of all T * nh
+//     rows, and rows beyond cu_seqlens[B] were written by no kernel of this call.
 //   * All calls share the one array. It keeps the previous call's contents;
 //     nothing in it has to start at zero, because every (piece, row) the merge
 //     reads is written by this call's first kernel. Two calls whose kernels
@@ -388,6 +391,8 @@ CELLM_API int cellm_attention_flash_noalloc(void* out, const void* q, const void
                                             int nh, int nkv, int hd, float scale, int window, int wide, int nsplit,
                                             int* err, cudaStream_t stream) {
     if (nsplit < 1) return CELLM_ERR_ARG;
+    // the sizes the kernel takes, before the question whether the pieces fit (so that a bad head size reads as one)
+    if (nkv <= 0 || nh <= 0 || nh % nkv != 0 || (hd != 32 && hd != 64 && hd != 128)) return CELLM_ERR_SIZE;
     if (T <= 0 || n_tiles <= 0) return CELLM_OK;
     const long long need = (long long)nsplit * T * nh * (hd + 2);
     if (nsplit > 1 && need > (long long)NOALLOC_SCRATCH_FLOATS) return CELLM_ERR_SCRATCH;

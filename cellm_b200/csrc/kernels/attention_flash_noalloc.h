@@ -25,7 +25,9 @@ extern "C" {
 
 /* out, q: [T, nh*hd] bfloat16; k_pool, v_pool: one layer's cache
  * [pages][kv heads][page size][hd] bfloat16; cu_seqlens [B+1], ctx_lens [B],
- * block_table [B][bt_stride] int32 on the device; n_tiles = sum over requests of
+ * block_table [B][bt_stride] int32 on the device; T must equal cu_seqlens[B] (the
+ * host cannot check it: with a larger T the merge of the pieces reads rows of the
+ * shared array that this call did not write); n_tiles = sum over requests of
  * ceil(q_len * (nh / nkv) / (wide ? 64 : 16)); err: device error word.
  * Returns 0, a cudaError_t (> 0), or a negative refusal code. */
 int cellm_attention_flash_noalloc(void* out, const void* q, const void* k_pool, const void* v_pool,

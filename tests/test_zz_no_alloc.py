@@ -64,7 +64,10 @@ def test_no_alloc_entry_point_matches_regular_entry_point():
     assert lib.cellm_attention_flash_noalloc_capacity() == 2 * 1024 * 1024
     err = torch.zeros(1, dtype=torch.int32, device="cuda:0")
     cases = [(_inputs([1, 1, 1], [300, 40, 513], 8, 2, 64, 16, seed=1), 4, False),
-             (_inputs([70, 1], [130, 900], 6, 2, 32, 8, seed=2), 3, True)]
+             (_inputs([70, 1], [130, 900], 6, 2, 32, 8, seed=2), 3, True),
+             (_inputs([33, 5], [0, 77], 4, 4, 128, 16, seed=4), 1, True),           # one piece: the array is not used at all
+             # the largest call that fits: 4 pieces x 992 tokens x 8 heads x 66 floats = 2,095,104 of 2,097,152
+             (_inputs([992], [0], 8, 2, 64, 16, seed=5), 4, True)]
     for x, nsplit, wide in cases:        # two calls in a row on the one shared array
         ref = attention_flash(x["q"], x["k"], x["v"], x["cu"], x["ctx"], x["bt"], x["q_lens"], x["nh"],
                               1.0 / math.sqrt(x["k"].shape[3]), 0, err, nsplit, wide)
@@ -93,3 +96,12 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit():
     assert b"scratch" in lib.cellm_attention_flash_noalloc_error(rc)
     rc, _ = _call_noalloc(lib, x, 0, True, err)
     assert rc == -4
+    # one token more than the largest call that fits (see the test above) is refused
+    rc, _ = _call_noalloc(lib, _inputs([993], [0], 8, 2, 64, 16, seed=5), 4, True, err)
+    assert rc == -5
+    # a head size the kernel does not take reads as that, whatever the pieces would need
+    bad = _inputs([600], [0], 32, 8, 48, 16, seed=6)
+    rc, _ = _call_noalloc(lib, bad, 8, True, err)
+    assert rc == -2
+    torch.cuda.synchronize()
+    assert err.item() == 0
