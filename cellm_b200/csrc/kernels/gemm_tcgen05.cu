@@ -648,6 +648,38 @@ __global__ void splitk_sum_kernel(const float* __restrict__ ws, TO* __restrict__
         C[(size_t)m * ldc + o0 + j] = from_float<TO>(EPI == 1 ? silu_mul(a[j], b[j]) : a[j]);
 }
 
+// Sixteen values of a row (the last chunk of a tile whose width is an odd multiple of 16).
+template <typename TO> __device__ __forceinline__ void store_half_row(TO* dst, const uint32_t* r, int valid, bool aligned);
+template <> __device__ __forceinline__ void store_half_row<float>(float* dst, const uint32_t* r, int valid, bool aligned) {
+    if (valid >= 16 && aligned) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (i < valid) dst[i] = __uint_as_float(r[i]);
+    }
+}
+template <> __device__ __forceinline__ void store_half_row<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t* r, int valid, bool aligned) {
+    if (valid >= 16 && aligned) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 2 * j]), __uint_as_float(r[8 * i + 2 * j + 1]));
+                p[j] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(p[0], p[1], p[2], p[3]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (i < valid) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+    }
+}
+
 // Persistent form for large products (plain tiles, no K split): one CTA per SM walks
 // the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles of A fastest, so
 // CTAs that run side by side share a tile of W in L2). The accumulator is double
@@ -658,12 +690,15 @@ template <int BN, int STAGES, int EPI, typename TO>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                                TO* __restrict__ C, int M, int N, int K, long long ldc, int w_is_static,
-                               int* __restrict__ err) {
+                               int* __restrict__ err, int bn) {
+    // bn: the width of a tile in columns, a multiple of 16 (of 128 with the SwiGLU epilogue) and at most BN, which
+    // sizes the stages and the accumulators. Widths between the powers of two let the number of tiles come close
+    // to a multiple of the SMs, so that the last wave is not half empty.
     extern __shared__ uint8_t smem_raw[];
     auto& sm = *reinterpret_cast<GemmSmem<BN, STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t TMEM_COLS = 2 * BN;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, num_tiles = m_tiles * n_tiles;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + bn - 1) / bn, num_tiles = m_tiles * n_tiles;
     const int nkb = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -688,13 +723,13 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             bool waited = false;
             if (!w_is_static) { pdl_wait(); waited = true; }
             for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
-                const int p0 = (tile % m_tiles) * BM, q0 = (tile / m_tiles) * BN;
+                const int p0 = (tile % m_tiles) * BM, q0 = (tile / m_tiles) * bn;
                 int kb = 0;
                 if (!waited) {
                     // static weights: the ring's first loads of W go out before the wait on the preceding kernel
                     const int early = nkb < STAGES ? nkb : STAGES;
                     for (int i = 0; i < early; ++i) {
-                        mbar_expect_tx(&sm.full[i], (BM + BN) * BK * 2);
+                        mbar_expect_tx(&sm.full[i], (uint32_t)((BM + bn) * BK * 2));
                         tma_load_2d(sm.b[i], &map_w, i * BK, q0, &sm.full[i]);
                     }
                     pdl_wait();
@@ -707,7 +742,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                     const int s = it % STAGES;
                     const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
                     if (!mbar_wait(&sm.empty[s], phase ^ 1u, abort_flag)) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); break; }
-                    mbar_expect_tx(&sm.full[s], (BM + BN) * BK * 2);
+                    mbar_expect_tx(&sm.full[s], (uint32_t)((BM + bn) * BK * 2));
                     tma_load_2d(sm.a[s], &map_a, kb * BK, p0, &sm.full[s]);
                     tma_load_2d(sm.b[s], &map_w, kb * BK, q0, &sm.full[s]);
                 }
@@ -715,7 +750,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(BM, BN);
+            const uint32_t idesc = umma_idesc(BM, bn);
             int it = 0, tcount = 0;
             for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
                 const int buf = tcount & 1;
@@ -754,32 +789,38 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             }
             tc_fence_after();
             if (!waited) { pdl_wait(); waited = true; }    // stores must not pass the kernel before this one
-            const int p0 = (tile % m_tiles) * BM, q0 = (tile / m_tiles) * BN;
+            const int p0 = (tile % m_tiles) * BM, q0 = (tile / m_tiles) * bn;
             const int p = p0 + pl;
             const uint32_t lane_addr = tmem + ((uint32_t)(qtr * 32) << 16) + (uint32_t)(buf * BN);
             if constexpr (EPI == 0) {
                 const bool aligned = ((reinterpret_cast<uintptr_t>(C) | (uintptr_t)(ldc * sizeof(TO))) & 15) == 0 &&
                                      ((q0 * sizeof(TO)) & 15) == 0;
+                const int chunks = (bn + 31) / 32;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < chunks; ++c) {
                     uint32_t r[32];
-                    tmem_ld32(lane_addr + (uint32_t)(c * 32), r);
-                    if (c == BN / 32 - 1) { tc_fence_before(); mbar_arrive(&sm.acc_empty2[buf]); }
+                    const int cols = bn - c * 32 >= 32 ? 32 : 16;          // the last chunk of a width that is an odd multiple of 16
+                    if (cols == 32) tmem_ld32(lane_addr + (uint32_t)(c * 32), r);
+                    else tmem_ld16(lane_addr + (uint32_t)(c * 32), r);
+                    if (c == chunks - 1) { tc_fence_before(); mbar_arrive(&sm.acc_empty2[buf]); }
                     const int q = q0 + c * 32;
-                    if (p < M && q < N) store_row<TO>(C + (size_t)p * ldc + q, r, N - q, aligned);
+                    if (p < M && q < N) {
+                        if (cols == 32) store_row<TO>(C + (size_t)p * ldc + q, r, N - q, aligned);
+                        else store_half_row<TO>(C + (size_t)p * ldc + q, r, N - q, aligned);
+                    }
                 }
             } else {
                 const int o0 = q0 / 2;
                 const bool aligned = ((reinterpret_cast<uintptr_t>(C) | (uintptr_t)(ldc * sizeof(TO))) & 15) == 0 &&
                                      ((o0 * sizeof(TO)) & 15) == 0;
 #pragma unroll 1
-                for (int j = 0; j < BN / 128; ++j) {
+                for (int j = 0; j < bn / 128; ++j) {
 #pragma unroll 1
                     for (int h = 0; h < 2; ++h) {
                         uint32_t g[32], u[32];
                         tmem_ld32(lane_addr + (uint32_t)(j * 128 + h * 32), g);
                         tmem_ld32(lane_addr + (uint32_t)(j * 128 + 64 + h * 32), u);
-                        if (j == BN / 128 - 1 && h == 1) { tc_fence_before(); mbar_arrive(&sm.acc_empty2[buf]); }
+                        if (j == bn / 128 - 1 && h == 1) { tc_fence_before(); mbar_arrive(&sm.acc_empty2[buf]); }
 #pragma unroll
                         for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(silu_mul(__uint_as_float(g[i]), __uint_as_float(u[i])));
                         const int o = o0 + j * 64 + h * 32;
@@ -833,7 +874,7 @@ int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* w
 
 template <int BN, int STAGES, int EPI, typename TO>
 int launch_persistent(const CUtensorMap& m_a, const CUtensorMap& m_w, TO* C, int M, int N, int K, long long ldc,
-                      int w_is_static, int* err, cudaStream_t stream) {
+                      int w_is_static, int* err, cudaStream_t stream, int bn) {
     const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
     static int sms = 0;
     if (sms == 0) {
@@ -844,10 +885,10 @@ int launch_persistent(const CUtensorMap& m_a, const CUtensorMap& m_w, TO* C, int
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
             return CELLM_ERR_ARG;
     }
-    const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    const int tiles = ((N + bn - 1) / bn) * ((M + BM - 1) / BM);
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     cudaError_t e = cellm_launch(gemm_tcgen05_persistent_kernel<BN, STAGES, EPI, TO>, grid, dim3(192), smem, stream, m_a,
-                                 m_w, C, M, N, K, ldc, w_is_static, err);
+                                 m_w, C, M, N, K, ldc, w_is_static, err, bn);
     return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
@@ -892,7 +933,9 @@ static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K,
     if (epilogue < 0 || epilogue > 3) return CELLM_ERR_ARG;
     const bool swap = bn < 0;
     const int narrow = swap ? -bn : bn;
-    if (swap ? (narrow != 16 && narrow != 32 && narrow != 64) : (narrow != 64 && narrow != 128 && narrow != 256))
+    // plain tiles: 64, 128 or 256 columns; unsplit products (the persistent kernel) also any multiple of 16 from 128 to 256
+    const bool odd_width = !swap && narrow > 128 && narrow < 256 && (narrow & 15) == 0 && epilogue == 0;
+    if (swap ? (narrow != 16 && narrow != 32 && narrow != 64) : (narrow != 64 && narrow != 128 && narrow != 256 && !odd_width))
         return CELLM_ERR_SIZE;
     if (epilogue == 1 && ((N & 127) || (!swap && narrow < 128))) return CELLM_ERR_SIZE;
     long long ws_floats;
@@ -908,6 +951,7 @@ static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K,
     if (ws_floats > 0 && workspace == nullptr) return CELLM_ERR_ARG;
     // Plain tiles without counters: the pieces go to the workspace and a second kernel sums them, all SMs at work
     // (with counters the last CTA of a tile sums its pieces alone, which is slow for tiles of 128 tokens).
+    if (odd_width && split > 1) return CELLM_ERR_SIZE;
     const bool sum_later = split > 1 && !in_cluster && !swap && counters == nullptr;
     if (split > 1 && !in_cluster && !sum_later) {
         if (counters == nullptr) return CELLM_ERR_ARG;
@@ -925,11 +969,11 @@ static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K,
     if (!swap && split == 1 && narrow >= 128) {
 #define GOP(BN_, ST_, EP_)                                                                                          \
     do {                                                                                                            \
-        if (out_dtype == CELLM_F32) rc = launch_persistent<BN_, ST_, EP_, float>(map_a, map_w, (float*)C, M, N, K, ldc, w_is_static, err, stream); \
-        else rc = launch_persistent<BN_, ST_, EP_, __nv_bfloat16>(map_a, map_w, (__nv_bfloat16*)C, M, N, K, ldc, w_is_static, err, stream); \
+        if (out_dtype == CELLM_F32) rc = launch_persistent<BN_, ST_, EP_, float>(map_a, map_w, (float*)C, M, N, K, ldc, w_is_static, err, stream, narrow); \
+        else rc = launch_persistent<BN_, ST_, EP_, __nv_bfloat16>(map_a, map_w, (__nv_bfloat16*)C, M, N, K, ldc, w_is_static, err, stream, narrow); \
     } while (0)
         if (narrow == 128) { if (epilogue == 0) GOP(128, 6, 0); else GOP(128, 6, 1); }
-        else { if (epilogue == 0) GOP(256, 4, 0); else GOP(256, 4, 1); }
+        else { if (epilogue == 0) GOP(256, 4, 0); else GOP(256, 4, 1); }       // 144 to 256 columns
 #undef GOP
         return rc;
     }

@@ -266,11 +266,15 @@ void plan_tiles(i64 M, i64 N, i64 K, i64 sms, i64* bn_out, i64* split_out) {
     }
     i64 bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
     if (bn == 256) {
-        // 128-wide tiles cost about 0.55 of a 256-wide one; take them when their waves finish sooner
+        // The persistent kernel takes any width from 128 to 256 in steps of 16. A tile costs about 0.1 + 0.9 * width / 256
+        // of a 256-wide one (a 128-wide one 0.55); the width whose waves finish soonest wins, the wider on a tie: it
+        // is the one whose number of tiles comes closest to a multiple of the SMs from below.
         const i64 mt = ceil_div(M, 128);
-        const i64 waves256 = ceil_div(mt * ceil_div(N, 256), sms);
-        const i64 waves128 = ceil_div(mt * ceil_div(N, 128), sms);
-        if ((double)waves128 * 0.55 < (double)waves256 * 0.95) bn = 128;
+        double best = 1e30;
+        for (i64 w = 256; w >= 128; w -= 16) {
+            const double cost = (double)ceil_div(mt * ceil_div(N, w), sms) * (0.1 + 0.9 * (double)w / 256.0);
+            if (cost < best * 0.98) { best = cost; bn = w; }
+        }
     }
     i64 tiles = ceil_div(N, bn) * ceil_div(M, 128);
     if (tiles < sms / 2) {
@@ -304,6 +308,7 @@ void Run::feed_forward(const SwiGLUParams& L, const void* x, void* out) {
         i64 bn, split;
         plan_tiles(T, L.gate_up.N, L.gate_up.K, p.sms, &bn, &split);
         if (bn == 64) bn = 128;
+        else if (bn > 128 && bn < 256) bn = 256;       // gate and up blocks of 64: widths of 128 and 256 only
         h = arena.take(T * L.ff * elt(act));
         gemm_tc(h, x, L.gate_up, T, L.gate_up.N, H, act, bn, split, 1);
     } else if (L.fused) {

@@ -65,7 +65,8 @@ def test_prompt_step(monkeypatch):
     assert names.count("cellm_attention_tc") == 1 and names.count("cellm_short_conv") == 1
     gemms = rec.of("cellm_gemm_tcgen05")
     body, head = gemms[:-1], gemms[-1]
-    assert all(g[G_M] == 2048 and g[G_BN] in (128, 256) and g[G_SPLIT] == 1 for g in body)     # plain tiles, persistent kernel
+    assert all(g[G_M] == 2048 and 128 <= g[G_BN] <= 256 and g[G_SPLIT] == 1 for g in body)     # plain tiles, persistent kernel
+    assert [g[G_BN] for g in body] == [240, 240, 256, 240, 176, 240, 256, 240]                  # widths that fill the waves of 148 SMs
     assert [g[G_EPI] for g in body] == [0, 0, 1, 0, 0, 0, 1, 0]
     assert (head[G_M], head[G_N]) == (1, V) and head[G_BN] == -16                               # one wanted row
     assert rec.of("cellm_short_conv")[0][15] == 2048

@@ -521,7 +521,8 @@ def test_gemm_plain(dtype, out, M, N, K):
     (40, 1000, 224, -64, 1), (64, 96, 96, -64, 2), (70, 300, 4096, 64, 4),
     (130, 300, 1024, -64, 4), (500, 2048, 2048, -64, 1), (70, 520, 512, -32, 2),     # swapped tiles, several token tiles side by side
     (512, 2048, 2048, 128, 4), (300, 330, 1024, 128, 16), (200, 72, 4096, 64, 8),     # plain tiles, pieces summed by a second kernel
-    (1500, 4000, 256, 256, 1), (2100, 2500, 192, 128, 1)])      # more tiles than SMs: CTAs of the persistent kernel loop
+    (1500, 4000, 256, 256, 1), (2100, 2500, 192, 128, 1),       # more tiles than SMs: CTAs of the persistent kernel loop
+    (2048, 3072, 512, 176, 1), (300, 1000, 256, 240, 1), (1300, 2048, 128, 144, 1), (200, 520, 1024, 208, 1)])   # widths between 128 and 256
 def test_gemm_tcgen05(out, M, N, K, bn, split):
     from cellm_b200.ops.gemm_bf16 import error_word, gemm_tcgen05
     a = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
