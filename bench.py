@@ -307,8 +307,13 @@ def main() -> int:
     if not args.no_points:
         for b in (1, 64):
             e, r = decode_setup(loaded, b, b * CONTEXT_LEN // PAGE, rng)
-            ms, _, _, _, _, _ = time_decode(e, r, max(8, args.steps // 2), args.warmup, rng)
+            n_steps = max(8, args.steps // 2)
+            ms, _, _, _, _, c_end = time_decode(e, r, n_steps, args.warmup, rng)
             points[f"decode_b{b}"] = round(b / (ms * 1e-3), 1)
+            # the same roofline as the main run's: weights once and the live requests' cache, over the step's time
+            b_bytes = weight_bytes + b * (c_end - n_steps / 2) * kv_bytes_tok
+            points[f"decode_b{b}_ms"] = round(ms, 4)
+            points[f"decode_b{b}_hbm_frac"] = round(b_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
             for x in r:
                 e.cancel(x)
             del e

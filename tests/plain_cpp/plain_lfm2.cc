@@ -1,12 +1,12 @@
 // A second plain LFM2, in C++, for tests only: one token at a time with a growing
 // list of keys and values and a ring of the last convolution inputs, as the
 // reference's CPU path walks a sequence (crates/cellm-model/src/lfm.rs:263-763),
-// all in double precision. It shares no code with the package nor with the
+// in double precision for the tests and in 32-bit for the timed CPU baseline. It shares no code with the package nor with the
 // Python plain implementation beside it (which works on whole sequences), so a
 // slip in reading the reference would have to be made twice, in two forms, to
 // go unseen. Each function cites the lines it restates.
 //
-// Built by tests/test_plain.py with the host compiler; called through ctypes.
+// Built by tests/test_plain.py and by tests/plain_cpp/time_cpu_baseline.py with the host compiler; called through ctypes.
 #include <cmath>
 #include <cstddef>
 #include <vector>
@@ -22,68 +22,70 @@ struct Config {
 enum Slot { OPERATOR_NORM, FFN_NORM, W1, W2, W3, IN_PROJ, CONV_W, CONV_B, OUT_PROJ, WQ, WK, WV, WO, Q_NORM, K_NORM, SLOTS };
 
 // crates/cellm-kernels/src/cpu_kernels.rs:17-34: ms = sum x^2 / n; out = x / sqrt(ms + eps) * w (weight as it is).
-void rms_norm(const double* x, const double* w, int n, double eps, double* out) {
-    double ss = 0.0;
+template <typename R>
+void rms_norm(const R* x, const R* w, int n, double eps, R* out) {
+    R ss = 0;
     for (int i = 0; i < n; ++i) ss += x[i] * x[i];
-    const double inv = 1.0 / std::sqrt(ss / n + eps);
+    const R inv = (R)1 / std::sqrt(ss / n + (R)eps);
     for (int i = 0; i < n; ++i) out[i] = x[i] * inv * w[i];
 }
 
 // out[r] = sum_c W[r][c] x[c], W row-major [rows, cols], no bias (crates/cellm-model/src/lfm.rs:952-1000).
-void linear(const double* W, const double* x, int rows, int cols, double* out) {
+template <typename R>
+void linear(const R* W, const R* x, int rows, int cols, R* out) {
     for (int r = 0; r < rows; ++r) {
-        double acc = 0.0;
-        const double* wr = W + (size_t)r * cols;
+        R acc = 0;
+        const R* wr = W + (size_t)r * cols;
         for (int c = 0; c < cols; ++c) acc += wr[c] * x[c];
         out[r] = acc;
     }
 }
 
 // crates/cellm-kernels/src/cpu_kernels.rs:264-277 with rotary_dim = head_dim: pairs (i, i + hd/2).
-void rope(double* h, int hd, int pos, double theta) {
+template <typename R>
+void rope(R* h, int hd, int pos, double theta) {
     const int half = hd / 2;
     for (int i = 0; i < half; ++i) {
-        const double inv_freq = std::pow(theta, -(2.0 * i) / hd);
-        const double a = pos * inv_freq, c = std::cos(a), s = std::sin(a);
-        const double x0 = h[i], x1 = h[half + i];
+        const R inv_freq = (R)std::pow((R)theta, (R)(-(2.0 * i) / hd));
+        const R a = pos * inv_freq, c = std::cos(a), s = std::sin(a);
+        const R x0 = h[i], x1 = h[half + i];
         h[i] = x0 * c - x1 * s;
         h[half + i] = x1 * c + x0 * s;
     }
 }
 
-}  // namespace
 
 // Logits [T, vocab] of one sequence. `w`: embed, final norm, head (null: the embedding is the
 // head; an untied head is an addition to the reference, which always ties: lfm.rs:689-757), then
 // SLOTS pointers per layer (null where the layer kind has no such tensor). `is_attention[l]`
 // chooses the mixer. Returns 0, or -1 for a token id outside the vocabulary (lfm.rs:817-890).
-extern "C" int plain_lfm2_forward(const Config* cfg, const double* const* w, const int* is_attention, const int* ids,
-                                  int T, double* logits) {
+template <typename R>
+int forward(const Config* cfg, const R* const* w, const int* is_attention, const int* ids, int T, R* logits) {
     const Config& c = *cfg;
     const int H = c.hidden, hd = c.head_dim, A = c.heads * hd, KV = c.kv_heads * hd, ks = c.taps;
-    const double* embed = w[0];
-    const double* final_norm = w[1];
-    const double* head = w[2] ? w[2] : w[0];
+    const R* embed = w[0];
+    const R* final_norm = w[1];
+    const R* head = w[2] ? w[2] : w[0];
     // per layer: the keys and values of all tokens so far, or the last `taps` columns of B*x
-    std::vector<std::vector<double>> keys(c.layers), values(c.layers), conv_state(c.layers);
+    std::vector<std::vector<R>> keys(c.layers), values(c.layers), conv_state(c.layers);
     for (int l = 0; l < c.layers; ++l)
-        if (!is_attention[l]) conv_state[l].assign((size_t)ks * H, 0.0);
-    std::vector<double> x(H), xn(H), mix(H), bcx(3 * H), y(H), q(A), k(KV), v(KV), att(A), g(c.ff), u(c.ff), d(H), s;
+        if (!is_attention[l]) conv_state[l].assign((size_t)ks * H, (R)0);
+    std::vector<R> x(H), xn(H), mix(H), bcx(3 * H), y(H), q(A), k(KV), v(KV), att(A), g(c.ff), u(c.ff), d(H), s;
     for (int t = 0; t < T; ++t) {
         if (ids[t] < 0 || ids[t] >= c.vocab) return -1;
         for (int i = 0; i < H; ++i) x[i] = embed[(size_t)ids[t] * H + i];
         for (int l = 0; l < c.layers; ++l) {
-            const double* const* lw = w + 3 + (size_t)l * SLOTS;
+            const R* const* lw = w + 3 + (size_t)l * SLOTS;
             rms_norm(x.data(), lw[OPERATOR_NORM], H, c.eps, xn.data());                  // lfm.rs:333-347
             if (!is_attention[l]) {
                 // lfm.rs:350-417: in_proj -> B | C | x; bx = B*x; the state shifts by one column and
                 // takes bx; tap ks-1 meets the current token, tap 0 the oldest (:388-398); y = C*conv.
                 linear(lw[IN_PROJ], xn.data(), 3 * H, H, bcx.data());
-                std::vector<double>& st = conv_state[l];
+                std::vector<R>& st = conv_state[l];
                 for (int ch = 0; ch < H; ++ch) {
                     for (int j = 0; j + 1 < ks; ++j) st[(size_t)ch * ks + j] = st[(size_t)ch * ks + j + 1];
                     st[(size_t)ch * ks + ks - 1] = bcx[ch] * bcx[2 * H + ch];
-                    double conv = lw[CONV_B] ? lw[CONV_B][ch] : 0.0;                      // the bias is an addition
+                    R conv = lw[CONV_B] ? lw[CONV_B][ch] : (R)0;                      // the bias is an addition
                     for (int j = 0; j < ks; ++j) conv += lw[CONV_W][(size_t)ch * ks + j] * st[(size_t)ch * ks + j];
                     y[ch] = bcx[H + ch] * conv;
                 }
@@ -96,7 +98,7 @@ extern "C" int plain_lfm2_forward(const Config* cfg, const double* const* w, con
                 linear(lw[WQ], xn.data(), A, H, q.data());
                 linear(lw[WK], xn.data(), KV, H, k.data());
                 linear(lw[WV], xn.data(), KV, H, v.data());
-                std::vector<double> tmp(hd);
+                std::vector<R> tmp(hd);
                 for (int h = 0; h < c.heads; ++h) {
                     rms_norm(&q[(size_t)h * hd], lw[Q_NORM], hd, c.eps, tmp.data());
                     for (int i = 0; i < hd; ++i) q[(size_t)h * hd + i] = tmp[i];
@@ -110,21 +112,21 @@ extern "C" int plain_lfm2_forward(const Config* cfg, const double* const* w, con
                 keys[l].insert(keys[l].end(), k.begin(), k.end());
                 values[l].insert(values[l].end(), v.begin(), v.end());
                 const int group = c.heads / c.kv_heads;
-                const double scale = 1.0 / std::sqrt((double)hd);
+                const R scale = (R)1 / std::sqrt((R)hd);
                 s.resize(t + 1);
                 for (int h = 0; h < c.heads; ++h) {
                     const int kvh = h / group;
-                    double mx = -INFINITY;
+                    R mx = -INFINITY;
                     for (int j = 0; j <= t; ++j) {
-                        double dot = 0.0;
+                        R dot = 0;
                         for (int i = 0; i < hd; ++i) dot += q[(size_t)h * hd + i] * keys[l][(size_t)j * KV + (size_t)kvh * hd + i];
                         s[j] = dot * scale;
-                        mx = std::fmax(mx, s[j]);
+                        mx = s[j] > mx ? s[j] : mx;
                     }
-                    double sum = 0.0;
+                    R sum = 0;
                     for (int j = 0; j <= t; ++j) { s[j] = std::exp(s[j] - mx); sum += s[j]; }
                     for (int i = 0; i < hd; ++i) {
-                        double acc = 0.0;
+                        R acc = 0;
                         for (int j = 0; j <= t; ++j) acc += s[j] * values[l][(size_t)j * KV + (size_t)kvh * hd + i];
                         att[(size_t)h * hd + i] = acc / sum;
                     }
@@ -135,7 +137,7 @@ extern "C" int plain_lfm2_forward(const Config* cfg, const double* const* w, con
             rms_norm(x.data(), lw[FFN_NORM], H, c.eps, xn.data());                       // lfm.rs:615-629
             linear(lw[W1], xn.data(), c.ff, H, g.data());                               // lfm.rs:631-662
             linear(lw[W3], xn.data(), c.ff, H, u.data());
-            for (int i = 0; i < c.ff; ++i) g[i] = g[i] * (1.0 / (1.0 + std::exp(-g[i]))) * u[i];
+            for (int i = 0; i < c.ff; ++i) g[i] = g[i] * ((R)1 / ((R)1 + std::exp(-g[i]))) * u[i];
             linear(lw[W2], g.data(), H, c.ff, d.data());
             for (int i = 0; i < H; ++i) x[i] += d[i];                                    // lfm.rs:665-667
         }
@@ -143,4 +145,18 @@ extern "C" int plain_lfm2_forward(const Config* cfg, const double* const* w, con
         linear(head, xn.data(), c.vocab, H, logits + (size_t)t * c.vocab);               // lfm.rs:689-757
     }
     return 0;
+}
+}  // namespace
+
+// In double precision: the tests' second restatement.
+extern "C" int plain_lfm2_forward(const Config* cfg, const double* const* w, const int* is_attention, const int* ids, int T,
+                                  double* logits) {
+    return forward<double>(cfg, w, is_attention, ids, T, logits);
+}
+
+// In 32-bit, as the reference's CPU path computes (crates/cellm-model/src/lfm.rs works on f32 throughout): the
+// timed CPU baseline (tests/plain_cpp/time_cpu_baseline.py).
+extern "C" int plain_lfm2_forward_f32(const Config* cfg, const float* const* w, const int* is_attention, const int* ids, int T,
+                                      float* logits) {
+    return forward<float>(cfg, w, is_attention, ids, T, logits);
 }

@@ -161,9 +161,10 @@ def test_short_conv_long_portions_of_several_requests(taps, bias):
 @pytest.mark.parametrize("H,K,taps,bias,M", [(2048, 2048, 3, False, 8), (96, 96, 4, True, 3), (100 * 8, 64, 2, True, 33),
                                              (42, 200, 1, False, 1), (520, 1032, 3, True, 64), (2048, 2048, 3, False, 1)])
 def test_in_proj_with_the_convolution_in_its_epilogue(H, K, taps, bias, M):
-    """Decode steps: in_proj and the gated convolution as one kernel against the product
-    followed by short_conv, four steps in a row (the state is carried in slots that change
-    place from step to step), widths that do and do not fill the tiles of 42 channels."""
+    """Decode steps: in_proj and the gated convolution as one kernel against the same arithmetic in 64-bit torch
+    (B, C and x rounded to bfloat16 as a product would store them), four steps in a row (the state is carried in
+    slots that change place from step to step), widths that do and do not fill the tiles of 42 channels; and
+    against the product followed by short_conv, which it replaces."""
     from cellm_b200 import ops
     from cellm_b200.ops import gemm_bf16 as tc
     g = torch.Generator(device=DEV).manual_seed(H + taps)
@@ -182,17 +183,34 @@ def test_in_proj_with_the_convolution_in_its_epilogue(H, K, taps, bias, M):
     for step in range(4):
         x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
         sl = ((torch.arange(M, device=DEV) + step) % slots).int()
+        before = state_b.double().clone()
         ref = ops.short_conv(ops.gemm(x, w_in, torch.bfloat16), w, b, state_a, sl, seq, cu, e, 1)
         got = tc.gemm_conv_bf16(x, tiled, H, w, b, state_b, sl, plan, e)
         assert e.item() == 0
+        # 64-bit torch on the state the kernel started from
+        bcx = bf16r(x.double() @ w_in.double().T)
+        B, C, xx = bcx[:, :H], bcx[:, H:2 * H], bcx[:, 2 * H:]
+        hist = torch.cat([before[sl.long()], (B * xx)[:, None, :]], dim=1)          # [M, taps, H]
+        conv = (hist * w.double().T[None]).sum(dim=1)
+        if bias:
+            conv = conv + b.double()[None]
+        close(got, C * conv, torch.bfloat16, f"step {step} against 64-bit torch")
+        want_state = before.clone()
+        want_state[sl.long()] = hist[:, 1:]
+        close(state_b, want_state, torch.bfloat16, f"state after step {step}")        # B*x of sums rounded to bfloat16
         # the same sums rounded at the same places (the K split may differ, hence a unit of bfloat16 rounding here and there)
-        close(got, ref.double().cpu(), torch.bfloat16, f"step {step}")
+        close(got, ref.double().cpu(), torch.bfloat16, f"step {step} against product + short_conv")
         assert torch.allclose(state_a, state_b, rtol=2e-2, atol=1e-3)
     # a slot outside the pool is reported, and nothing is written for it
     bad = torch.full((M,), slots, dtype=torch.int32, device=DEV)
     tc.gemm_conv_bf16(torch.randn(M, K, device=DEV).bfloat16(), tiled, H, w, b, state_b, bad, plan, e)
     assert e.item() == 4
     e.zero_()
+
+
+def bf16r(t):
+    """Rounded to bfloat16 and back, as a product that stores its result in bfloat16 leaves it."""
+    return t.to(torch.bfloat16).double()
 
 
 @pytest.mark.parametrize("dtype", DT)
@@ -275,6 +293,16 @@ def test_qkv_product_with_norm_rotation_and_cache_write_in_its_epilogue(nh, nkv,
     assert plan is not None
     got = tc.gemm_rope_bf16(x, w, qw, kw, 1e-5, pos, bt, kp_b, vp_b, nh, nkv, inv, plan, e)
     assert e.item() == 0
+    # against 64-bit torch: the plain implementation's norm and rotation on the sums rounded to bfloat16
+    qkv = bf16r(x.double() @ w.double().T).cpu()
+    q64 = plain.rope_rotate_half(plain.rms_norm(qkv[:, :nh * hd].reshape(M, nh, hd), qw.double().cpu(), 1e-5), pos.cpu(), theta)
+    k64 = plain.rope_rotate_half(plain.rms_norm(qkv[:, nh * hd:(nh + nkv) * hd].reshape(M, nkv, hd), kw.double().cpu(), 1e-5), pos.cpu(), theta)
+    v64 = qkv[:, (nh + nkv) * hd:].reshape(M, nkv, hd)
+    close(got, q64.reshape(M, nh * hd), torch.bfloat16, "q against 64-bit torch")
+    for t in range(M):
+        page, off = int(bt[t, pos[t] // ps]), int(pos[t]) % ps
+        close(kp_b[page, :, off], k64[t], torch.bfloat16, f"k of token {t} against 64-bit torch")
+        assert torch.equal(vp_b[page, :, off].double().cpu(), v64[t])
     # the same sums rounded at the same places (the K split may differ, hence a unit of bfloat16 rounding here and there)
     close(got, ref, torch.bfloat16, "q")
     close(kp_b, kp_a, torch.bfloat16, "keys")
