@@ -302,7 +302,7 @@ def test_qkv_product_with_norm_rotation_and_cache_write_in_its_epilogue(nh, nkv,
     for t in range(M):
         page, off = int(bt[t, pos[t] // ps]), int(pos[t]) % ps
         close(kp_b[page, :, off], k64[t], torch.bfloat16, f"k of token {t} against 64-bit torch")
-        assert torch.equal(vp_b[page, :, off].double().cpu(), v64[t])
+        close(vp_b[page, :, off], v64[t], torch.bfloat16, f"v of token {t} against 64-bit torch")
     # the same sums rounded at the same places (the K split may differ, hence a unit of bfloat16 rounding here and there)
     close(got, ref, torch.bfloat16, "q")
     close(kp_b, kp_a, torch.bfloat16, "keys")
