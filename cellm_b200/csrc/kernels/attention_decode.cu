@@ -10,11 +10,13 @@
 // (several CTAs fit an SM). The warps' partial results (maximum, sum,
 // unnormalised output) are combined through shared memory at the end.
 //
-// When the keys of a request are split over several CTAs (gridDim.z > 1), each
-// CTA leaves its piece in the workspace and adds one to the counter of its
-// (request, key/value head); the CTA that finds the counter at gridDim.z - 1
-// combines the pieces in the order of the splits, writes the output and sets
-// the counter back to zero. No CTA waits for another, and no second kernel runs.
+// When the keys of a request are split over several CTAs (gridDim.z > 1) and these are at most eight, they form
+// one thread-block cluster: each leaves its piece (maximum, sum, unnormalised output of its rows) in its own shared
+// memory, and after a cluster barrier the pieces are combined in the order of the splits by reading the peers'
+// memory, every CTA a share of the outputs. With more pieces than a cluster holds each CTA leaves its piece in the
+// workspace and adds one to the counter of its (request, key/value head); the CTA that finds the counter at
+// gridDim.z - 1 combines the pieces in the order of the splits, writes the output and sets the counter back to
+// zero. Either way no second kernel runs.
 //
 // Programmatic dependent launch: the keys and values that were in the cache before
 // this step (every block below the request's context length) are written by no
@@ -42,12 +44,28 @@ struct DecodeSmem {
     static constexpr size_t o_off = kv_off;                               // [NW][16][HD] float, over the ring once the keys are done
     static constexpr size_t ml_off = kv_off + (size_t)ST * 2 * KV_BYTES;  // [NW][16][2] float
     static constexpr size_t flag_off = ml_off + (size_t)NW * 16 * 2 * 4;
-    static constexpr size_t pages_off = flag_off + 16;                    // [bt_stride] int: this CTA's slice of the block table
+    static constexpr size_t co_off = flag_off + 16;                       // [16][HD] float: this CTA's piece for its cluster
+    static constexpr size_t cml_off = co_off + (size_t)16 * HD * 4;       // [16][2] float
+    static constexpr size_t pages_off = cml_off + 16 * 2 * 4;             // [bt_stride] int: this CTA's slice of the block table
     static constexpr size_t fixed = pages_off;
     static_assert((size_t)NW * 16 * HD * 4 <= (size_t)ST * 2 * KV_BYTES, "the warps' outputs must fit the ring");
 };
 
-template <int HD, int NW>
+__device__ __forceinline__ float ld_peer(const float* local, uint32_t rank) {
+    uint32_t addr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// CL: the CTAs of a split (gridDim.z of them, at most 8) are one cluster along z and combine their pieces through
+// shared memory.
+template <int HD, int NW, bool CL>
 __global__ void __launch_bounds__(NW * 32)
 attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ counters, const __nv_bfloat16* __restrict__ q,
@@ -62,6 +80,8 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     float* o_s = reinterpret_cast<float*>(dec_smem + L::o_off);
     float* ml_s = reinterpret_cast<float*>(dec_smem + L::ml_off);
     int* flag_s = reinterpret_cast<int*>(dec_smem + L::flag_off);
+    float* co_s = reinterpret_cast<float*>(dec_smem + L::co_off);
+    float* cml_s = reinterpret_cast<float*>(dec_smem + L::cml_off);
     int* page_s = reinterpret_cast<int*>(dec_smem + L::pages_off);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint8_t* kv_s = dec_smem + L::kv_off;
@@ -255,12 +275,35 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         const size_t gr = (size_t)(t_base + row / G) * nh + kvh * G + row % G;
         if (nsplit == 1) {
             out[gr * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else if (CL) {
+            co_s[row * HD + d] = acc;
+            if (d == 0) { cml_s[row * 2] = m; cml_s[row * 2 + 1] = l; }
         } else {
             part_o[((size_t)split * n_rows + gr) * HD + d] = acc;
             if (d == 0) { part_ml[((size_t)split * n_rows + gr) * 2] = m; part_ml[((size_t)split * n_rows + gr) * 2 + 1] = l; }
         }
     }
     if (nsplit == 1) return;
+    if constexpr (CL) {
+        // ---- the pieces of a split meet through the cluster's shared memory: every CTA combines a share of the outputs
+        cluster_sync_all();
+        for (int e = (int)split * THREADS + (int)threadIdx.x; e < rows * HD; e += nsplit * THREADS) {
+            const int row = e / HD, d = e % HD;
+            const size_t gr = (size_t)(t_base + row / G) * nh + kvh * G + row % G;
+            float m = -INFINITY;
+            for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, ld_peer(&cml_s[row * 2], (uint32_t)sp));
+            const float use = m == -INFINITY ? 0.f : m;
+            float l = 0.f, acc = 0.f;
+            for (int sp = 0; sp < nsplit; ++sp) {
+                const float f = exp2f(ld_peer(&cml_s[row * 2], (uint32_t)sp) - use);
+                l += f * ld_peer(&cml_s[row * 2 + 1], (uint32_t)sp);
+                if (f != 0.f) acc += f * ld_peer(&co_s[row * HD + d], (uint32_t)sp);
+            }
+            out[gr * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        }
+        cluster_sync_all();         // nobody leaves while a peer may still read its memory
+        return;
+    }
 
     // ---- the pieces of a split meet in the workspace; the last CTA combines them
     __threadfence();
@@ -298,23 +341,46 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, int* counte
     // the CTA's slice of a block-table row is at most the row
     const size_t smem = DecodeSmem<HD, NW>::fixed + (size_t)(bt_stride > 0 ? bt_stride : 1) * sizeof(int);
     if (smem > 200 * 1024) return CELLM_ERR_SIZE;
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const bool in_cluster = nsplit >= 2 && nsplit <= 8;
+    static size_t configured[2] = {0, 0};
+    if (smem > configured[in_cluster]) {
+        cudaError_t e = in_cluster ? cudaFuncSetAttribute(attention_decode_kernel<HD, NW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                   : cudaFuncSetAttribute(attention_decode_kernel<HD, NW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = smem;
+        configured[in_cluster] = smem;
     }
     dim3 grid((unsigned)B, (unsigned)nkv, (unsigned)nsplit);
-    CELLM_RUN((attention_decode_kernel<HD, NW>), grid, NW * 32, smem, stream, out, part_o, part_ml, counters, q, k_pool,
-              v_pool, cu, ctx, bt, bt_stride, T, num_pages, page_size, nh, nkv, scale * 1.4426950408889634f, window, err);
-    return CELLM_OK;
+    if (!in_cluster) {
+        CELLM_RUN((attention_decode_kernel<HD, NW, false>), grid, NW * 32, smem, stream, out, part_o, part_ml, counters, q, k_pool,
+                  v_pool, cu, ctx, bt, bt_stride, T, num_pages, page_size, nh, nkv, scale * 1.4426950408889634f, window, err);
+        return CELLM_OK;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NW * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;       // the pieces of a (request, key/value head) are one cluster along z
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = (unsigned)nsplit;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    const float scale_log2e = scale * 1.4426950408889634f;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, NW, true>, out, part_o, part_ml, counters, q, k_pool, v_pool, cu,
+                                       ctx, bt, bt_stride, T, num_pages, page_size, nh, nkv, scale_log2e, window, err);
+    return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
 }  // namespace
 
 // out, q: [T, nh*hd] bf16; request b owns tokens cu_seqlens[b]..cu_seqlens[b+1], at most
-// 16 / (nh / nkv) of them. nsplit > 1 needs part_o [nsplit, T*nh, hd], part_ml
-// [nsplit, T*nh, 2] floats and B*nkv zeroed counters (left zero by the call).
+// 16 / (nh / nkv) of them. nsplit > 8 needs part_o [nsplit, T*nh, hd], part_ml
+// [nsplit, T*nh, 2] floats and B*nkv zeroed counters (left zero by the call); 2 to 8 pieces meet in a thread-block
+// cluster and need none of them.
 CELLM_API int cellm_attention_decode(void* out, float* part_o, float* part_ml, int* counters, const void* q,
                                      const void* k_pool, const void* v_pool, const int* cu_seqlens,
                                      const int* ctx_lens, const int* block_table, int bt_stride, int B, int T,
@@ -322,7 +388,7 @@ CELLM_API int cellm_attention_decode(void* out, float* part_o, float* part_ml, i
                                      int nsplit, int* err, cudaStream_t stream) {
     if (T <= 0 || B <= 0) return CELLM_OK;
     if (nkv <= 0 || nh % nkv || nh / nkv > 16) return CELLM_ERR_SIZE;
-    if (nsplit < 1 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return CELLM_ERR_ARG;
+    if (nsplit < 1 || (nsplit > 8 && (!part_o || !part_ml || !counters))) return CELLM_ERR_ARG;      // up to 8 pieces meet in a cluster
     if (nkv > 65535 || nsplit > 65535) return CELLM_ERR_SIZE;
 #define GO(HD_, NW_)                                                                                                \
     return launch_decode<HD_, NW_>((__nv_bfloat16*)out, part_o, part_ml, counters, (const __nv_bfloat16*)q,         \

@@ -362,7 +362,7 @@ void* Run::attend(const AttentionParams& L, const ExecItem& it, const void* q, v
             const i64 blocks = ceil_div(s.max_total_len, 64);
             const i64 nsplit = std::max<i64>(1, std::min(4 * p.sms / (s.B * nkv), blocks / 4));
             void *part_o = nullptr, *part_ml = nullptr, *counters = nullptr;
-            if (nsplit > 1) {
+            if (nsplit > 8) {          // up to 8 pieces meet inside a thread-block cluster and need no workspace
                 if (s.B * nkv > p.max_counters) throw std::runtime_error("executor: too many (request, kv head) pairs for the counters");
                 const i64 rows = T * nh;
                 need_attn_ws = std::max(need_attn_ws, nsplit * rows * (hd + 2));

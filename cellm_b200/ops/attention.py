@@ -56,7 +56,8 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
                      err: torch.Tensor, nsplit: int = 1) -> torch.Tensor:
     """Tensor-core attention for short portions (decoded tokens): every request has
     at most 16 / (nh / kv heads) tokens in the step. One CTA per (request, kv head,
-    piece of the keys); with nsplit > 1 the last CTA of a request combines the pieces."""
+    piece of the keys). Up to 8 pieces are one thread-block cluster and are combined through its shared memory; more
+    go through a workspace, and the last CTA of a request to finish combines them."""
     require_cuda(q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, err)
     pages, nkv, page_size, hd = k_pool.shape
     T = q.shape[0]
@@ -64,7 +65,7 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
         raise ValueError("attention_decode: bfloat16 with head size 32, 64 or 128 only")
     out = torch.empty_like(q)
     part_o = part_ml = counters = None
-    if nsplit > 1:
+    if nsplit > 8:
         from ._state import MAX_COUNTERS, counters as _counters
         if B * nkv > MAX_COUNTERS:
             raise ValueError("attention_decode: too many (request, kv head) pairs for the counters")
