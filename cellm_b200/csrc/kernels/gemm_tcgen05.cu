@@ -38,10 +38,7 @@
 
 namespace {
 
-// Tokens whose pieces a CTA asks its cluster peers for at once (more in flight cost registers and gained nothing).
-#define CELLM_CLUSTER_TOKENS_IN_FLIGHT 1
-
-// RED: floats of a tile kept for the sum of K-split pieces inside a thread-block cluster.
+// RED: floats in which a CTA receives, from every CTA of its cluster, the pieces of the tokens whose sums it owns.
 template <int BN, int STAGES, int RED = 0>
 struct alignas(1024) GemmSmem {
     uint8_t a[STAGES][BM * BK * 2];
@@ -110,10 +107,13 @@ template <> __device__ __forceinline__ void store_row<__nv_bfloat16>(__nv_bfloat
 // back to zero. No CTA waits for another.
 //
 // CLUSTER (swapped tiles only): the CTAs of a tile's K split form one thread-block
-// cluster (gridDim.z of them, at most 8). Each keeps its piece in its own shared
-// memory; after a cluster barrier every CTA sums, in the order of the ranks, the
-// pieces of its share of the tile's tokens, reading the peers' memory directly, and
-// writes those outputs. No workspace, no counter, no fence to global memory.
+// cluster (gridDim.z of them, at most 8). Token t of the tile is summed by the CTA of
+// rank t mod split: every CTA stores its piece of that token straight into the owner's
+// shared memory (slot t / split of the sender's own plane, so nobody writes where
+// another does), and after one cluster barrier every CTA adds the planes of its tokens
+// in the order of the ranks, out of its own memory, and writes those outputs. No
+// workspace, no counter, no fence to global memory, and no CTA reads a peer's memory, so
+// none has to wait for the others before it leaves.
 //
 // EPI = 2 (swapped tiles in a cluster; every token of the step belongs to a request of its own):
 // the gated short convolution in the epilogue of its in_proj. W is in_proj cut into tiles of 128
@@ -137,7 +137,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     static_assert(!CLUSTER || SWAP, "the cluster reduction serves swapped tiles");
     static_assert(EPI < 2 || CLUSTER, "the convolution and rotation epilogues are written for the cluster's reduction");
     extern __shared__ uint8_t smem_raw[];
-    using Smem = GemmSmem<BN, STAGES, CLUSTER ? BN * BM : 0>;
+    using Smem = GemmSmem<BN, STAGES, CLUSTER ? (BN + 8) * BM : 0>;
     auto& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -164,6 +164,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     __syncthreads();
     tc_fence_after();
     pdl_trigger();
+    if constexpr (CLUSTER) cluster_arrive();     // this CTA runs: peers may store into its shared memory
     const uint32_t tmem = sm.tmem_base;
     volatile int* abort_flag = &sm.abort_flag;
     // EPI = 2: what an epilogue thread fetches ahead of the accumulator (see there)
@@ -275,17 +276,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         const uint32_t lane_addr = tmem + ((uint32_t)(qtr * 32) << 16);
         const bool through_ws = !CLUSTER && (splits > 1 || (EPI == 1 && SWAP));
         if constexpr (CLUSTER) {
-            // this CTA's piece, token-major: red[token of the tile][row of the tile]
+            // This CTA's piece goes to the owners of its tokens: plane `rank` of the owner's buffer, [slot][row of the tile].
             constexpr int W = BN < 32 ? 16 : 32;
+            cluster_wait();                      // every CTA of the cluster has started
+            const uint32_t rank = cluster_rank();
+            const int slots = (BN + splits - 1) / splits;           // tokens of a tile that one CTA can own
+            const int valid = min(Q - q0, BN);
+            float* plane = sm.red + (size_t)rank * slots * BM + pl;
 #pragma unroll 1
             for (int c = 0; c < BN / W; ++c) {
+                if (c * W >= valid) break;
                 uint32_t r[W];
                 if (ok) {
                     if constexpr (W == 16) tmem_ld16(lane_addr + (uint32_t)(c * W), r);
                     else tmem_ld32(lane_addr + (uint32_t)(c * W), r);
                 }
+                int owner = (c * W) % splits, slot = (c * W) / splits;
 #pragma unroll
-                for (int j = 0; j < W; ++j) sm.red[(c * W + j) * BM + pl] = ok ? __uint_as_float(r[j]) : 0.f;
+                for (int j = 0; j < W; ++j) {
+                    if (c * W + j < valid) st_peer_shared(plane + slot * BM, (uint32_t)owner, ok ? __uint_as_float(r[j]) : 0.f);
+                    if (++owner == splits) { owner = 0; ++slot; }
+                }
             }
         }
         if (ok && !through_ws && !CLUSTER) {
@@ -451,26 +462,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         }
     }
     if constexpr (CLUSTER) {
-        cluster_sync_all();                     // every piece is in its CTA's shared memory
+        if (warp < 2) cluster_wait();           // the producer's and the issuer's half of the barrier the epilogue warps passed above
+        cluster_sync_all();                     // every piece is in its owner's shared memory
         if (warp >= 2 && !*abort_flag) {
             const int pl = (warp & 3) * 32 + lane, p = p0 + pl;
             const uint32_t rank = cluster_rank();
             const int q_end = min(Q, q0 + BN);
+            const int slots = (BN + splits - 1) / splits;
+            const size_t plane = (size_t)slots * BM;                // floats between two senders' pieces of a token
             if constexpr (EPI == 3) {
                 // Tokens rank, rank + splits, ... of the tile are this CTA's, one at a time; warps 0 and 1 of the
                 // epilogue hold the tile's first head (values 0..31 and 32..63), warps 2 and 3 its second.
                 const int wl = warp & 3, i = pl & 63, half = wl & 1;
                 const int hh = p0 / 64 + (pl >> 6);
                 const int kind = hh < rope.nh ? 0 : (hh < rope.nh + rope.nkv ? 1 : (hh < rope.nh + 2 * rope.nkv ? 2 : 3));
-                for (int ql = (int)rank; q0 + ql < q_end; ql += splits) {
+                for (int ql = (int)rank, k = 0; q0 + ql < q_end; ql += splits, ++k) {
                     const int q = q0 + ql;
-                    const float* mine = &sm.red[ql * BM + pl];
-                    float v[8];
-#pragma unroll
-                    for (int r = 0; r < 8; ++r) v[r] = r < splits ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
+                    const float* mine = &sm.red[k * BM + pl];
                     float x = 0.f;
 #pragma unroll
-                    for (int r = 0; r < 8; ++r) x += v[r];
+                    for (int r = 0; r < 8; ++r) x += r < splits ? mine[r * plane] : 0.f;
                     x = __bfloat162float(__float2bfloat16_rn(x));     // as the plain product stores it
                     // the rotation of this thread's pair, meanwhile: angle = pos * (hi + lo) in split arithmetic
                     const int pos = sm.rope_pos[ql];
@@ -513,7 +524,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 const int sub = pl / CONV_CH, cl = pl % CONV_CH, ch = (p0 / BM) * CONV_CH + cl;
                 const int rows = conv.ntaps - 1;
                 if (cv_active) {
-                    for (int ql = (int)rank + sub * splits; q0 + ql < q_end; ql += 3 * splits) {
+                    for (int ql = (int)rank + sub * splits, k = sub; q0 + ql < q_end; ql += 3 * splits, k += 3) {
                         const int q = q0 + ql, slot = sm.conv_slots[ql];
                         float hist[CONV_MAX_TAPS - 1];
 #pragma unroll
@@ -527,17 +538,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                                                  ? conv.state[(long long)sn * conv.slot_stride + (size_t)k * conv.H + ch] : 0.f;
                         }
                         if (slot < 0 || slot >= conv.n_slots) { atomicOr(err, CELLM_DEV_BAD_SLOT); continue; }
-                        const float* mine = &sm.red[ql * BM + cl];
-                        float vb[8], vc[8], vx[8];
-#pragma unroll
-                        for (int r = 0; r < 8; ++r) {
-                            vb[r] = r < splits ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
-                            vc[r] = r < splits ? ld_peer_shared(mine + CONV_CH, (uint32_t)r) : 0.f;
-                            vx[r] = r < splits ? ld_peer_shared(mine + 2 * CONV_CH, (uint32_t)r) : 0.f;
-                        }
+                        const float* mine = &sm.red[k * BM + cl];
                         float b = 0.f, c = 0.f, x = 0.f;
 #pragma unroll
-                        for (int r = 0; r < 8; ++r) { b += vb[r]; c += vc[r]; x += vx[r]; }
+                        for (int r = 0; r < 8; ++r)
+                            if (r < splits) { b += mine[r * plane]; c += mine[r * plane + CONV_CH]; x += mine[r * plane + 2 * CONV_CH]; }
                         // the plain product stores B, C and x as bfloat16 before the convolution reads them
                         b = __bfloat162float(__float2bfloat16_rn(b));
                         c = __bfloat162float(__float2bfloat16_rn(c));
@@ -559,53 +564,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 }
             }
             // Tokens rank, rank + splits, ... of the tile are summed and written by this CTA.
-            // TU of this CTA's tokens at a time: all the peers' pieces of a token are asked for at once (a cluster
-            // has at most 8 CTAs), then added in the order of the ranks.
-            constexpr int TU = CELLM_CLUSTER_TOKENS_IN_FLIGHT;
-            for (int q = q0 + (int)rank; EPI < 2 && q < q_end; q += TU * splits) {
-                if constexpr (EPI == 0) {
-                    float v[TU][8];
+            if constexpr (EPI == 0) {
+                for (int q = q0 + (int)rank, k = 0; q < q_end; q += splits, ++k) {
+                    const float* mine = &sm.red[k * BM + pl];
+                    float acc = 0.f;
 #pragma unroll
-                    for (int t = 0; t < TU; ++t) {
-                        const int qt = q + t * splits;
-                        const float* mine = &sm.red[(qt - q0) * BM + pl];
+                    for (int r = 0; r < 8; ++r) acc += r < splits ? mine[r * plane] : 0.f;
+                    if (p < P) C[(size_t)q * ldc + p] = from_float<TO>(acc);
+                }
+            }
+            if constexpr (EPI == 1) {
+                // an output is silu(gate) * up of rows i and i + 64 of the tile: the lower 64 threads take this
+                // CTA's even tokens, the upper 64 its odd ones
+                const int row = pl & 63, half = pl >> 6;
+                for (int q = q0 + (int)rank + half * splits, k = half; q < q_end; q += 2 * splits, k += 2) {
+                    const float* mine = &sm.red[k * BM + row];
+                    float g = 0.f, u = 0.f;
 #pragma unroll
-                        for (int r = 0; r < 8; ++r) v[t][r] = (qt < q_end && r < splits) ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
-                    }
-#pragma unroll
-                    for (int t = 0; t < TU; ++t) {
-                        const int qt = q + t * splits;
-                        float acc = 0.f;
-#pragma unroll
-                        for (int r = 0; r < 8; ++r) acc += v[t][r];
-                        if (qt < q_end && p < P) C[(size_t)qt * ldc + p] = from_float<TO>(acc);
-                    }
-                } else {
-                    if (pl < 64) {
-                        float vg[TU][8], vu[TU][8];
-#pragma unroll
-                        for (int t = 0; t < TU; ++t) {
-                            const int qt = q + t * splits;
-                            const float* mine = &sm.red[(qt - q0) * BM + pl];
-#pragma unroll
-                            for (int r = 0; r < 8; ++r) {
-                                vg[t][r] = (qt < q_end && r < splits) ? ld_peer_shared(mine, (uint32_t)r) : 0.f;
-                                vu[t][r] = (qt < q_end && r < splits) ? ld_peer_shared(mine + 64, (uint32_t)r) : 0.f;
-                            }
-                        }
-#pragma unroll
-                        for (int t = 0; t < TU; ++t) {
-                            const int qt = q + t * splits;
-                            float g = 0.f, u = 0.f;
-#pragma unroll
-                            for (int r = 0; r < 8; ++r) { g += vg[t][r]; u += vu[t][r]; }
-                            if (qt < q_end && p + 64 < P) C[(size_t)qt * ldc + (p0 / 2 + pl)] = from_float<TO>(silu_mul(g, u));
-                        }
-                    }
+                    for (int r = 0; r < 8; ++r)
+                        if (r < splits) { g += mine[r * plane]; u += mine[r * plane + 64]; }
+                    if (p0 + row + 64 < P) C[(size_t)q * ldc + (p0 / 2 + row)] = from_float<TO>(silu_mul(g, u));
                 }
             }
         }
-        cluster_sync_all();                     // nobody leaves while a peer may still read its memory
     }
     tc_fence_before();
     __syncthreads();
@@ -840,7 +821,7 @@ template <int BN, int STAGES, bool SWAP, int EPI, bool CLUSTER, typename TO>
 int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* ws, int* counters, int M, int N, int K,
            long long ldc, int split_k, int kblocks_per_split, int w_is_static, int* err, cudaStream_t stream,
            const ConvEpi& conv, const RopeEpi& rope) {
-    const size_t smem = sizeof(GemmSmem<BN, STAGES, CLUSTER ? BN * BM : 0>) + 1024;
+    const size_t smem = sizeof(GemmSmem<BN, STAGES, CLUSTER ? (BN + 8) * BM : 0>) + 1024;
     static bool configured = false;
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, EPI, CLUSTER, TO>;
     if (!configured) {
