@@ -77,6 +77,9 @@ __global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const __nv_bfloat
             *reinterpret_cast<float4*>(x + (size_t)t * H + i0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
         }
     }
+    float wv[8];                 // the weights travel while the row's sum is taken
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wv[j] = on ? to_float(w[i0 + j]) : 0.f;
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
@@ -86,8 +89,7 @@ __global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const __nv_bfloat
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            __nv_bfloat162 pk = __floats2bfloat162_rn(v[2 * j] * inv * to_float(w[i0 + 2 * j]),
-                                                      v[2 * j + 1] * inv * to_float(w[i0 + 2 * j + 1]));
+            __nv_bfloat162 pk = __floats2bfloat162_rn(v[2 * j] * inv * wv[2 * j], v[2 * j + 1] * inv * wv[2 * j + 1]);
             o[j] = *reinterpret_cast<uint32_t*>(&pk);
         }
         *reinterpret_cast<uint4*>(y + (size_t)r * H + i0) = make_uint4(o[0], o[1], o[2], o[3]);

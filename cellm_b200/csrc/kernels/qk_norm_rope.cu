@@ -121,6 +121,21 @@ qk_norm_rope_hd64_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16*
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
     if (t >= T) return;
+    // The token's values are asked for first (the launcher gives a block at most sixteen heads: four rounds of four), so
+    // that they travel while the cosines, the weights and the page are looked up.
+    const int chunk = lane & 7;              // values 8 * chunk .. 8 * chunk + 7 of the head
+    const __nv_bfloat16* row = qkv + (size_t)t * row_stride;
+    // blockIdx.y takes a run of the token's heads: queries, then keys, then values
+    const int all = nh + 2 * nkv;
+    const int per = ((all + gridDim.y - 1) / gridDim.y + 3) / 4 * 4;
+    const int h_begin = blockIdx.y * per, h_end = min(all, h_begin + per);
+    uint4 ahead[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int hh = h_begin + 4 * r + (lane >> 3);
+        ahead[r] = make_uint4(0, 0, 0, 0);
+        if (hh < h_end) ahead[r] = *reinterpret_cast<const uint4*>(row + (size_t)hh * 64 + chunk * 8);
+    }
     const int pos = positions[t];
     {
         const float hi = inv_freq[2 * lane], lo = inv_freq[2 * lane + 1], fp = (float)pos;
@@ -133,7 +148,6 @@ qk_norm_rope_hd64_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16*
         trig[warp][32 + lane] = s * ce + c * se;
     }
     __syncwarp();
-    const int chunk = lane & 7;              // values 8 * chunk .. 8 * chunk + 7 of the head
     const int f0 = (chunk & 3) * 8;          // their frequencies (value i turns with frequency i mod 32)
     float cs[8], sn[8], wq[8], wk[8];
 #pragma unroll
@@ -151,17 +165,13 @@ qk_norm_rope_hd64_kernel(__nv_bfloat16* __restrict__ q_out, const __nv_bfloat16*
         if (page < 0 || page >= num_pages) { if (lane == 0) atomicOr(err, CELLM_DEV_BAD_PAGE); }
         else page_base = (long long)page * nkv * page_size * 64 + (long long)(pos % page_size) * 64;
     }
-    const __nv_bfloat16* row = qkv + (size_t)t * row_stride;
-    // blockIdx.y takes a run of the token's heads: queries, then keys, then values
-    const int all = nh + 2 * nkv;
-    const int per = ((all + gridDim.y - 1) / gridDim.y + 3) / 4 * 4;
-    const int h_begin = blockIdx.y * per, h_end = min(all, h_begin + per);
-#pragma unroll 2
-    for (int h0 = h_begin; h0 < h_end; h0 += 4) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int h0 = h_begin + 4 * r;
+        if (h0 >= h_end) break;
         const int hh = h0 + (lane >> 3);
         const bool on = hh < h_end;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (on) raw = *reinterpret_cast<const uint4*>(row + (size_t)hh * 64 + chunk * 8);
+        const uint4 raw = ahead[r];
         const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
         float v[8];
         {
