@@ -11,9 +11,9 @@
 // unnormalised output) are combined through shared memory at the end.
 //
 // When the keys of a request are split over several CTAs (gridDim.z > 1) and these are at most eight, they form
-// one thread-block cluster: each leaves its piece (maximum, sum, unnormalised output of its rows) in its own shared
-// memory, and after a cluster barrier the pieces are combined in the order of the splits by reading the peers'
-// memory, every CTA a share of the outputs. With more pieces than a cluster holds each CTA leaves its piece in the
+// one thread-block cluster: every CTA owns a share of the outputs, the others store their pieces (maximum, sum,
+// unnormalised output) of that share into its shared memory, and after a cluster barrier it combines them in the
+// order of the splits. With more pieces than a cluster holds each CTA leaves its piece in the
 // workspace and adds one to the counter of its (request, key/value head); the CTA that finds the counter at
 // gridDim.z - 1 combines the pieces in the order of the splits, writes the output and sets the counter back to
 // zero. Either way no second kernel runs.
@@ -35,36 +35,39 @@
 
 namespace {
 
-template <int HD, int NW>
+template <int HD, int NW, bool CL>
 struct DecodeSmem {
     static constexpr int KV_BYTES = FA_BN * HD * 2;
     static constexpr int ST = HD <= 64 ? 3 : 2;                           // stages of the ring
-    static constexpr size_t q_off = 0;
+    static constexpr size_t q_off = 0;                                    // [16][HD] bfloat16, until the fragments are in registers
     static constexpr size_t kv_off = 16 * HD * 2;                         // [ST stages][K | V]
     static constexpr size_t o_off = kv_off;                               // [NW][16][HD] float, over the ring once the keys are done
-    static constexpr size_t ml_off = kv_off + (size_t)ST * 2 * KV_BYTES;  // [NW][16][2] float
-    static constexpr size_t flag_off = ml_off + (size_t)NW * 16 * 2 * 4;
-    static constexpr size_t co_off = flag_off + 16;                       // [16][HD] float: this CTA's piece for its cluster
-    static constexpr size_t cml_off = co_off + (size_t)16 * HD * 4;       // [16][2] float
-    static constexpr size_t pages_off = cml_off + 16 * 2 * 4;             // [bt_stride] int: this CTA's slice of the block table
+    static constexpr size_t ml_off = o_off + (size_t)NW * 16 * HD * 4;    // [NW][16][2] float, over the ring as well
+    static constexpr size_t flag_off = kv_off + (size_t)ST * 2 * KV_BYTES;
+    // What a CTA receives from its cluster (CL). Of the outputs it owns (runs of 32 elements of the 16 x HD tile, dealt
+    // out in turn) every sender's piece, [sender][owned element]; and every sender's maximum and sum of all 16 rows,
+    // [8 senders][16][2] floats, where the queries lay: a CTA tells its cluster that it runs only after it has taken
+    // its queries into registers, and nobody stores into a peer before all have told.
+    static constexpr size_t co_off = flag_off + 16;
+    static constexpr size_t cml_off = q_off;
+    static constexpr size_t pages_off = co_off + (CL ? (size_t)(16 * HD + 7 * 32) * 4 : 0);   // [bt_stride] int: this CTA's slice of the block table
     static constexpr size_t fixed = pages_off;
-    static_assert((size_t)NW * 16 * HD * 4 <= (size_t)ST * 2 * KV_BYTES, "the warps' outputs must fit the ring");
+    static_assert((size_t)NW * 16 * (HD + 2) * 4 <= (size_t)ST * 2 * KV_BYTES, "the warps' outputs must fit the ring");
+    static_assert(!CL || 8 * 16 * 2 * 4 <= 16 * HD * 2, "the senders' maxima and sums must fit the queries' place");
 };
 
-__device__ __forceinline__ float ld_peer(const float* local, uint32_t rank) {
+// A float into the same place of the shared memory of CTA `rank` of this cluster.
+__device__ __forceinline__ void st_peer(float* local, uint32_t rank, float v) {
     uint32_t addr;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
-    return v;
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
-// CL: the CTAs of a split (gridDim.z of them, at most 8) are one cluster along z and combine their pieces through
-// shared memory.
+// CL: the CTAs of a split (gridDim.z of them, at most 8) are one cluster along z. Every CTA owns a share of the
+// outputs; the others store their pieces of that share straight into its shared memory, and after one cluster barrier
+// it combines them out of its own memory.
 template <int HD, int NW, bool CL>
 __global__ void __launch_bounds__(NW * 32)
 attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
@@ -74,7 +77,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const int* __restrict__ block_table, int bt_stride, int T, int num_pages, int page_size,
                         int nh, int nkv, float scale_log2e, int window, int* __restrict__ err) {
     constexpr int BN = FA_BN, CH = HD / 8, NT = HD / 8;
-    using L = DecodeSmem<HD, NW>;
+    using L = DecodeSmem<HD, NW, CL>;
     extern __shared__ __align__(128) uint8_t dec_smem[];
     uint8_t* q_s = dec_smem + L::q_off;
     float* o_s = reinterpret_cast<float*>(dec_smem + L::o_off);
@@ -151,6 +154,9 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks)
         ldmatrix_x4(qf[ks], q_s + tile_offset<HD>(lane & 15, ks * 2 + (lane >> 4)));
+    // this CTA runs and is done with its queries' place: its peers may store into its shared memory (the barrier's
+    // other half comes before the first such store)
+    if constexpr (CL) cluster_arrive();
 
     const int row_a = lane >> 2, row_b = row_a + 8;
     const int pos_a = row_a < rows ? ctx + row_a / G : -1, pos_b = row_b < rows ? ctx + row_b / G : -1;
@@ -258,6 +264,11 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     }
     __syncthreads();
     const size_t n_rows = (size_t)T * nh;
+    // CL: runs of 32 elements are dealt out to the CTAs in turn; `chunks_mine` of them, 32 floats each, lie side by
+    // side in a sender's plane of the owner's buffer
+    const int chunks = (rows * HD + 31) / 32;
+    const int plane = ((chunks + nsplit - 1) / nsplit) * 32;
+    if constexpr (CL) { if (nsplit > 1) cluster_wait(); }          // every CTA of the cluster has started
     // element e = (row, dim) of the 16 x HD tile, owned by thread e mod (NW*32)
     for (int e = threadIdx.x; e < rows * HD; e += NW * 32) {
         const int row = e / HD, d = e % HD;
@@ -276,8 +287,13 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         if (nsplit == 1) {
             out[gr * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         } else if (CL) {
-            co_s[row * HD + d] = acc;
-            if (d == 0) { cml_s[row * 2] = m; cml_s[row * 2 + 1] = l; }
+            const int chunk = e >> 5;
+            st_peer(co_s + split * plane + (chunk / nsplit) * 32 + (e & 31), (uint32_t)(chunk % nsplit), acc);
+            if (d == 0)
+                for (int to = 0; to < nsplit; ++to) {
+                    st_peer(cml_s + (split * 16 + row) * 2, (uint32_t)to, m);
+                    st_peer(cml_s + (split * 16 + row) * 2 + 1, (uint32_t)to, l);
+                }
         } else {
             part_o[((size_t)split * n_rows + gr) * HD + d] = acc;
             if (d == 0) { part_ml[((size_t)split * n_rows + gr) * 2] = m; part_ml[((size_t)split * n_rows + gr) * 2 + 1] = l; }
@@ -285,24 +301,30 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     }
     if (nsplit == 1) return;
     if constexpr (CL) {
-        // ---- the pieces of a split meet through the cluster's shared memory: every CTA combines a share of the outputs
-        cluster_sync_all();
-        for (int e = (int)split * THREADS + (int)threadIdx.x; e < rows * HD; e += nsplit * THREADS) {
-            const int row = e / HD, d = e % HD;
-            const size_t gr = (size_t)(t_base + row / G) * nh + kvh * G + row % G;
-            float m = -INFINITY;
-            for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, ld_peer(&cml_s[row * 2], (uint32_t)sp));
-            const float use = m == -INFINITY ? 0.f : m;
-            float l = 0.f, acc = 0.f;
-            for (int sp = 0; sp < nsplit; ++sp) {
-                const float f = exp2f(ld_peer(&cml_s[row * 2], (uint32_t)sp) - use);
-                l += f * ld_peer(&cml_s[row * 2 + 1], (uint32_t)sp);
-                if (f != 0.f) acc += f * ld_peer(&co_s[row * HD + d], (uint32_t)sp);
+        // ---- one barrier, then every CTA combines the outputs it owns, in the order of the splits
+        cluster_arrive();
+        cluster_wait();
+        const int mine = (chunks - split + nsplit - 1) / nsplit;          // runs of 32 that this CTA owns
+        for (int idx = threadIdx.x; idx < mine * 32; idx += THREADS) {
+            {
+                const int k = idx >> 5, i = idx & 31;
+                const int e = (split + k * nsplit) * 32 + i;
+                if (e >= rows * HD) continue;
+                const int row = e / HD, d = e % HD;
+                const size_t gr = (size_t)(t_base + row / G) * nh + kvh * G + row % G;
+                float m = -INFINITY;
+                for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, cml_s[(sp * 16 + row) * 2]);
+                const float use = m == -INFINITY ? 0.f : m;
+                float l = 0.f, acc = 0.f;
+                for (int sp = 0; sp < nsplit; ++sp) {
+                    const float f = exp2f(cml_s[(sp * 16 + row) * 2] - use);
+                    l += f * cml_s[(sp * 16 + row) * 2 + 1];
+                    if (f != 0.f) acc += f * co_s[sp * plane + k * 32 + i];
+                }
+                out[gr * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
             }
-            out[gr * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         }
-        cluster_sync_all();         // nobody leaves while a peer may still read its memory
-        return;
+        return;             // nobody reads a peer's memory: a CTA may leave before the others have finished
     }
 
     // ---- the pieces of a split meet in the workspace; the last CTA combines them
@@ -339,9 +361,9 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, int* counte
                   int bt_stride, int B, int T, int num_pages, int page_size, int nh, int nkv, float scale, int window,
                   int nsplit, int* err, cudaStream_t stream) {
     // the CTA's slice of a block-table row is at most the row
-    const size_t smem = DecodeSmem<HD, NW>::fixed + (size_t)(bt_stride > 0 ? bt_stride : 1) * sizeof(int);
-    if (smem > 200 * 1024) return CELLM_ERR_SIZE;
     const bool in_cluster = nsplit >= 2 && nsplit <= 8;
+    const size_t smem = (in_cluster ? DecodeSmem<HD, NW, true>::fixed : DecodeSmem<HD, NW, false>::fixed) + (size_t)(bt_stride > 0 ? bt_stride : 1) * sizeof(int);
+    if (smem > 200 * 1024) return CELLM_ERR_SIZE;
     static size_t configured[2] = {0, 0};
     if (smem > configured[in_cluster]) {
         cudaError_t e = in_cluster ? cudaFuncSetAttribute(attention_decode_kernel<HD, NW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
