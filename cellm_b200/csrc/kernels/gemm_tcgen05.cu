@@ -150,6 +150,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     const int kb1 = min(kb0 + kblocks_per_split, kblocks_total);
     const int nkb = kb1 - kb0;           // > 0 by construction of the grid
 
+    pdl_trigger();                       // the next kernel may set itself up beside this one
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
         mbar_init(&sm.acc_full, 1);
@@ -163,7 +164,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    pdl_trigger();
     if constexpr (CLUSTER) cluster_arrive();     // this CTA runs: peers may store into its shared memory
     const uint32_t tmem = sm.tmem_base;
     volatile int* abort_flag = &sm.abort_flag;
