@@ -13,23 +13,12 @@
 // When the keys of a request are split over several CTAs (gridDim.z > 1) and these are at most eight, they form
 // one thread-block cluster: every CTA owns a share of the outputs, the others store their pieces (maximum, sum,
 // unnormalised output) of that share into its shared memory, and after a cluster barrier it combines them in the
-// order of the splits. With more pieces than a cluster holds each CTA leaves its piece in the
-// workspace and adds one to the counter of its (request, key/value head); the CTA that finds the counter at
-// gridDim.z - 1 combines the pieces in the order of the splits, writes the output and sets the counter back to
-// zero. Either way no second kernel runs.
-//
-// Programmatic dependent launch: the keys and values that were in the cache before
-// this step (every block below the request's context length) are written by no
-// kernel of this step, so their copies (and the look-ups of the block table, which
-// the step's first copy from the host filled) go out before the wait on the kernel
-// before this one; only the queries and the blocks that hold this step's tokens
-// come after it. Most of a request's cache is on its way, or there, when the
-// queries arrive.
-//
-// Scores, mask and softmax are as in the flash kernel for prompts
-// (attention_flash.cu): q.k * scale, key <= the token's position, optional
-// window, 32-bit online softmax, probabilities rounded to bfloat16 for P.V.
-// Cache layout of one layer: [page][kv_head][slot in page][head_dim].
+// order of the splits. A multiple of eight pieces forms clusters of eight that do the same, and each cluster
+// leaves one piece in the workspace; other counts leave a piece per CTA there. A CTA that has left its piece adds one
+// to the counter of its (request, key/value head); the one that finds the counter at gridDim.z - 1 combines the
+// workspace's pieces in their order, writes the output and sets the counter back to zero. Either way no second
+// kernel runs.
+#include <algorithm>
 #include "common.cuh"
 #include "mma_tiles.cuh"
 
@@ -65,9 +54,10 @@ __device__ __forceinline__ void st_peer(float* local, uint32_t rank, float v) {
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
-// CL: the CTAs of a split (gridDim.z of them, at most 8) are one cluster along z. Every CTA owns a share of the
-// outputs; the others store their pieces of that share straight into its shared memory, and after one cluster barrier
-// it combines them out of its own memory.
+// CL: the CTAs of a split are clusters of cs = min(gridDim.z, 8) along z. Every CTA owns a share of the outputs; the
+// others of its cluster store their pieces of that share straight into its shared memory, and after one cluster
+// barrier it combines them out of its own memory. With several clusters the result is the cluster's piece in the
+// workspace.
 template <int HD, int NW, bool CL>
 __global__ void __launch_bounds__(NW * 32)
 attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
@@ -96,9 +86,14 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     pdl_trigger();
     const int t_base = cu_seqlens[b], q_len = cu_seqlens[b + 1] - t_base, rows = q_len * G;   // rows <= 16
     const int ctx = ctx_lens[b];
-    const int key_end = ctx + q_len;
+    // keys beyond what a row of the block table can name are reported and left out (the CTA's slice of the table in
+    // shared memory is sized from the row)
+    const int key_end = min(ctx + q_len, bt_stride * page_size);
+    if (ctx + q_len > key_end && threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_PAGE);
     const int key_begin = window > 0 ? max(0, ctx - window + 1) : 0;
     const int kb_begin = key_begin / BN, kb_end = (key_end + BN - 1) / BN;
+    const int cs = CL ? min(nsplit, 8) : 1;           // CTAs of a cluster, this CTA's rank in it, clusters
+    const int crank = split % cs, n_clusters = nsplit / cs, cid = split / cs;
     const int per = (kb_end - kb_begin + nsplit - 1) / nsplit;
     const int my_begin = kb_begin + split * per, my_end = min(kb_end, my_begin + per);
     const int* bt = block_table + (size_t)b * bt_stride;
@@ -267,7 +262,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     // CL: runs of 32 elements are dealt out to the CTAs in turn; `chunks_mine` of them, 32 floats each, lie side by
     // side in a sender's plane of the owner's buffer
     const int chunks = (rows * HD + 31) / 32;
-    const int plane = ((chunks + nsplit - 1) / nsplit) * 32;
+    const int plane = ((chunks + cs - 1) / cs) * 32;
     if constexpr (CL) { if (nsplit > 1) cluster_wait(); }          // every CTA of the cluster has started
     // element e = (row, dim) of the 16 x HD tile, owned by thread e mod (NW*32)
     for (int e = threadIdx.x; e < rows * HD; e += NW * 32) {
@@ -288,11 +283,11 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
             out[gr * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         } else if (CL) {
             const int chunk = e >> 5;
-            st_peer(co_s + split * plane + (chunk / nsplit) * 32 + (e & 31), (uint32_t)(chunk % nsplit), acc);
+            st_peer(co_s + crank * plane + (chunk / cs) * 32 + (e & 31), (uint32_t)(chunk % cs), acc);
             if (d == 0)
-                for (int to = 0; to < nsplit; ++to) {
-                    st_peer(cml_s + (split * 16 + row) * 2, (uint32_t)to, m);
-                    st_peer(cml_s + (split * 16 + row) * 2 + 1, (uint32_t)to, l);
+                for (int to = 0; to < cs; ++to) {
+                    st_peer(cml_s + (crank * 16 + row) * 2, (uint32_t)to, m);
+                    st_peer(cml_s + (crank * 16 + row) * 2 + 1, (uint32_t)to, l);
                 }
         } else {
             part_o[((size_t)split * n_rows + gr) * HD + d] = acc;
@@ -304,27 +299,31 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         // ---- one barrier, then every CTA combines the outputs it owns, in the order of the splits
         cluster_arrive();
         cluster_wait();
-        const int mine = (chunks - split + nsplit - 1) / nsplit;          // runs of 32 that this CTA owns
+        const int mine = (chunks - crank + cs - 1) / cs;          // runs of 32 that this CTA owns
         for (int idx = threadIdx.x; idx < mine * 32; idx += THREADS) {
-            {
-                const int k = idx >> 5, i = idx & 31;
-                const int e = (split + k * nsplit) * 32 + i;
-                if (e >= rows * HD) continue;
-                const int row = e / HD, d = e % HD;
-                const size_t gr = (size_t)(t_base + row / G) * nh + kvh * G + row % G;
-                float m = -INFINITY;
-                for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, cml_s[(sp * 16 + row) * 2]);
-                const float use = m == -INFINITY ? 0.f : m;
-                float l = 0.f, acc = 0.f;
-                for (int sp = 0; sp < nsplit; ++sp) {
-                    const float f = exp2f(cml_s[(sp * 16 + row) * 2] - use);
-                    l += f * cml_s[(sp * 16 + row) * 2 + 1];
-                    if (f != 0.f) acc += f * co_s[sp * plane + k * 32 + i];
-                }
+            const int k = idx >> 5, i = idx & 31;
+            const int e = (crank + k * cs) * 32 + i;
+            if (e >= rows * HD) continue;
+            const int row = e / HD, d = e % HD;
+            const size_t gr = (size_t)(t_base + row / G) * nh + kvh * G + row % G;
+            float m = -INFINITY;
+            for (int sp = 0; sp < cs; ++sp) m = fmaxf(m, cml_s[(sp * 16 + row) * 2]);
+            const float use = m == -INFINITY ? 0.f : m;
+            float l = 0.f, acc = 0.f;
+            for (int sp = 0; sp < cs; ++sp) {
+                const float f = exp2f(cml_s[(sp * 16 + row) * 2] - use);
+                l += f * cml_s[(sp * 16 + row) * 2 + 1];
+                if (f != 0.f) acc += f * co_s[sp * plane + k * 32 + i];
+            }
+            if (n_clusters == 1) {
                 out[gr * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+            } else {            // the cluster's piece
+                part_o[((size_t)cid * n_rows + gr) * HD + d] = acc;
+                if (d == 0) { part_ml[((size_t)cid * n_rows + gr) * 2] = m; part_ml[((size_t)cid * n_rows + gr) * 2 + 1] = l; }
             }
         }
-        return;             // nobody reads a peer's memory: a CTA may leave before the others have finished
+        // nobody reads a peer's memory: a CTA may leave before the others of its cluster have finished
+        if (n_clusters == 1) return;
     }
 
     // ---- the pieces of a split meet in the workspace; the last CTA combines them
@@ -339,14 +338,15 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     __syncthreads();
     if (*flag_s == 0) return;
     __threadfence();
+    const int pieces = CL ? n_clusters : nsplit;
     for (int e = threadIdx.x; e < rows * HD; e += NW * 32) {
         const int row = e / HD, d = e % HD;
         const size_t gr = (size_t)(t_base + row / G) * nh + kvh * G + row % G;
         float m = -INFINITY;
-        for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, part_ml[((size_t)sp * n_rows + gr) * 2]);
+        for (int sp = 0; sp < pieces; ++sp) m = fmaxf(m, part_ml[((size_t)sp * n_rows + gr) * 2]);
         const float use = m == -INFINITY ? 0.f : m;
         float l = 0.f, acc = 0.f;
-        for (int sp = 0; sp < nsplit; ++sp) {
+        for (int sp = 0; sp < pieces; ++sp) {
             const float f = exp2f(part_ml[((size_t)sp * n_rows + gr) * 2] - use);
             l += f * part_ml[((size_t)sp * n_rows + gr) * 2 + 1];
             if (f != 0.f) acc += f * part_o[((size_t)sp * n_rows + gr) * HD + d];
@@ -361,8 +361,13 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, int* counte
                   int bt_stride, int B, int T, int num_pages, int page_size, int nh, int nkv, float scale, int window,
                   int nsplit, int* err, cudaStream_t stream) {
     // the CTA's slice of a block-table row is at most the row
-    const bool in_cluster = nsplit >= 2 && nsplit <= 8;
-    const size_t smem = (in_cluster ? DecodeSmem<HD, NW, true>::fixed : DecodeSmem<HD, NW, false>::fixed) + (size_t)(bt_stride > 0 ? bt_stride : 1) * sizeof(int);
+    const bool in_cluster = nsplit >= 2 && (nsplit <= 8 || nsplit % 8 == 0);     // clusters of nsplit, or of eight
+    // A CTA keeps the block-table entries of its own keys: at most its share of the blocks a row of the table can
+    // name (a page more at either end where a block's edge is not a page's), and never more than the row.
+    const long long row_blocks = ((long long)(bt_stride > 0 ? bt_stride : 1) * page_size + FA_BN - 1) / FA_BN;
+    const long long share = (row_blocks + nsplit - 1) / nsplit;
+    const long long slice = std::min<long long>(bt_stride > 0 ? bt_stride : 1, share * FA_BN / page_size + 2);
+    const size_t smem = (in_cluster ? DecodeSmem<HD, NW, true>::fixed : DecodeSmem<HD, NW, false>::fixed) + (size_t)slice * sizeof(int);
     if (smem > 200 * 1024) return CELLM_ERR_SIZE;
     static size_t configured[2] = {0, 0};
     if (smem > configured[in_cluster]) {
@@ -388,7 +393,7 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, int* counte
     attr[1].id = cudaLaunchAttributeClusterDimension;       // the pieces of a (request, key/value head) are one cluster along z
     attr[1].val.clusterDim.x = 1;
     attr[1].val.clusterDim.y = 1;
-    attr[1].val.clusterDim.z = (unsigned)nsplit;
+    attr[1].val.clusterDim.z = (unsigned)(nsplit <= 8 ? nsplit : 8);
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     const float scale_log2e = scale * 1.4426950408889634f;
@@ -401,8 +406,8 @@ int launch_decode(__nv_bfloat16* out, float* part_o, float* part_ml, int* counte
 
 // out, q: [T, nh*hd] bf16; request b owns tokens cu_seqlens[b]..cu_seqlens[b+1], at most
 // 16 / (nh / nkv) of them. nsplit > 8 needs part_o [nsplit, T*nh, hd], part_ml
-// [nsplit, T*nh, 2] floats and B*nkv zeroed counters (left zero by the call); 2 to 8 pieces meet in a thread-block
-// cluster and need none of them.
+// [nsplit, T*nh, 2] floats (a multiple of eight uses the first nsplit / 8 of them) and B*nkv zeroed counters (left
+// zero by the call); 2 to 8 pieces meet in a thread-block cluster and need none of them.
 CELLM_API int cellm_attention_decode(void* out, float* part_o, float* part_ml, int* counters, const void* q,
                                      const void* k_pool, const void* v_pool, const int* cu_seqlens,
                                      const int* ctx_lens, const int* block_table, int bt_stride, int B, int T,

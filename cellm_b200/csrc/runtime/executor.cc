@@ -360,7 +360,13 @@ void* Run::attend(const AttentionParams& L, const ExecItem& it, const void* q, v
         if (s.max_q_len * G <= 16) {
             // decoded tokens: one CTA per (request, kv head, piece of the keys)
             const i64 blocks = ceil_div(s.max_total_len, 64);
-            const i64 nsplit = std::max<i64>(1, std::min(4 * p.sms / (s.B * nkv), blocks / 4));
+            // Pieces of the keys: as many as fill four CTAs an SM, of four blocks of 64 keys or more. Where that asks for
+            // more than one cluster of eight, pieces of two blocks and a multiple of eight of them: clusters of eight
+            // combine their pieces in shared memory and only one piece a cluster goes through the workspace.
+            const i64 fill = 4 * p.sms / (s.B * nkv);
+            i64 nsplit = std::max<i64>(1, std::min(fill, blocks / 4));
+            if (blocks / 4 > 8) nsplit = std::max<i64>(1, std::min(fill, blocks / 2));
+            if (nsplit >= 16) nsplit = nsplit / 8 * 8;
             void *part_o = nullptr, *part_ml = nullptr, *counters = nullptr;
             if (nsplit > 8) {          // up to 8 pieces meet inside a thread-block cluster and need no workspace
                 if (s.B * nkv > p.max_counters) throw std::runtime_error("executor: too many (request, kv head) pairs for the counters");

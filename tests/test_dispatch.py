@@ -42,6 +42,21 @@ def test_decode_step(monkeypatch):
     assert (dec[11], dec[12]) == (8, 8) and 2 <= dec[20] <= 8 and dec[1] is None      # keys split over the CTAs of a cluster
 
 
+def test_decode_attention_pieces_by_batch_and_context(monkeypatch):
+    """How many pieces the keys of a request are cut into: one cluster of up to 8 for short contexts, a multiple
+    of 8 (clusters of eight, a piece per cluster through the workspace) where few requests have long contexts,
+    and what fills four CTAs an SM otherwise."""
+    rec = Recorder(monkeypatch)
+    cfg, plan, model = zero_model(WIDE)
+    for lens, want in (([2048], 8), ([4096], 32), ([8192], 64), ([32768], 72), ([8192] * 2, 32), ([32768] * 8, 9),
+                       ([2048] * 64, 1)):
+        rec.calls.clear()
+        run_step(model, plan, [1] * len(lens), lens)
+        dec = rec.of("cellm_attention_decode")[0]
+        assert dec[20] == want, (lens, dec[20])
+        assert (dec[1] is not None) == (want > 8)                  # a workspace only beyond one cluster
+
+
 def test_decode_step_without_the_fused_decode_kernels(monkeypatch):
     from cellm_b200.runtime import program
     monkeypatch.setitem(program.OPTIONS, "fused_rope", False)

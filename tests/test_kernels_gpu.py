@@ -494,15 +494,16 @@ def test_attention_tc_refuses_what_it_does_not_take():
 @pytest.mark.parametrize("window", [0, 33])
 def test_attention_decode(hd, ps, nh, nkv, window):
     """Decoded tokens (and portions of two or three where the group is small)
-    through the kernel with a ring per warp: unsplit, split over the CTAs of a cluster (up to 8 pieces), and split
-    into more pieces than a cluster holds (through the workspace and the counters)."""
+    through the kernel with a ring per warp: unsplit, split over the CTAs of a cluster (up to 8 pieces), split
+    into more pieces than a cluster holds (11: a piece per CTA through the workspace and the counters; 16: two
+    clusters of eight, a piece per cluster through the workspace)."""
     from cellm_b200.ops.attention import attention_decode
     G = nh // nkv
     few = max(1, min(3, 16 // G))
     c = paged_case([1, few, 1, 1, 1], [3, 700, 64, 255, 1000], nh, nkv, hd, ps, torch.bfloat16, seed=5)
     ref = attention_reference(c, nh, nkv, hd, hd ** -0.5, window)
     e = err_word()
-    for nsplit in (1, 2, 5, 8, 11):
+    for nsplit in (1, 2, 5, 8, 11, 16):
         for _ in range(2):            # twice: the counters must be back at zero
             out = attention_decode(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], 5, nh, hd ** -0.5, window, e, nsplit)
             close(out, ref, torch.bfloat16, f"nsplit {nsplit}")
