@@ -191,7 +191,7 @@ def time_prefill(loaded, rng, reps=5, warmup=3):
 
 def profile_region(loaded, args, rng) -> int:
     """One decode step of the batch (launched kernel by kernel, no graph) or one
-    2,048-token prefill between cudaProfilerStart and cudaProfilerStop."""
+    prefill (2,048 tokens unless --profile-tokens says fewer) between cudaProfilerStart and cudaProfilerStop."""
     import torch
     from cellm_b200.engine import StepEntry
     if args.profile_region == "decode":
@@ -206,12 +206,13 @@ def profile_region(loaded, args, rng) -> int:
         cache = CacheManager(model.cache_needs(), [e.cache_of for e in plan.order], PAGE, 4 * (PROMPT_LEN // PAGE + 1), 4,
                              model.dtype, model.device)
         runner = StepRunner(model, cache)
-        toks = rng.integers(0, plan.vocab_size, PROMPT_LEN).tolist()
+        n_tok = max(1, min(args.profile_tokens, PROMPT_LEN))
+        toks = rng.integers(0, plan.vocab_size, n_tok).tolist()
         counter = [0]
 
         def step():
             cache.add(counter[0])
-            runner.run([StepEntry(counter[0], toks, [PROMPT_LEN - 1])])
+            runner.run([StepEntry(counter[0], toks, [n_tok - 1])])
             counter[0] += 1
     for _ in range(max(args.warmup, 1)):
         step()
@@ -235,6 +236,8 @@ def main() -> int:
     ap.add_argument("--profile-region", choices=["decode", "prefill"], default=None,
                     help="for a profiler started with --profile-from-start off: run the set-up, then one eager "
                          "decode step (or one prefill) between cudaProfilerStart/Stop, print no bench line")
+    ap.add_argument("--profile-tokens", type=int, default=PROMPT_LEN,
+                    help="with --profile-region prefill: the prompt's length (the bench line's prefill is always 2,048)")
     args = ap.parse_args()
 
     if args.impl == "reference":

@@ -265,6 +265,15 @@ void plan_tiles(i64 M, i64 N, i64 K, i64 sms, i64* bn_out, i64* split_out) {
         return;
     }
     i64 bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+    if (bn == 256 && kblocks >= 64 && M > 256 && ceil_div(N, 256) * ceil_div(M, 128) < sms / 2) {
+        // A long K (the feed-forward's way back), three row tiles or more, too few tiles of 128 x 256 for the SMs: those tiles stay, whose
+        // products run nearer the tensor pipe's rate than narrower ones, and K is split until the SMs are filled; the
+        // pieces go through the workspace and a second kernel sums them.
+        const i64 t256 = ceil_div(N, 256) * ceil_div(M, 128);
+        *bn_out = 256;
+        *split_out = std::max<i64>(1, std::min({ceil_div(sms * 85 / 100, t256), kblocks / 4, (i64)16}));
+        return;
+    }
     if (bn == 256) {
         // The persistent kernel takes any width from 128 to 256 in steps of 16. A tile costs about 0.1 + 0.9 * width / 256
         // of a 256-wide one (a 128-wide one 0.55); the width whose waves finish soonest wins, the wider on a tie: it
@@ -281,10 +290,12 @@ void plan_tiles(i64 M, i64 N, i64 K, i64 sms, i64* bn_out, i64* split_out) {
         // Too few plain tiles to fill the GPU (a few hundred tokens, or a narrow product).
         if (M <= 128) {
             // up to two token tiles: swapped tiles of 128 weight rows by 64 tokens, the K split summed in a cluster
+            // (as for fewer tokens, no CTA with much more than ~300 KB of weights to stream by itself)
             const i64 stiles = ceil_div(N, 128) * ceil_div(M, 64);
             const i64 want = sms * 85 / 100;
+            const i64 stream = ceil_div(128 * K * 2, 300 * 1024);
             *bn_out = -64;
-            *split_out = stiles >= want ? 1 : std::max<i64>(1, std::min({ceil_div(want, stiles), kblocks / 4, (i64)8}));
+            *split_out = stiles >= want ? 1 : std::max<i64>(1, std::min({std::max(ceil_div(want, stiles), stream), kblocks / 4, (i64)8}));
             return;
         }
         // more tokens: tiles of 128 x 128 with K split until the SMs are filled; the pieces go through the

@@ -51,7 +51,7 @@ def test_tile_planning_properties():
                 assert bn == -64 and m <= 128 and split <= 8
             else:
                 assert (bn == 64 or (128 <= bn <= 256 and bn % 16 == 0)) and split <= 16
-                assert split == 1 or bn in (64, 128)          # the widths between are for unsplit products
+                assert split == 1 or bn in (64, 128, 256)     # the widths between are for unsplit products
     # a prompt of 2,048 tokens on 148 SMs: the q/k/v product (3,072 columns) in 16 x 18 tiles of 176 columns (two full
     # waves less a few), the products of 2,048 columns in 16 x 9 tiles of 240 (one wave)
     assert plan_tiles(2048, 3072, 2048, 148) == (176, 1) and plan_tiles(2048, 2048, 8192, 148) == (240, 1)
