@@ -31,6 +31,7 @@ def test_parse_tokens_and_default_blocks():
     ("workload", ["continuous", "long-context", "--shape", "--requests", "--prompt-min", "--prompt-max", "--gen",
                   "--long-prompt", "--prefill-chunk", "--max-batch-tokens", "--total-blocks"]),
     ("trace_run", ["--model", "--dtype", "--out", "--max-tokens"]),
+    ("kernel_timing", ["attention-decode", "product-chain"]),
 ])
 def test_tools_offer_their_options(tool, options):
     p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", tool), "--help"], capture_output=True, text=True, timeout=120)

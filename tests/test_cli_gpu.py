@@ -74,3 +74,13 @@ def test_bench_tool_reports_prefill_and_decode(tmp_path, dtype):
     assert re.search(r"^Prefill: 48 tokens in \d+\.\d+s$", out, re.M)
     m = re.search(r"^Decode: (\d+) tokens in \d+\.\d+s \((\d+\.\d+) tok/s\)$", out, re.M)
     assert m and int(m.group(1)) == 3 * 8 and float(m.group(2)) > 0
+
+
+def test_kernel_timing_tool_times_the_decode_kernels_alone():
+    """Small sizes: the tool runs the kernels it names through the wrappers serving uses and prints a line for each."""
+    out = run_tool("kernel_timing", "attention-decode", "--batch", 2, "--context", 700, "--pieces", 1, 4, 8, "--heads", 8,
+                   "--kv-heads", 2)
+    lines = re.findall(r"^attention_decode batch 2 context 700 pieces +(\d+): +(\d+\.\d+) us", out, re.M)
+    assert [int(p) for p, _ in lines] == [1, 4, 8] and all(float(us) > 0 for _, us in lines)
+    out = run_tool("kernel_timing", "product-chain", "--tokens", 5, "--hidden", 256, "--ff", 512)
+    assert len(re.findall(r"^5 tokens, .*: +\d+\.\d+ us a link", out, re.M)) == 4
