@@ -107,3 +107,27 @@ def test_decoding_past_a_graph_width_bucket(tmp_path, dtype):
                     dtype, f"{dtype} kernel by kernel vs graphs, request {i}", k=K_SELF[dtype])
         if dtype == "float32":
             assert tokens == tokens2
+
+
+def test_decoding_at_a_long_context_beside_a_short_one(tmp_path):
+    """One request with 2,300 tokens behind it decodes beside one with 20: the decode attention cuts the keys into 16
+    pieces (two clusters of eight CTAs that leave a piece each in the workspace), most of which are empty for the
+    short request. The logits of every decoded token against the plain model. (With random weights 2,300 keys weigh
+    about the same, so this run shows the step's wiring at that size: workspace, counters, graph replay; that no
+    piece is lost is shown where one key towers, test_kernels_gpu.py.)"""
+    from cellm_b200 import Engine, SamplingParams
+    from cellm_b200.runtime import program
+    folder = make_model(tmp_path, "tiny_b", overrides={"max_position_embeddings": 4096})
+    cfg, w = plain.load_folder(folder)
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (2300, 20)]
+    eng = Engine(folder, dtype="bfloat16", tokens_per_block=16, total_blocks=160, max_num_seqs=2, max_batch_tokens=4096,
+                 prefill_chunk=4096)
+    before = program.CALLS.get("cellm_attention_decode", 0)
+    outs, graph_steps, _ = run_engine(eng, prompts, SamplingParams.greedy(10, stop_eos=False))
+    assert graph_steps >= 8 and program.CALLS.get("cellm_attention_decode", 0) > before
+    for i, p in enumerate(prompts):
+        tokens, logits = outs[i]
+        seq = p + tokens[:-1]
+        ref = plain.forward(cfg, w, seq, rows=list(range(len(p) - 1, len(seq)))).numpy()
+        check_close(logits, ref, "bfloat16", f"request {i}")

@@ -446,6 +446,25 @@ def test_a_far_key_among_hundreds_is_found(kernel):
         close(out, attention_reference(c, nh, nkv, hd, 1.0, 0), dtype, f"far key {far}, all rows")
 
 
+@pytest.mark.parametrize("pieces", [8, 11, 16, 24])
+def test_a_far_key_among_thousands_through_every_way_the_decode_pieces_meet(pieces):
+    """2,500 keys cut into 8 pieces (one cluster), 11 (a piece per CTA through the workspace), 16 and 24 (clusters of
+    eight, a piece per cluster through the workspace); the towering key lies in the first piece, in a middle one (the
+    second cluster's where there are two) and in the last. A merge that loses a cluster's piece, or a piece of a
+    cluster, cannot pass; neither can one that keeps a stale piece of the call before (every call has another key)."""
+    from cellm_b200.ops.attention import attention_decode
+    nh, nkv, hd, ps = 4, 2, 64, 16
+    e = err_word()
+    for far in (7, 1290, 2499):
+        c = paged_case([1, 1], [2500, 70], nh, nkv, hd, ps, torch.bfloat16, seed=far, scale_one=(0, far, 1.0))
+        kh = c["k_seq"][0][far, 0]
+        c["q"][0, :hd] = (kh / kh.norm() * 60).to(torch.bfloat16).to(DEV)
+        out = attention_decode(c["q"], c["kp"], c["vp"], c["cu"], c["ctx"], c["bt"], 2, nh, 1.0, 0, e, pieces)
+        close(out[0, :hd], c["v_seq"][0][far, 0], torch.bfloat16, f"{pieces} pieces, far key {far}")
+        close(out, attention_reference(c, nh, nkv, hd, 1.0, 0), torch.bfloat16, f"{pieces} pieces, far key {far}, all rows")
+    assert e.item() == 0
+
+
 @pytest.mark.parametrize("hd,ps,nh,nkv", [(32, 8, 3, 1), (64, 16, 8, 2), (128, 32, 4, 4), (64, 4, 32, 8)])
 @pytest.mark.parametrize("window", [0, 33])
 def test_attention_flash(hd, ps, nh, nkv, window):
