@@ -964,10 +964,11 @@ static int gemm_impl(void* C, const void* A, const void* W, int M, int N, int K,
         else rc = launch<BN_, ST_, SW_, EP_, CL_, __nv_bfloat16>(m_rows, m_cols, (__nv_bfloat16*)C, workspace, counters, M, N, K, ldc, split, per, w_is_static, err, stream, conv, rope); \
     } while (0)
 #define GO2(BN_, ST_, SW_, EP_) GO3(BN_, ST_, SW_, EP_, false)
-    // swapped: ST_ stages without, CST_ stages with the cluster's reduction buffer (two CTAs must still fit an SM)
+    // swapped: ST_ stages without, CST_ stages with the cluster's reduction buffer (two CTAs must still fit an SM); the
+    // SwiGLU product, which has two CTAs an SM, takes three, so that a CTA of the product after it fits beside them
 #define GOS(BN_, ST_, CST_)                                                                                           \
     do {                                                                                                              \
-        if (in_cluster) { if (epilogue == 0) GO3(BN_, CST_, true, 0, true); else if (epilogue == 1) GO3(BN_, CST_, true, 1, true); else if (epilogue == 2) GO3(BN_, CST_, true, 2, true); else GO3(BN_, CST_, true, 3, true); } \
+        if (in_cluster) { if (epilogue == 0) GO3(BN_, CST_, true, 0, true); else if (epilogue == 1) GO3(BN_, (CST_ > 3 ? 3 : CST_), true, 1, true); else if (epilogue == 2) GO3(BN_, CST_, true, 2, true); else GO3(BN_, CST_, true, 3, true); } \
         else { if (epilogue == 0) GO3(BN_, ST_, true, 0, false); else GO3(BN_, ST_, true, 1, false); }                 \
     } while (0)
 #define GO(BN_, ST_, SW_)                           \
