@@ -54,6 +54,7 @@ def lib():
             "cellm_sched_plan_fill": ([c_void_p, c_void_p, c_int, c_int, c_int], c_int),
             "cellm_sched_append_rows": ([c_void_p, c_void_p, c_void_p, c_void_p, c_int], c_int),
             "cellm_sched_append": ([c_void_p, c_longlong, c_int, c_int], c_int),
+            "cellm_sched_resolve_rows": ([c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int], c_int),
             "cellm_sched_cancel": ([c_void_p, c_longlong], c_int),
             "cellm_sched_forget": ([c_void_p, c_longlong], c_int),
             "cellm_sched_has": ([c_void_p, c_longlong], c_int),

@@ -38,7 +38,7 @@ def continuous(args) -> dict:
     need = sum(-(-(n + args.gen) // page) for n in lens)
     pages = args.total_blocks or need + 8
     eng = Engine(loaded, dtype=args.dtype, tokens_per_block=page, total_blocks=pages, max_num_seqs=args.requests,
-                 max_batch_tokens=args.max_batch_tokens, prefill_chunk=args.prefill_chunk)
+                 max_batch_tokens=args.max_batch_tokens, prefill_chunk=args.prefill_chunk, run_ahead=not args.no_run_ahead)
     prompts = [rng.integers(0, V, n).tolist() for n in lens]
     eng.generate([p[:64] for p in prompts[:2]], SamplingParams.greedy(4, stop_eos=False))     # warm-up: loads the kernels
     torch.cuda.synchronize()
@@ -68,7 +68,7 @@ def long_context(args) -> dict:
     need = sum(-(-(n + gen) // page) for n in ctxs) + -(-(args.long_prompt + 8) // page)
     eng = Engine(loaded, dtype=args.dtype, tokens_per_block=page, total_blocks=args.total_blocks or need + 8,
                  max_num_seqs=args.requests + 1, max_batch_tokens=args.prefill_chunk + args.requests,
-                 prefill_chunk=args.prefill_chunk)
+                 prefill_chunk=args.prefill_chunk, run_ahead=not args.no_run_ahead)
     params = SamplingParams.greedy(gen, stop_eos=False)
     streams = [eng.add_request(rng.integers(0, V, n).tolist(), params) for n in ctxs]
     while any(eng.scheduler.info(r)["state"] != "decoding" for r in streams):
@@ -108,6 +108,8 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens-per-block", type=int, default=16)
     ap.add_argument("--total-blocks", type=int, default=None, help="pages (default: what all requests need at once)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-run-ahead", action="store_true",
+                    help="read every step's tokens before the next step is planned (EngineConfig.run_ahead = False)")
     args = ap.parse_args(argv)
     cont = args.workload == "continuous"
     args.shape = args.shape or ("lfm2-2.6b" if cont else "lfm2-700m")

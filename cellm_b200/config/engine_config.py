@@ -33,6 +33,10 @@ class EngineConfig:
     device: str = "cuda:0"
     seed: int = 1
     use_cuda_graphs: bool = True
+    # A captured decode step whose tokens are all arg-maxes leaves them on the device for the step after it, and the
+    # engine plans and launches that step before it reads them (its own work runs beside the GPU's); step() then
+    # returns a step's tokens one call later. False: every step's tokens are read before the next is planned.
+    run_ahead: bool = True
 
     def __post_init__(self):
         self.dtype = parse_dtype(self.dtype)

@@ -120,6 +120,49 @@ CELLM_API int cellm_argmax(int* out, const float* logits, int R, int V, unsigned
     return CELLM_OK;
 }
 
+// ------------------------------------------------------- tokens that stay on the device between two steps
+// The engine may launch a step before it has read the tokens of the step before (its own work for the next step then
+// runs beside the GPU's). The ids of such tokens come to this step as -1; their values are where the step before
+// left them: last[state slot of the token's request].
+__global__ void take_pending_tokens_kernel(int* __restrict__ ids, const int* __restrict__ seq_of_token,
+                                           const int* __restrict__ slot_ids, const int* __restrict__ last, int T,
+                                           int n_slots, int* __restrict__ err) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T || ids[t] >= 0) return;
+    const int slot = slot_ids[seq_of_token[t]];
+    if (slot < 0 || slot >= n_slots) { atomicOr(err, CELLM_DEV_BAD_SLOT); return; }
+    ids[t] = last[slot];
+}
+
+__global__ void keep_last_tokens_kernel(int* __restrict__ last, const int* __restrict__ slot_ids,
+                                        const int* __restrict__ tokens, int R, int n_slots) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    const int slot = slot_ids[r];
+    if (slot >= 0 && slot < n_slots) last[slot] = tokens[r];
+}
+
+// ids: [T] token ids of the step (changed in place where -1); seq_of_token: [T] entry of each token; slot_ids: one
+// per entry; last: [n_slots]. Launched as the first kernel of a step: it starts only when everything earlier on the
+// stream has finished.
+CELLM_API int cellm_take_pending_tokens(int* ids, const int* seq_of_token, const int* slot_ids, const int* last, int T,
+                                        int n_slots, int* err, cudaStream_t stream) {
+    if (T <= 0) return CELLM_OK;
+    CELLM_RUN_SERIAL(take_pending_tokens_kernel, (unsigned)((T + 127) / 128), 128, 0, stream, ids, seq_of_token, slot_ids,
+                     last, T, n_slots, err);
+    return CELLM_OK;
+}
+
+// last[slot_ids[r]] = tokens[r] for the R rows of a step in which every entry is one decoded token.
+CELLM_API int cellm_keep_last_tokens(int* last, const int* slot_ids, const int* tokens, int R, int n_slots,
+                                     cudaStream_t stream) {
+    if (R <= 0) return CELLM_OK;
+    CELLM_RUN(keep_last_tokens_kernel, (unsigned)((R + 127) / 128), 128, 0, stream, last, slot_ids, tokens, R, n_slots);
+    return CELLM_OK;
+}
+
 // ------------------------------------------------------- temperature sampling
 // One block per row. With top_k > 0 the k largest logits are the candidates, in
 // descending order of logit and ascending id among equal logits (a stable

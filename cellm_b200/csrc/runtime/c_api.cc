@@ -218,10 +218,23 @@ API int cellm_sched_append_rows(void* s, const int* tokens, const int* stops, in
         for (const auto& e : plan_of(s).entries) {
             if (!e.wants_logits) continue;
             if (r >= n) { g_error = "scheduler: fewer tokens than wanted rows"; return -3; }
+            // -2: the row's request ended meanwhile (a token of an earlier step, read after this step was planned,
+            // ended it): nothing is appended
+            if (tokens[r] == -2) { finished[r] = 1; ++r; continue; }
             finished[r] = sc->append_token(e.id, tokens[r], stops[r] != 0) ? 1 : 0;
             ++r;
         }
         return r;
+    });
+}
+// The values of tokens that were appended as pending: request ids, their places in the requests' tokens, the
+// values and whether each ends its request; finished[i] = 1 where the request is finished (or gone) afterwards.
+API int cellm_sched_resolve_rows(void* s, const long long* ids, const int* index, const int* tokens, const int* stops,
+                                 int* finished, int n) {
+    return guarded([&] {
+        auto* sc = static_cast<cellm::Scheduler*>(s);
+        for (int i = 0; i < n; ++i) finished[i] = sc->resolve_token(ids[i], index[i], tokens[i], stops[i] != 0) ? 1 : 0;
+        return n;
     });
 }
 API int cellm_sched_step_done(void* s) {

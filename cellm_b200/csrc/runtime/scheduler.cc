@@ -200,6 +200,24 @@ bool Scheduler::append_token(int64_t id, int32_t token, bool stop) {
     return false;
 }
 
+bool Scheduler::resolve_token(int64_t id, int index, int32_t token, bool stop) {
+    auto it = requests_.find(id);
+    if (it == requests_.end()) return true;           // cancelled and forgotten meanwhile
+    Request& r = it->second;
+    if (index < r.prompt_len || index >= (int)r.tokens.size() || r.tokens[index] != PENDING_TOKEN)
+        throw SchedulerError("scheduler: request " + std::to_string(id) + " has no pending token at " + std::to_string(index));
+    r.tokens[index] = token;
+    if (stop) {
+        // the request ends here; a token appended after this one came from a step that ran on it
+        if (r.state != RequestState::Finished) finish(r, "stop");
+        else r.finish_reason = "stop";
+        r.tokens.resize((size_t)index + 1);
+        r.generated = index + 1 - r.prompt_len;
+        return true;
+    }
+    return r.state == RequestState::Finished;
+}
+
 void Scheduler::cancel(int64_t id) {
     auto it = requests_.find(id);
     if (it == requests_.end()) throw SchedulerError("scheduler: unknown request " + std::to_string(id));

@@ -78,6 +78,12 @@ public:
     // Appends a sampled token; returns true when the request is finished
     // (max_new reached or `stop` set), in which case its pages and slot are freed.
     bool append_token(int64_t id, int32_t token, bool stop);
+    // A token may be appended as PENDING_TOKEN while the step that forms it still runs (the engine launches the
+    // next step before it has read this one's tokens; the kernels take the value from the device). resolve_token
+    // gives the value of the pending token at `index` of the request's tokens later. With `stop` the request ends
+    // at that token: whatever was appended after it is dropped. Returns true when the request is finished or gone.
+    static constexpr int32_t PENDING_TOKEN = -1;
+    bool resolve_token(int64_t id, int index, int32_t token, bool stop);
     void cancel(int64_t id);
     void forget(int64_t id);  // drops a finished request's record
 

@@ -51,6 +51,11 @@ class Engine:
         self._samplers: dict[int, RequestSampler] = {}
         self._outputs: dict[int, RequestOutput] = {}
         self._next_id = 0
+        self._prompt_len: dict[int, int] = {}
+        # the step whose tokens are still on the device: (requests in row order, where each token goes among its
+        # request's tokens, pinned buffer, rows, event after the copy), and how many such tokens each request has
+        self._ahead = None
+        self._pending: dict[int, int] = {}
         self._check_due = False
         self.max_layers: Optional[int] = None     # run only the first layers (tools/infer --max-layers)
         # Called after every step's forward pass with (ids of the requests whose logits were formed, in row
@@ -77,6 +82,7 @@ class Engine:
         self.scheduler.add_request(rid, prompt, params.max_new_tokens)
         self._samplers[rid] = RequestSampler(params, params.seed if seed is None else seed, prompt)
         self._outputs[rid] = RequestOutput(rid)
+        self._prompt_len[rid] = len(prompt)
         return rid
 
     def cancel(self, request_id: int) -> None:
@@ -90,37 +96,60 @@ class Engine:
         out.finish_reason = self.scheduler.info(rid)["finish_reason"]
         self.scheduler.forget(rid)
         self._samplers.pop(rid, None)
+        self._prompt_len.pop(rid, None)
+        self._pending.pop(rid, None)
 
     def has_unfinished(self) -> bool:
-        return not self.scheduler.stats()["idle"]
+        return self._ahead is not None or not self.scheduler.stats()["idle"]
 
     # ------------------------------------------------------------------ step
     def step(self) -> list[tuple[int, int]]:
-        """Runs one batch; returns (request, new token) for every request that
-        produced a token in it."""
+        """Plans and runs one batch; returns (request, new token) pairs. A captured decode step of greedy requests
+        leaves its tokens on the device (EngineConfig.run_ahead): they are returned by the next call, which has
+        launched its own step before it reads them. Otherwise the pairs are this step's."""
+        produced: list[tuple[int, int]] = []
+        before, self._ahead = self._ahead, None
         rows, preempted, admitted, n_entries = self.scheduler.schedule_rows()
         for rid, slot in admitted:
             self.cache.zero_slot(slot)
         if n_entries == 0 or preempted:
             for rid in list(self._outputs):
-                if not self._outputs[rid].finished and self.scheduler.has(rid) \
+                if not self._outputs[rid].finished and self.scheduler.has(rid) and not self._pending.get(rid) \
                         and self.scheduler.info(rid)["state"] == "finished":
                     self._finish(rid)     # the scheduler gave the request up (cannot fit)
         if n_entries == 0:
-            return []
+            if before is not None:
+                produced += self._settle(before)
+            return produced
         logits = self.runner.run_planned(self.scheduler, self.max_layers)
         self.scheduler.step_done()
-        produced = []
-        if rows:
+        ahead = bool(rows) and self._tokens_may_stay(rows)
+        if ahead:
+            # every row has a token, value to come; the scheduler counts it now (a request may end by its length)
+            self.scheduler.append_pending_rows(len(rows))
+            where = []
+            for rid in rows:
+                where.append(self._prompt_len[rid] + len(self._outputs[rid].tokens) + self._pending.get(rid, 0))
+                self._pending[rid] = self._pending.get(rid, 0) + 1
+            self._ahead = (list(rows), where) + self.runner.tokens_to_host()
+        if before is not None:
+            produced += self._settle(before)          # the step before this one: its tokens come first
+        if rows and not ahead:
             if self.on_logits is not None:
                 self.on_logits(list(rows), logits)
-            samplers = [self._samplers[r] for r in rows]
-            tokens = sample_rows(logits, samplers, self.runner.last_argmax)
+            live = [not self._outputs[r].finished for r in rows]      # a token just read may have ended a request of this step
+            samplers = [self._samplers.get(r) for r in rows]
+            if all(live):
+                tokens = sample_rows(logits, samplers, self.runner.last_argmax)
+            else:
+                tokens = self._sample_live(logits, samplers, live)
             self.runner.check_rarely()
             eos = self.plan.eos_token_id
-            stops = [s.params.stop_eos and eos is not None and tok == eos for s, tok in zip(samplers, tokens)]
-            finished = self.scheduler.append_rows(tokens, stops)
-            for rid, s, tok, fin in zip(rows, samplers, tokens, finished):
+            stops = [ok and s.params.stop_eos and eos is not None and tok == eos for ok, s, tok in zip(live, samplers, tokens)]
+            finished = self.scheduler.append_rows([tok if ok else -2 for ok, tok in zip(live, tokens)], stops)
+            for rid, ok, s, tok, fin in zip(rows, live, samplers, tokens, finished):
+                if not ok:
+                    continue
                 s.history.append(tok)
                 self._outputs[rid].tokens.append(tok)
                 produced.append((rid, tok))
@@ -129,6 +158,55 @@ class Engine:
         if self._check_due:
             self._check_due = False
             self.runner.check()
+        return produced
+
+    def _tokens_may_stay(self, rows) -> bool:
+        """The step just launched was a captured decode step and every one of its tokens is an arg-max."""
+        if not self.config.run_ahead or self.on_logits is not None or self.runner.last_argmax is None:
+            return False
+        if self.runner.last_argmax.numel() != len(rows):
+            return False
+        return all(self._samplers[r].params.temperature <= 0.0 for r in rows)
+
+    def _sample_live(self, logits, samplers, live) -> list[int]:
+        """sample_rows for the rows whose requests still run; -2 elsewhere."""
+        import torch
+        keep = [i for i, ok in enumerate(live) if ok]
+        out = [-2] * len(live)
+        if keep:
+            idx = torch.tensor(keep, dtype=torch.long, device=logits.device)
+            for i, tok in zip(keep, sample_rows(logits.index_select(0, idx), [samplers[i] for i in keep], None)):
+                out[i] = tok
+        return out
+
+    def _settle(self, ahead) -> list[tuple[int, int]]:
+        """Reads the tokens a step left on the device and gives them to the scheduler and the outputs."""
+        rows, where, buf, n, event = ahead
+        event.synchronize()
+        values = buf[:n].tolist()
+        self.runner.check_rarely()
+        eos = self.plan.eos_token_id
+        ids, index, tokens, stops = [], [], [], []
+        for rid, at, tok in zip(rows, where, values):
+            if rid in self._pending:
+                self._pending[rid] -= 1
+            if self._outputs[rid].finished:
+                continue              # ended by an earlier token (or cancelled) after this step was launched
+            ids.append(rid)
+            index.append(at)
+            tokens.append(tok)
+            stops.append(self._samplers[rid].params.stop_eos and eos is not None and tok == eos)
+        produced = []
+        if ids:
+            finished = self.scheduler.resolve_rows(ids, index, tokens, stops)
+            for rid, tok, stop, fin in zip(ids, tokens, stops, finished):
+                self._samplers[rid].history.append(tok)
+                self._outputs[rid].tokens.append(tok)
+                produced.append((rid, tok))
+                # a request that ended by its length did so when its last token was counted, which may be the token of
+                # the step after this one: it is finished here only once that one has been read too
+                if stop or (fin and not self._pending.get(rid)):
+                    self._finish(rid)
         return produced
 
     def output(self, request_id: int) -> RequestOutput:

@@ -89,6 +89,23 @@ class Scheduler:
                                               fin, n), SchedulerError)
         return [bool(fin[i]) for i in range(n)]
 
+    PENDING_TOKEN = -1
+
+    def append_pending_rows(self, n: int) -> list[bool]:
+        """One token per wanted row of the planned step whose value is not known yet (its step still runs);
+        returns which requests have all their tokens with it."""
+        return self.append_rows([self.PENDING_TOKEN] * n, [False] * n)
+
+    def resolve_rows(self, request_ids, indices, tokens, stops) -> list[bool]:
+        """The values of pending tokens (request, place among the request's tokens, value, whether it ends the
+        request); returns which requests are finished (or gone) afterwards."""
+        n = len(tokens)
+        fin = (ctypes.c_int * max(n, 1))()
+        ids = (ctypes.c_longlong * max(n, 1))(*[int(r) for r in request_ids])
+        checked(lib().cellm_sched_resolve_rows(self._h, ids, int_array(list(indices)), int_array(list(tokens)),
+                                               int_array([1 if x else 0 for x in stops]), fin, n), SchedulerError)
+        return [bool(fin[i]) for i in range(n)]
+
     def schedule_rows(self):
         """Plans the next step like schedule(), but returns only what the engine needs
         per step: (ids of the requests whose logits are wanted, in row order;

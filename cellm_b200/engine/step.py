@@ -63,6 +63,12 @@ class StepRunner:
         # arg-max of the last step's logits where the step's graph has computed it (greedy requests then
         # need no launch of their own); None after a step that ran without a graph
         self.last_argmax: Optional[torch.Tensor] = None
+        # The tokens a captured decode step chose, by state slot of their requests: the step after it takes the ids it
+        # was given as -1 from here (the engine may launch it before it has read this step's tokens).
+        self.last_token = torch.zeros(max(cache.num_slots, 1), dtype=torch.int32, device=self.device)
+        self._tok_host = [None, None]
+        self._tok_events = [None, None]
+        self._tok_flip = 0
 
     # ------------------------------------------------------------------
     def _staging(self, n: int) -> torch.Tensor:
@@ -273,7 +279,22 @@ class StepRunner:
         self._uploaded()
         ctx_lens = stage.numpy()[spans["ctx"][0]:spans["ctx"][0] + B].tolist()
         ctx, tabs, logit_rows = self._context(dev, spans, tables, q_lens, ctx_lens, max_total)
+        if self.device.type == "cuda":
+            ops.take_pending_tokens(ctx.token_ids, ctx.seq_of_token, ctx.slot_ids, self.last_token, self.err)
         return self._forward(ctx, self.cache.bindings(tabs), logit_rows, max_layers)
+
+    def tokens_to_host(self):
+        """Starts the copy of the last captured step's arg-max to pinned host memory; returns (pinned int32
+        tensor, number of rows, event recorded after the copy). Two buffers take turns."""
+        self._tok_flip ^= 1
+        i = self._tok_flip
+        n = self.last_argmax.numel()
+        if self._tok_host[i] is None or self._tok_host[i].numel() < n:
+            self._tok_host[i] = torch.empty(max(n, self.cache.num_slots, 64), dtype=torch.int32, pin_memory=True)
+            self._tok_events[i] = torch.cuda.Event()
+        self._tok_host[i][:n].copy_(self.last_argmax, non_blocking=True)
+        self._tok_events[i].record()
+        return self._tok_host[i], n, self._tok_events[i]
 
     def _capture(self, g: dict, spans, tables, q_lens, ctx_lens, max_total_len: int, slots) -> None:
         """Captures the forward pass over g["meta"] as a CUDA graph (see _run_decode_graph)."""
@@ -284,6 +305,7 @@ class StepRunner:
         # put back afterwards, because the captured run will update it again.
         slot_idx = torch.tensor(slots, dtype=torch.long, device=self.device)
         saved = [s[:, slot_idx].clone() for s in self.cache.states]
+        ops.take_pending_tokens(ctx.token_ids, ctx.seq_of_token, ctx.slot_ids, self.last_token, self.err)
         self.model.forward(ctx, bindings, logit_rows)
         for s, keep in zip(self.cache.states, saved):
             s[:, slot_idx] = keep
@@ -291,8 +313,10 @@ class StepRunner:
         graph = torch.cuda.CUDAGraph()
         before = LAUNCHES[0]
         with torch.cuda.graph(graph):
+            ops.take_pending_tokens(ctx.token_ids, ctx.seq_of_token, ctx.slot_ids, self.last_token, self.err)
             g["logits"] = self.model.forward(ctx, bindings, logit_rows)
             g["argmax"] = ops.argmax(g["logits"])          # greedy requests read their tokens here
+            ops.keep_last_tokens(self.last_token, ctx.slot_ids, g["argmax"])
         g["graph"] = graph
         g["launches"] = LAUNCHES[0] - before     # kernels one replay runs
         LAUNCHES[0] = before

@@ -27,6 +27,8 @@ _SIGNATURES = {
         "cellm_qk_norm_rope": [P, P, L, P, P, I, F, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, I, P, P],
         "cellm_attention_plain": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P],
         "cellm_argmax": [P, P, I, I, P, P],
+        "cellm_take_pending_tokens": [P, P, P, P, I, I, P, P],
+        "cellm_keep_last_tokens": [P, P, P, I, I, P],
         "cellm_sample": [P, P, I, I, P, P, P, P, P, I, I, P, P],
     },
     "gemm_plain": {

@@ -134,6 +134,22 @@ def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     return out
 
 
+def take_pending_tokens(ids: torch.Tensor, seq_of_token: torch.Tensor, slot_ids: torch.Tensor, last: torch.Tensor,
+                        err: torch.Tensor) -> None:
+    """Token ids of -1 (decoded tokens the host has not read yet) are replaced, in place, by last[state slot of the
+    token's request], where the step before left them."""
+    require_cuda(ids, seq_of_token, slot_ids, last, err)
+    check(fn(_LIB, "cellm_take_pending_tokens")(ptr(ids), ptr(seq_of_token), ptr(slot_ids), ptr(last), ids.numel(),
+                                                last.numel(), ptr(err), stream_of(ids)), "take_pending_tokens")
+
+
+def keep_last_tokens(last: torch.Tensor, slot_ids: torch.Tensor, tokens: torch.Tensor) -> None:
+    """last[slot_ids[r]] = tokens[r]: the tokens a decode step chose stay on the device for the step after it."""
+    require_cuda(last, slot_ids, tokens)
+    check(fn(_LIB, "cellm_keep_last_tokens")(ptr(last), ptr(slot_ids), ptr(tokens), tokens.numel(), last.numel(),
+                                             stream_of(tokens)), "keep_last_tokens")
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     """Row-wise arg-max of float32 logits [R, V] as int32 [R]; lowest id among equals."""
     require_cuda(logits)

@@ -286,3 +286,50 @@ def test_two_schedulers_keep_their_own_plans():
     s1.step_done()
     s2.step_done()
     assert s1.info(0)["computed"] == 5 and s2.info(7)["computed"] == 8
+
+
+def test_tokens_whose_values_come_later():
+    """A step's tokens may be counted before their values are known (the engine launches the next step before it
+    reads them): they are appended as pending, the next step is planned on them, and the values follow. A value that
+    ends its request drops what was counted after it; a request that ended by its length keeps all its tokens."""
+    cm, s = make(pages=32, slots=3, budget=16, chunk=8)
+    s.add_request(0, [1, 2, 3], 4)
+    s.add_request(1, [4, 5], 3)
+    plan = s.schedule()
+    s.step_done()
+    assert s.append_rows([10, 20], [False, False]) == [False, False]          # the prompts' tokens, read at once
+    # two decode steps counted ahead of their values
+    for _ in range(2):
+        plan = s.schedule()
+        assert [(e.request_id, e.count) for e in plan.entries] == [(0, 1), (1, 1)]
+        s.step_done()
+        fin = s.append_pending_rows(2)
+    assert fin == [False, True] and s.info(1)["state"] == "finished"          # request 1 has its three tokens
+    assert s.tokens(0) == [1, 2, 3, 10, -1, -1] and s.tokens(1) == [4, 5, 20, -1, -1]
+    # the plan's ids carry the pending marker: the kernels take the value from the device
+    plan = s.schedule()
+    assert [(e.request_id, e.start) for e in plan.entries] == [(0, 5)]
+    s.step_done()
+    assert s.append_pending_rows(1) == [True]                                  # and request 0 its four
+    # values: the first step's, then the second's in which request 0's token ends it
+    assert s.resolve_rows([0, 1], [4, 3], [11, 21], [False, False]) == [True, True]      # both have ended by their length
+    assert s.resolve_rows([0, 1], [5, 4], [12, 22], [True, False]) == [True, True]
+    assert s.tokens(0) == [1, 2, 3, 10, 11, 12] and s.info(0)["finish_reason"] == "stop" and s.info(0)["generated"] == 3
+    assert s.tokens(1) == [4, 5, 20, 21, 22] and s.info(1)["finish_reason"] == "length"
+    with pytest.raises(SchedulerError, match="no pending token"):
+        s.resolve_rows([1], [4], [9], [False])                                # given already
+    with pytest.raises(SchedulerError, match="no pending token"):
+        s.resolve_rows([1], [1], [9], [False])                                # a prompt token
+    assert s.resolve_rows([77], [0], [9], [False]) == [True]                  # a request nobody knows any more
+    s.forget(0)
+    s.forget(1)
+    assert s.stats()["idle"] and cm.free_slots == 3 and cm.free_pages(0) == 32
+    # a row whose request ended meanwhile is passed over when the step's tokens are appended
+    s.add_request(2, [1, 2], 5)
+    s.add_request(3, [3], 5)
+    s.schedule(); s.step_done()
+    assert s.append_rows([7, 8], [False, False]) == [False, False]
+    s.schedule(); s.step_done()
+    s.cancel(3)
+    assert s.append_rows([9, -2], [False, False]) == [False, True]
+    assert s.tokens(2) == [1, 2, 7, 9] and s.tokens(3) == [3, 8]
