@@ -60,7 +60,7 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
 }
 
-// ---- thread-block clusters: barrier over all threads of all CTAs, and reads of a peer's shared memory
+// ---- thread-block clusters: barrier over all threads of all CTAs, and stores into a peer's shared memory
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -74,14 +74,6 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ float ld_peer_shared(const float* local, uint32_t rank) {
-    uint32_t addr;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
-    return v;
-}
-
 // A float into the same place of the shared memory of CTA `rank` of this cluster.
 __device__ __forceinline__ void st_peer_shared(float* local, uint32_t rank, float v) {
     uint32_t addr;
