@@ -524,7 +524,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                 const int sub = pl / CONV_CH, cl = pl % CONV_CH, ch = (p0 / BM) * CONV_CH + cl;
                 const int rows = conv.ntaps - 1;
                 if (cv_active) {
-                    for (int ql = (int)rank + sub * splits, k = sub; q0 + ql < q_end; ql += 3 * splits, k += 3) {
+                    for (int ql = (int)rank + sub * splits, own = sub; q0 + ql < q_end; ql += 3 * splits, own += 3) {     // own: the token's slot among this CTA's
                         const int q = q0 + ql, slot = sm.conv_slots[ql];
                         float hist[CONV_MAX_TAPS - 1];
 #pragma unroll
@@ -538,7 +538,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
                                                  ? conv.state[(long long)sn * conv.slot_stride + (size_t)k * conv.H + ch] : 0.f;
                         }
                         if (slot < 0 || slot >= conv.n_slots) { atomicOr(err, CELLM_DEV_BAD_SLOT); continue; }
-                        const float* mine = &sm.red[k * BM + cl];
+                        const float* mine = &sm.red[own * BM + cl];
                         float b = 0.f, c = 0.f, x = 0.f;
 #pragma unroll
                         for (int r = 0; r < 8; ++r)
