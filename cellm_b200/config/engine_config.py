@@ -33,6 +33,10 @@ class EngineConfig:
     device: str = "cuda:0"
     seed: int = 1
     use_cuda_graphs: bool = True
+    # A decode step's shape (requests, block-table width bucket) is captured as a graph when it is met for this many
+    # times; before that its steps are launched kernel by kernel (a capture costs several steps' time, and a batch
+    # that shrinks as requests end meets many shapes once or twice).
+    capture_after: int = 3
     # A captured decode step whose tokens are all arg-maxes leaves them on the device for the step after it, and the
     # engine plans and launches that step before it reads them (its own work runs beside the GPU's); step() then
     # returns a step's tokens one call later. False: every step's tokens are read before the next is planned.
@@ -40,6 +44,6 @@ class EngineConfig:
 
     def __post_init__(self):
         self.dtype = parse_dtype(self.dtype)
-        for n in ("tokens_per_block", "total_blocks", "max_num_seqs", "max_batch_tokens", "prefill_chunk"):
+        for n in ("tokens_per_block", "total_blocks", "max_num_seqs", "max_batch_tokens", "prefill_chunk", "capture_after"):
             if getattr(self, n) <= 0:
                 raise ValueError(f"EngineConfig.{n} must be positive")

@@ -47,6 +47,7 @@ class Engine:
         self.cache = CacheManager(self.model.cache_needs(), [e.cache_of for e in self.plan.order],
                                   c.tokens_per_block, c.total_blocks, c.max_num_seqs, c.dtype, c.device)
         self.runner = StepRunner(self.model, self.cache, use_graphs=c.use_cuda_graphs)
+        self.runner.capture_after = c.capture_after
         self.scheduler = Scheduler(self.cache, c.max_batch_tokens, c.prefill_chunk, self.plan.max_positions)
         self._samplers: dict[int, RequestSampler] = {}
         self._outputs: dict[int, RequestOutput] = {}

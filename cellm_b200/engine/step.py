@@ -60,6 +60,11 @@ class StepRunner:
         # and activations (tens of MB at large batches), so a long-running engine keeps only the most recent ones.
         self._graphs: OrderedDict = OrderedDict()
         self.max_graphs = 128
+        # A shape is captured when it is met for the capture_after-th time; until then its steps are launched kernel
+        # by kernel. A capture costs several steps' time, and a batch that shrinks as requests end meets many shapes
+        # once or twice.
+        self.capture_after = 1
+        self._met: dict = {}
         # arg-max of the last step's logits where the step's graph has computed it (greedy requests then
         # need no launch of their own); None after a step that ran without a graph
         self.last_argmax: Optional[torch.Tensor] = None
@@ -209,6 +214,19 @@ class StepRunner:
         self.last_argmax = g["argmax"]
         return g["logits"]
 
+    def _ripe(self, key) -> bool:
+        """Whether a decode step of this (entries, width bucket) is to be replayed as a graph (capturing it if need be)."""
+        if key in self._graphs:
+            return True
+        n = self._met.get(key, 0) + 1
+        if n >= self.capture_after:
+            self._met.pop(key, None)
+            return True
+        if len(self._met) > 4096:
+            self._met.clear()
+        self._met[key] = n
+        return False
+
     def _graph_slot(self, key, n_meta: int) -> dict:
         """The record of the captured step for `key`, made (and the least recently used one dropped) if need be."""
         g = self._graphs.get(key)
@@ -247,6 +265,7 @@ class StepRunner:
         ps = self.cache.page_size
         need = (max_total + ps - 1) // ps
         graph = self.use_graphs and all_decode and max_layers is None
+        graph = graph and self._ripe((B, -(-need // self.graph_width_step) * self.graph_width_step))
         width = -(-need // self.graph_width_step) * self.graph_width_step if graph else need
         lay = self._layouts.get((B, T, R, width))
         if lay is None:
@@ -326,7 +345,10 @@ class StepRunner:
         the order of the entries and of their `want`, or None if nothing is wanted.
         The tensor may be overwritten by the next step."""
         if self.use_graphs and max_layers is None and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            return self._run_decode_graph(entries)
+            ps = self.cache.page_size
+            need = max((self.cache.tokens(e.request_id) + ps) // ps for e in entries)      # pages of tokens + 1
+            if self._ripe((len(entries), -(-need // self.graph_width_step) * self.graph_width_step)):
+                return self._run_decode_graph(entries)
         self.last_argmax = None
         ctx, tables, logit_rows, totals = self.build_context(entries)
         logits = self._forward(ctx, self.cache.bindings(tables), logit_rows, max_layers)

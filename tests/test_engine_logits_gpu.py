@@ -57,7 +57,7 @@ def test_logits_of_served_steps_with_many_live_requests(full_width, live):
     eng = Engine(loaded, dtype="bfloat16", tokens_per_block=16, total_blocks=6 * live, max_num_seqs=live,
                  max_batch_tokens=2048, prefill_chunk=512)
     outs, graph_steps, eager_steps = run_engine(eng, prompts, SamplingParams.greedy(n_new, stop_eos=False))
-    assert graph_steps >= n_new - 2 and eager_steps >= 1
+    assert graph_steps >= n_new - 4 and eager_steps >= 1          # a shape is captured when it is met the third time
     assert max(key[0] for key in eng.runner._graphs) == live, "no decode step held all the requests"
     # the plain model on every request (8 live) or every fourth (64 live): 64-bit on the CPU takes its time
     for i in range(0, live, 1 if live <= 8 else 4):
@@ -124,7 +124,7 @@ def test_decoding_at_a_long_context_beside_a_short_one(tmp_path):
     eng = Engine(folder, dtype="bfloat16", tokens_per_block=16, total_blocks=160, max_num_seqs=2, max_batch_tokens=4096,
                  prefill_chunk=4096)
     before = program.CALLS.get("cellm_attention_decode", 0)
-    outs, graph_steps, _ = run_engine(eng, prompts, SamplingParams.greedy(10, stop_eos=False))
+    outs, graph_steps, _ = run_engine(eng, prompts, SamplingParams.greedy(12, stop_eos=False))
     assert graph_steps >= 8 and program.CALLS.get("cellm_attention_decode", 0) > before
     for i, p in enumerate(prompts):
         tokens, logits = outs[i]
