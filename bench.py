@@ -7,7 +7,10 @@ Default run: LFM2-1.2B layer sizes, random bfloat16 weights, 8 requests with
 2,048-token random prompts in a cache sized for 8,192 tokens per request. A
 "step" is one decode step of the whole batch. One JSON line is printed:
 `value` = decoded tokens a second timed on the device, `e2e` = the same through
-the Python entry point with host tokens in and out, `prefill` = one 2,048-token
+the Python entry point with host tokens in and out (Engine.step(): every step uploads
+its index arrays from pinned memory and every step's tokens are read on the host; with
+EngineConfig.run_ahead, the default, a step's tokens are read after the next step has been
+launched, which takes them from the device), `prefill` = one 2,048-token
 prompt, `roofline` = the bytes a decode step has to read over its time,
 `points` = decoding at batch 1 and 64.
 """
@@ -338,7 +341,9 @@ def main() -> int:
                    "l2": "inputs larger than L2: %.2f GB of weights read every step" % (weight_bytes / 1e9),
                    "peaks": pk_src},
         "e2e": {"value": round(B / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                "tokens_read": "every step's, one step late: the next step is launched first" if eng.config.run_ahead
+                               else "every step's, before the next step is planned"},
         "gpu_launches": int(launches * args.steps),
         "prefill": {"value": round(PROMPT_LEN / (pf_ms * 1e-3), 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
                     "frac": round(pf_frac, 4)},
