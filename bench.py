@@ -289,6 +289,7 @@ def main() -> int:
     eng, ids = decode_setup(loaded, B, B * CONTEXT_LEN // PAGE, rng)
     dev_ms, e2e_ms, launches, h2d, d2h, ctx = time_decode(eng, ids, args.steps, args.warmup, rng, sampler)
     kv_bytes_tok = eng.cache.bytes_per_token()
+    run_ahead = bool(eng.config.run_ahead)
     for r in ids:
         eng.cancel(r)
     del eng
@@ -342,7 +343,7 @@ def main() -> int:
                    "peaks": pk_src},
         "e2e": {"value": round(B / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                "tokens_read": "every step's, one step late: the next step is launched first" if eng.config.run_ahead
+                "tokens_read": "every step's, one step late: the next step is launched first" if run_ahead
                                else "every step's, before the next step is planned"},
         "gpu_launches": int(launches * args.steps),
         "prefill": {"value": round(PROMPT_LEN / (pf_ms * 1e-3), 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
