@@ -84,3 +84,20 @@ def test_kernel_timing_tool_times_the_decode_kernels_alone():
     assert [int(p) for p, _ in lines] == [1, 4, 8] and all(float(us) > 0 for _, us in lines)
     out = run_tool("kernel_timing", "product-chain", "--tokens", 5, "--hidden", 256, "--ff", 512)
     assert len(re.findall(r"^5 tokens, .*: +\d+\.\d+ us a link", out, re.M)) == 4
+
+
+def test_bench_py_prints_its_line():
+    """The measurement script itself, shortened: one JSON line with the keys its readers take."""
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--steps", "4", "--warmup", "3", "--no-points"],
+                       capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-3000:]
+    lines = [l for l in p.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    rec = json.loads(lines[0])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "e2e", "gpu_launches", "prefill", "roofline", "clocks"):
+        assert key in rec, key
+    assert rec["n_gpus"] == 1 and rec["steps"] == 4 and rec["value"] > 0 and rec["gpu_launches"] > 0
+    assert rec["e2e"]["value"] > 0 and rec["e2e"]["h2d_bytes_per_step"] > 0 and rec["e2e"]["d2h_bytes_per_step"] > 0
+    assert rec["prefill"]["tokens"] == 2048 and 0 < rec["prefill"]["frac"] < 1.2 and 0 < rec["roofline"]["frac"] < 1.2
+    assert len(rec["config"]) <= 20 and all(not isinstance(v, (list, dict)) for v in rec["config"].values())
